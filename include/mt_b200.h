@@ -1,0 +1,141 @@
+/*
+ * C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * Every entry point takes raw device pointers, 64-bit sizes and a CUDA stream, launches
+ * asynchronously on that stream, allocates nothing, never synchronises the device and
+ * returns 0 on success or a negative mt_status on failure (mt_last_error_string() then
+ * describes it for the calling thread). Pointers must be 16-byte aligned unless stated.
+ *
+ * Reference interfaces these replace are cited per function as file:line inside
+ * fy1214/miniTransformer.
+ */
+#ifndef MT_B200_H_
+#define MT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* mt_stream_t; /* cudaStream_t */
+
+enum mt_status {
+  MT_OK = 0,
+  MT_ERR_INVALID_ARG = -1,   /* null pointer, bad shape, bad alignment, bad flag */
+  MT_ERR_UNSUPPORTED = -2,   /* valid request this build does not implement */
+  MT_ERR_CUDA = -3,          /* a CUDA runtime / driver call failed */
+  MT_ERR_DEVICE_TIMEOUT = -4 /* a bounded device-side wait expired (see mt_read_device_status) */
+};
+
+/* Output element types of the GEMM entry points. */
+enum mt_dtype { MT_BF16 = 0, MT_F32 = 1 };
+
+/* Flags of mt_quantize_nvfp4 / mt_amax_bf16. */
+enum mt_quantize_flags {
+  MT_Q_2D = 1,       /* one scale per 16x16 block, shared by both copies */
+  MT_Q_RHT = 2,      /* 16-point randomized Hadamard transform on the transposed copy */
+  MT_Q_ROWPAD16 = 4  /* scale tensors have their row count padded to a multiple of 16 */
+};
+
+int mt_version(void);
+const char* mt_last_error_string(void);
+
+/* Number of bytes of the GEMM-ready ("swizzled") scale-factor tensor for an operand with
+ * `rows` rows and `k_blocks` scale factors per row: ceil(rows/128) x ceil(k_blocks/4)
+ * chunks of 512 bytes, chunk (rb, kc) holding rows rb*128.. and blocks kc*4.., byte
+ * (r%32)*16 + (r/32)*4 + (kb%4); the K-chunk count is rounded up to a multiple of 4.
+ * This is the layout the reference anticipates for its cuBLASLt call
+ * (miniTransformer/csrc/util/common.h:29-33, csrc/ops/fp4/gemm/gemm_cublas.cu:275-277). */
+int64_t mt_swizzled_scale_bytes(int64_t rows, int64_t k_blocks);
+
+/* Per-tensor abs-max of a bf16 matrix x[rows, cols] (row stride = cols).
+ * amax_row <- max|x|. If amax_col is non-null: with MT_Q_RHT it receives the abs-max of the
+ * Hadamard-transformed transpose (groups of 16 consecutive rows of one column, fixed sign
+ * vector, scale 1/4, rounded to bf16), otherwise a copy of amax_row. Both are device fp32
+ * scalars and are overwritten. rows % 16 == 0 is required with MT_Q_RHT; cols % 8 == 0 always.
+ * Replaces the two torch.max(torch.abs(.)) reductions of
+ * miniTransformer/ops/nvfp4_quantize_op_ref.py:357-369. */
+int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags,
+                 float* amax_row, float* amax_col, mt_stream_t stream);
+
+/* NVFP4 cast (+ transpose): E2M1 codes packed two per byte (even column in the low
+ * nibble), one E4M3 scale per 1x16 block (or per 16x16 block with MT_Q_2D), using the
+ * per-tensor abs-max values already on the device (mt_amax_bf16, optionally max-reduced
+ * across ranks by the caller).
+ *   x        bf16 [rows, cols], cols % 16 == 0, rows % 2 == 0
+ *   q        u8 [rows, cols/2]
+ *   s        u8 (E4M3) [rows_s, cols/16], row stride s_stride bytes; rows_s = rows, or rows
+ *            rounded up to 16 with MT_Q_ROWPAD16 / MT_Q_2D (padded rows are written as 0)
+ *   s_swz    optional GEMM-ready copy of s (mt_swizzled_scale_bytes(rows, cols/16) bytes)
+ *   q_t      optional u8 [cols, rows/2]: codes of x^T (after the transform with MT_Q_RHT)
+ *   s_t      u8 [cols_s, ceil(rows/16)], row stride s_t_stride; required iff q_t
+ *   s_t_swz  optional GEMM-ready copy of s_t
+ * Replaces fp4_gemm.quantize_transpose_nvfp4 (miniTransformer/csrc/ops.h:7-15,
+ * csrc/ops/fp4/quantization/quantize_transpose_nvfp4.cu:1136-1228) with the arithmetic of
+ * Nvfp4TiledQuantizeRefOp._quantize (miniTransformer/ops/nvfp4_quantize_op_ref.py:258-417). */
+int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags,
+                      const float* amax_row, const float* amax_col,
+                      uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                      uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                      mt_stream_t stream);
+
+/* MXFP8 cast (+ transpose): E4M3 elements, one E8M0 scale byte (exponent + 127) per 1x32
+ * block. Scale rule: 2^ceil(log2(amax/448)) clamped to 2^+-127 (cast_to_e8,
+ * miniTransformer/ops/nvfp4_quantize_op_ref.py:12-21).
+ *   x bf16 [rows, cols], cols % 32 == 0; q u8 [rows, cols]; s u8 [rows, cols/32];
+ *   q_t optional u8 [cols, rows] (x^T, blocks along rows; a ragged row count is padded
+ *   with zeros to 32 for the scale); s_t u8 [cols, ceil(rows/32)]; *_swz as above. */
+int mt_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
+                      uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                      uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                      mt_stream_t stream);
+
+/* Row-major scale bytes s[rows, k_blocks] (row stride s_stride) -> GEMM-ready layout.
+ * Rows / blocks beyond the source extent are written as 0. */
+int mt_swizzle_scales(const uint8_t* s, int64_t rows, int64_t k_blocks, int64_t s_stride,
+                      uint8_t* s_swz, mt_stream_t stream);
+
+/* Block-scaled GEMM  D[M,N] = alpha * (A . B^T) (+ bias[N]) (+ D when accumulate), both
+ * operands K-major, fp32 accumulation in tensor memory (tcgen05.mma, block_scale).
+ *   NVFP4: a u8 [M, K/2], b u8 [N, K/2], K % 32 == 0, scales E4M3 per 16, swizzled layout;
+ *          alpha = amax_a[0] * amax_b[0] / (6*6*448*448) read on the device.
+ *   MXFP8: a u8 [M, K],   b u8 [N, K],   K % 16 == 0, scales E8M0 per 32; alpha = 1.
+ *   d: bf16 or fp32 [M, N] with row stride ldd elements; bias: optional fp32/bf16 per
+ *   bias_dtype; accumulate != 0 adds the previous contents of d (fp32 add, then rounding).
+ * Replaces QuantizeOpBase.qgemm (miniTransformer/ops/quantization.py:121-160), i.e. the
+ * emulation Nvfp4TiledQuantizeRefOp._ref_qgemm (ops/nvfp4_quantize_op_ref.py:449-560) and
+ * the cuBLASLt call the reference intended (csrc/ops/fp4/gemm/gemm_cublas.cu:75-255). */
+int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a,
+                  const uint8_t* b, const uint8_t* sb_swz, const float* amax_b,
+                  int64_t M, int64_t N, int64_t K,
+                  void* d, int d_dtype, int64_t ldd,
+                  const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
+
+int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz,
+                  const uint8_t* b, const uint8_t* sb_swz,
+                  int64_t M, int64_t N, int64_t K,
+                  void* d, int d_dtype, int64_t ldd,
+                  const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
+
+/* Same contracts, computed by a plain CUDA-core kernel that follows the emulation's
+ * summation structure (per-block fp32 dot, scaled, fp32 accumulate). Scales are given in
+ * the row-major layout. It exists so the tensor-core kernels can be checked on the device at
+ * sizes where a CPU check would take minutes; it is not a product path. */
+int mt_gemm_nvfp4_check(const uint8_t* a, const uint8_t* sa, int64_t sa_stride, const float* amax_a,
+                        const uint8_t* b, const uint8_t* sb, int64_t sb_stride, const float* amax_b,
+                        int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
+                        int accumulate, mt_stream_t stream);
+int mt_gemm_mxfp8_check(const uint8_t* a, const uint8_t* sa, int64_t sa_stride,
+                        const uint8_t* b, const uint8_t* sb, int64_t sb_stride,
+                        int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
+                        int accumulate, mt_stream_t stream);
+
+/* Reads and clears the device-side status word the kernels raise when a bounded wait
+ * expires (0 = clean). Synchronises the given stream. */
+int mt_read_device_status(int* status_out, mt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MT_B200_H_ */

@@ -1,0 +1,73 @@
+"""ctypes binding of libmt_b200.so, the C-ABI library of sm_100a kernels.
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+import re
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmt_b200.so")
+HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "mt_b200.h")
+
+MT_BF16, MT_F32 = 0, 1
+MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16 = 1, 2, 4
+
+_c = ctypes
+_vp, _i64, _int = _c.c_void_p, _c.c_int64, _c.c_int
+
+_SIGNATURES = {
+    "mt_version": (_int, []),
+    "mt_last_error_string": (_c.c_char_p, []),
+    "mt_swizzled_scale_bytes": (_i64, [_i64, _i64]),
+    "mt_amax_bf16": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "mt_quantize_nvfp4": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "mt_quantize_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "mt_swizzle_scales": (_int, [_vp, _i64, _i64, _i64, _vp, _vp]),
+    "mt_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
+    "mt_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
+    "mt_gemm_nvfp4_check": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
+    "mt_gemm_mxfp8_check": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
+    "mt_read_device_status": (_int, [_c.POINTER(_int), _vp]),
+}
+
+_lib = None
+
+
+class MtError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+
+def declared_symbols(header_path: str = HEADER_PATH):
+    """Names of every function the public header declares."""
+    text = open(header_path).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mt_[a-z0-9_]+)\s*\(", text)))
+
+
+def load():
+    """Loads the shared library (once) and sets the argument types."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise MtError(
+            f"{LIB_PATH} is missing: build it with `python -m minitransformer_b200.build` "
+            "(there is no CPU or PyTorch fallback for these kernels)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str = "") -> None:
+    if status != 0:
+        msg = load().mt_last_error_string().decode(errors="replace")
+        raise MtError(f"{what or 'libmt_b200'} failed with status {status}: {msg}")
+
+
+def call(name: str, *args) -> None:
+    check(getattr(load(), name)(*args), name)

@@ -1,0 +1,506 @@
+// Block-scaled GEMM for sm_100a: D[M,N] = alpha * (A . B^T) with FP4 (E2M1, E4M3 scale per
+// 16) or FP8 (E4M3, E8M0 scale per 32) operands, both K-major, fp32 accumulation in tensor
+// memory.
+//
+// Persistent, warp-specialised CTA (one per SM, 192 threads):
+//   warp 0     TMA producer: per K step one 2-D tiled load each for the A and B tiles
+//              (128-byte rows, 128-byte swizzle) and 1-D bulk copies of the scale-factor
+//              chunks, all completing on the stage's "full" mbarrier;
+//   warp 1     allocates tensor memory; one elected lane copies the scale factors
+//              shared -> tensor memory (tcgen05.cp) and issues tcgen05.mma ... block_scale,
+//              releasing each shared-memory stage with tcgen05.commit;
+//   warps 2-5  epilogue: tcgen05.ld of the 128 x BLOCK_N fp32 accumulator (one 32-lane
+//              quarter per warp), alpha / bias / accumulate, conversion, global stores.
+// Every wait on an mbarrier is bounded; on expiry the CTA raises a bit in the device status
+// word, abandons its remaining tiles, frees its tensor memory and exits.
+//
+// The grouped variants reuse the same kernel: a tile is described by (group, m block,
+// n block) and the operand / output bases are looked up per group.
+#include <algorithm>
+
+#include "mt_common.cuh"
+
+namespace mt {
+
+constexpr int G_BLOCK_M = 128;
+constexpr int G_BLOCK_KB = 128;  // bytes of K per row per stage (256 FP4 or 128 FP8 elements)
+constexpr int G_THREADS = 192;
+constexpr int G_TMEM_COLS = 512;
+
+enum GemmFormat : int { FMT_NVFP4 = 0, FMT_MXFP8 = 1 };
+enum GemmMode : int { MODE_DENSE = 0, MODE_GROUPED_ROWS = 1, MODE_GROUPED_K = 2 };
+
+constexpr int kMaxGroups = 256;
+
+struct GemmArgs {
+  // operands
+  const uint8_t* sa;   // A scale factors, chunk layout
+  const uint8_t* sb;   // B scale factors, chunk layout
+  int64_t kc_a, kc_b;  // chunks per 128-row block in sa / sb
+  int64_t rb_a, rb_b;  // number of 128-row blocks available in sa / sb
+  int64_t M, N, K_bytes;
+  // output
+  void* d;
+  int64_t ldd;
+  int d_dtype;
+  const void* bias;
+  int bias_dtype;
+  int accumulate;
+  const float* amax_a;
+  const float* amax_b;
+  int* status;
+  // tiling
+  int tiles_m, tiles_n, num_tiles;
+  // grouping
+  int mode;
+  int num_groups;
+  const int64_t* group_offsets;  // device int64[G+1]: row (MODE_GROUPED_ROWS) or K-element
+                                 // (MODE_GROUPED_K) offsets, multiples of 128
+  const int32_t* tile_group;     // device int32[num_tiles]  (grouped modes)
+  const int32_t* tile_mblk;      // device int32[num_tiles]: m block inside the group (rows mode)
+  int64_t b_group_rows;          // rows of B per group (MODE_GROUPED_ROWS): N
+  int64_t d_group_stride;        // elements between consecutive group outputs (MODE_GROUPED_K)
+  int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
+};
+
+template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
+struct GemmCfg {
+  static constexpr int CH = (kFormat == FMT_NVFP4) ? 4 : 1;   // SF chunks per stage per 128 rows
+  static constexpr int NH = BLOCK_N / 128;                    // 128-row halves of the B tile
+  static constexpr int A_BYTES = G_BLOCK_M * G_BLOCK_KB;
+  static constexpr int B_BYTES = BLOCK_N * G_BLOCK_KB;
+  static constexpr int SFA_BYTES = CH * 512;
+  static constexpr int SFB_BYTES = NH * CH * 512;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = STAGES * A_BYTES;
+  static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
+  static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
+  static constexpr int OFF_BAR = OFF_SFB + STAGES * SFB_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * ACC_STAGES;
+  static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16;
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack for manual 1024-byte alignment
+  static constexpr int TMEM_ACC = 0;
+  static constexpr int TMEM_SFA = ACC_STAGES * BLOCK_N;
+  static constexpr int TMEM_SFB = TMEM_SFA + 4 * CH;
+  static_assert(TMEM_SFB + 4 * CH * NH <= G_TMEM_COLS, "tensor memory over-subscribed");
+  static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory over-subscribed");
+};
+
+__device__ __forceinline__ uint32_t make_idesc(int format, int block_n, int sf_id) {
+  uint32_t d = 0;
+  if (format == FMT_NVFP4) {
+    d |= 1u << 7;   // A: E2M1
+    d |= 1u << 10;  // B: E2M1
+    // scale format UE4M3 = 0 at bit 23
+  } else {
+    // A, B: E4M3 = 0
+    d |= 1u << 23;                             // scale format UE8M0
+    d |= static_cast<uint32_t>(sf_id) << 4;    // B scale-factor byte inside the 32-bit column
+    d |= static_cast<uint32_t>(sf_id) << 29;   // A scale-factor byte
+  }
+  d |= static_cast<uint32_t>(block_n >> 3) << 17;
+  d |= static_cast<uint32_t>(G_BLOCK_M >> 4) << 24;
+  return d;
+}
+
+template <int kFormat>
+__device__ __forceinline__ void issue_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if (kFormat == FMT_NVFP4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
+struct TileCoord {
+  int64_t a_row0;      // first row of the A tile (TMA y coordinate)
+  int64_t b_row0;      // first row of the B tile
+  int64_t k_byte0;     // first K byte (TMA x coordinate) of the contraction range
+  int num_k;           // K steps of 128 bytes
+  int64_t sfa_rb;      // 128-row block index into sa
+  int64_t sfb_rb;      // 128-row block index into sb (first half)
+  int64_t sf_kc0;      // first chunk index along K in sa / sb
+  int64_t d_row0;      // first output row
+  int64_t d_col0;      // first output column
+  int64_t d_rows_end;  // exclusive bound on output rows for this tile's group
+  int64_t d_base;      // element offset of the group's output matrix
+};
+
+template <int kFormat, int BLOCK_N>
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int tile) {
+  constexpr int CH = (kFormat == FMT_NVFP4) ? 4 : 1;
+  TileCoord t;
+  const int nb = tile / a.tiles_m;
+  int mb = tile - nb * a.tiles_m;
+  t.k_byte0 = 0;
+  t.num_k = (int)((a.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB);
+  t.sf_kc0 = 0;
+  t.d_base = 0;
+  if (a.mode == MODE_DENSE) {
+    t.a_row0 = (int64_t)mb * G_BLOCK_M;
+    t.b_row0 = (int64_t)nb * BLOCK_N;
+    t.d_row0 = t.a_row0;
+    t.d_rows_end = a.M;
+  } else if (a.mode == MODE_GROUPED_ROWS) {
+    // tiles are enumerated n-block major over a flattened list of (group, m block)
+    const int g = a.tile_group[mb];
+    const int64_t g0 = a.group_offsets[g];
+    t.a_row0 = g0 + (int64_t)a.tile_mblk[mb] * G_BLOCK_M;
+    t.b_row0 = (int64_t)g * a.b_group_rows + (int64_t)nb * BLOCK_N;
+    t.d_row0 = t.a_row0;
+    t.d_rows_end = a.group_offsets[g + 1];
+  } else {
+    // MODE_GROUPED_K: tile index = ((g * tiles_n) + nb) * tiles_m + mb, regrouped by the caller
+    const int per_group = a.tiles_m * a.tiles_n;
+    const int g = tile / per_group;
+    const int r = tile - g * per_group;
+    const int nb2 = r / a.tiles_m;
+    mb = r - nb2 * a.tiles_m;
+    const int64_t e0 = a.group_offsets[g], e1 = a.group_offsets[g + 1];
+    t.a_row0 = (int64_t)mb * G_BLOCK_M;
+    t.b_row0 = (int64_t)nb2 * BLOCK_N;
+    t.k_byte0 = e0 * 2 / a.k_elems_per_byte_x2;
+    t.num_k = (int)(((e1 - e0) * 2 / a.k_elems_per_byte_x2 + G_BLOCK_KB - 1) / G_BLOCK_KB);
+    t.sf_kc0 = t.k_byte0 / G_BLOCK_KB * CH;
+    t.d_row0 = t.a_row0;
+    t.d_rows_end = a.M;
+    t.d_base = (int64_t)g * a.d_group_stride;
+    t.sfa_rb = mb;
+    t.sfb_rb = (int64_t)nb2 * (BLOCK_N / 128);
+    t.d_col0 = t.b_row0;
+    return t;
+  }
+  t.sfa_rb = t.a_row0 / 128;
+  t.sfb_rb = t.b_row0 / 128;
+  t.d_col0 = (int64_t)nb * BLOCK_N;
+  return t;
+}
+
+template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
+__global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                        const __grid_constant__ CUtensorMap map_b,
+                                                                        const GemmArgs a) {
+  using Cfg = GemmCfg<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
+  constexpr int CH = Cfg::CH, NH = Cfg::NH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* acc_full = bars + 2 * STAGES;
+  uint64_t* acc_empty = bars + 2 * STAGES + ACC_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < ACC_STAGES; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    mbar_fence_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, G_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < a.num_tiles && alive; tile += gridDim.x) {
+        const TileCoord t = tile_coord<kFormat, BLOCK_N>(a, tile);
+        for (int k = 0; k < t.num_k; ++k, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.status, DS_EMPTY_WAIT)) { alive = false; break; }
+          uint32_t bytes = Cfg::A_BYTES + Cfg::B_BYTES + Cfg::SFA_BYTES;
+          int nh_valid = 0;
+#pragma unroll
+          for (int h = 0; h < NH; ++h) nh_valid += (t.sfb_rb + h < a.rb_b) ? 1 : 0;
+          bytes += nh_valid * CH * 512;
+          mbar_expect_tx(&full_bar[s], bytes);
+          const int32_t kx = (int32_t)(t.k_byte0 + (int64_t)k * G_BLOCK_KB);
+          tma_load_2d(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, &full_bar[s], kx, (int32_t)t.a_row0);
+          tma_load_2d(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, &full_bar[s], kx, (int32_t)t.b_row0);
+          const int64_t kc = t.sf_kc0 + (int64_t)k * CH;
+          bulk_load_1d(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, a.sa + (t.sfa_rb * a.kc_a + kc) * 512, CH * 512,
+                       &full_bar[s]);
+#pragma unroll
+          for (int h = 0; h < NH; ++h) {
+            if (t.sfb_rb + h < a.rb_b)
+              bulk_load_1d(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + h * CH * 512,
+                           a.sb + ((t.sfb_rb + h) * a.kc_b + kc) * 512, CH * 512, &full_bar[s]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (elect_one()) {
+      uint32_t it = 0, tile_it = 0;
+      bool alive = true;
+      const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
+      const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
+      for (int tile = blockIdx.x; tile < a.num_tiles && alive; tile += gridDim.x, ++tile_it) {
+        const TileCoord t = tile_coord<kFormat, BLOCK_N>(a, tile);
+        const int as = tile_it % ACC_STAGES;
+        const uint32_t aph = (tile_it / ACC_STAGES) & 1;
+        if (!mbar_wait_bounded(&acc_empty[as], aph ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + as * BLOCK_N;
+        for (int k = 0; k < t.num_k; ++k, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
+          tc_fence_after();
+          // scale factors: shared -> tensor memory
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            tc_copy_sf(tmem_base + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
+#pragma unroll
+          for (int h = 0; h < NH; ++h)
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+              tc_copy_sf(tmem_base + Cfg::TMEM_SFB + 4 * (c * NH + h),
+                         umma_desc_sf(sfb_base + s * Cfg::SFB_BYTES + (h * CH + c) * 512));
+          const uint64_t adesc = umma_desc_sw128(a_base + s * Cfg::A_BYTES);
+          const uint64_t bdesc = umma_desc_sw128(b_base + s * Cfg::B_BYTES);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t idesc = make_idesc(kFormat, BLOCK_N, j);
+            const uint32_t sfa_t = tmem_base + Cfg::TMEM_SFA + (kFormat == FMT_NVFP4 ? 4 * j : 0);
+            const uint32_t sfb_t = tmem_base + Cfg::TMEM_SFB + (kFormat == FMT_NVFP4 ? 4 * NH * j : 0);
+            issue_mma<kFormat>(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, (k > 0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);
+        }
+        if (alive) tc_commit(&acc_full[as]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================= epilogue =================
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    float alpha = 1.0f;
+    if (a.amax_a != nullptr && a.amax_b != nullptr)
+      alpha = __fdiv_rn(__fmul_rn(*a.amax_a, *a.amax_b), 6.0f * 6.0f * 448.0f * 448.0f);
+    uint32_t tile_it = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < a.num_tiles && alive; tile += gridDim.x, ++tile_it) {
+      const TileCoord t = tile_coord<kFormat, BLOCK_N>(a, tile);
+      const int as = tile_it % ACC_STAGES;
+      const uint32_t aph = (tile_it / ACC_STAGES) & 1;
+      if (t.num_k == 0) {
+        // empty contraction: the MMA warp still signals the barrier pair; result is all zeros
+      }
+      if (!mbar_wait_bounded(&acc_full[as], aph, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
+      tc_fence_after();
+      const int64_t row = t.d_row0 + q * 32 + lane;
+      const bool row_ok = row < t.d_rows_end;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + as * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
+        tc_wait_ld();
+        const int64_t col0 = t.d_col0 + c * 32;
+        if (row_ok && col0 < a.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = (t.num_k > 0) ? __fmul_rn(alpha, __uint_as_float(r[i])) : 0.0f;
+          const int nvalid = (int)min((int64_t)32, a.N - col0);
+          if (a.bias != nullptr) {
+            for (int i = 0; i < nvalid; ++i)
+              v[i] += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col0 + i]
+                                               : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col0 + i]);
+          }
+          const int64_t off = t.d_base + row * a.ldd + col0;
+          if (a.d_dtype == MT_F32) {
+            float* dst = static_cast<float*>(a.d) + off;
+            if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+              float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (a.accumulate) { float4 p = d4[i]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
+                d4[i] = o;
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) dst[i] = a.accumulate ? dst[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + off;
+            if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if (a.accumulate) {
+                  uint4 p = d4[i];
+                  const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    v[8 * i + 2 * j] += __uint_as_float(pw[j] << 16);
+                    v[8 * i + 2 * j + 1] += __uint_as_float(pw[j] & 0xFFFF0000u);
+                  }
+                }
+                uint32_t ow[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+                  ow[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                d4[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+              }
+            } else {
+              for (int i = 0; i < nvalid; ++i) {
+                float o = a.accumulate ? __bfloat162float(dst[i]) + v[i] : v[i];
+                dst[i] = __float2bfloat16_rn(o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, G_TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t st) {
+  using Cfg = GemmCfg<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
+  auto kern = gemm_blockscaled_kernel<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    attr_set = true;
+  }
+  const int grid = std::min(args.num_tiles, sm_count());
+  kern<<<grid, G_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, args);
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
+static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
+
+// Environment override used while tuning: MT_GEMM_BLOCK_N = 128 or 256.
+static int pick_block_n(int64_t N) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("MT_GEMM_BLOCK_N");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 128 || forced == 256) return forced;
+  return N > 128 ? 256 : 128;
+}
+
+static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const float* amax_a, const uint8_t* b,
+                       const uint8_t* sb, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,
+                       int64_t ldd, const void* bias, int bias_dtype, int accumulate, cudaStream_t st) {
+  const char* name = format == FMT_NVFP4 ? "mt_gemm_nvfp4" : "mt_gemm_mxfp8";
+  MT_REQUIRE(a && sa && b && sb && d, "%s: null pointer", name);
+  MT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative shape", name);
+  MT_REQUIRE(d_dtype == MT_BF16 || d_dtype == MT_F32, "%s: output dtype %d not supported", name, d_dtype);
+  MT_REQUIRE(bias == nullptr || bias_dtype == MT_BF16 || bias_dtype == MT_F32, "%s: bias dtype %d not supported", name, bias_dtype);
+  MT_REQUIRE(ldd >= N, "%s: ldd (%lld) smaller than N (%lld)", name, (long long)ldd, (long long)N);
+  const int64_t kmult = format == FMT_NVFP4 ? 32 : 16;
+  MT_REQUIRE(K % kmult == 0, "%s: K (%lld) must be a multiple of %lld", name, (long long)K, (long long)kmult);
+  MT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sa) && aligned16(sb), "%s: operands must be 16-byte aligned", name);
+  if (format == FMT_NVFP4) MT_REQUIRE(amax_a && amax_b, "%s: per-tensor abs-max pointers are required", name);
+  if (M == 0 || N == 0) return MT_OK;
+  const int64_t K_bytes = format == FMT_NVFP4 ? K / 2 : K;
+  const int64_t block = format == FMT_NVFP4 ? 16 : 32;
+
+  GemmArgs args{};
+  args.sa = sa; args.sb = sb;
+  args.kc_a = args.kc_b = padded_chunks(K / block);
+  args.rb_a = (M + 127) / 128; args.rb_b = (N + 127) / 128;
+  args.M = M; args.N = N; args.K_bytes = K_bytes;
+  args.d = d; args.ldd = ldd; args.d_dtype = d_dtype;
+  args.bias = bias; args.bias_dtype = bias_dtype; args.accumulate = accumulate;
+  args.amax_a = format == FMT_NVFP4 ? amax_a : nullptr;
+  args.amax_b = format == FMT_NVFP4 ? amax_b : nullptr;
+  args.status = device_status_ptr();
+  if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+  args.mode = MODE_DENSE;
+  args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
+  const int bn = pick_block_n(N);
+  args.tiles_m = (int)((M + G_BLOCK_M - 1) / G_BLOCK_M);
+  args.tiles_n = (int)((N + bn - 1) / bn);
+  args.num_tiles = args.tiles_m * args.tiles_n;
+
+  CUtensorMap ma, mb;
+  // K == 0: no loads are issued, but the maps must still be well-formed
+  const uint64_t kb = (uint64_t)std::max<int64_t>(K_bytes, 16);
+  int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, kb, (uint64_t)M, kb, G_BLOCK_KB, G_BLOCK_M,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, kb, (uint64_t)N, kb, G_BLOCK_KB, (uint32_t)bn,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  if (format == FMT_NVFP4) {
+    return bn == 256 ? launch_gemm<FMT_NVFP4, 256, 4, 1>(ma, mb, args, st) : launch_gemm<FMT_NVFP4, 128, 6, 2>(ma, mb, args, st);
+  }
+  return bn == 256 ? launch_gemm<FMT_MXFP8, 256, 4, 1>(ma, mb, args, st) : launch_gemm<FMT_MXFP8, 128, 6, 2>(ma, mb, args, st);
+}
+
+}  // namespace mt
+
+extern "C" {
+
+int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, const uint8_t* b,
+                  const uint8_t* sb_swz, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,
+                  int64_t ldd, const void* bias, int bias_dtype, int accumulate, mt_stream_t stream) {
+  return mt::gemm_common(mt::FMT_NVFP4, a, sa_swz, amax_a, b, sb_swz, amax_b, M, N, K, d, d_dtype, ldd, bias,
+                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream));
+}
+
+int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz, int64_t M,
+                  int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd, const void* bias, int bias_dtype,
+                  int accumulate, mt_stream_t stream) {
+  return mt::gemm_common(mt::FMT_MXFP8, a, sa_swz, nullptr, b, sb_swz, nullptr, M, N, K, d, d_dtype, ldd, bias,
+                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

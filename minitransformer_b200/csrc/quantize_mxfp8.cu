@@ -1,0 +1,235 @@
+// MXFP8 block quantize for sm_100a: bf16 -> E4M3 elements with one E8M0 (power-of-two)
+// scale byte per 1x32 block, row-wise copy plus an optional transposed copy whose blocks
+// run along the original rows.
+//
+// Same tiling as the NVFP4 kernel: one CTA per 128x128 tile, one TMA load (zero fill
+// outside the tensor), a row pass from shared memory straight to global memory and a
+// column pass staged through shared memory so that global stores stay 16-byte and
+// row-contiguous. There is no per-tensor scale in this format, hence no abs-max pre-pass.
+#include "quantize_common.cuh"
+
+namespace mt {
+
+struct __align__(128) Mxfp8Smem {
+  uint16_t in[QT_ROWS][QT_COLS];      // 32 KiB, TMA destination
+  uint8_t out_t[QT_COLS][QT_ROWS];    // 16 KiB, transposed codes (16-byte chunks XOR-swizzled)
+  uint8_t s_lin[QT_ROWS][4];
+  uint8_t s_swz[512];
+  uint8_t st_lin[QT_COLS][4];
+  uint8_t st_swz[512];
+  uint64_t bar;
+  int abort_flag;
+};
+
+struct Mxfp8Args {
+  int64_t rows, cols;
+  int64_t s_stride, s_t_stride;
+  int64_t kc_row, kc_col;
+  uint8_t *q, *s, *s_swz, *q_t, *s_t, *s_t_swz;
+  int* status;
+};
+
+template <bool kTranspose>
+__global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_constant__ CUtensorMap in_map,
+                                                                   const Mxfp8Args a) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  Mxfp8Smem& sm = *reinterpret_cast<Mxfp8Smem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t k0 = (int64_t)blockIdx.x * QT_COLS;
+  const int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar, QT_ROWS * QT_COLS * 2);
+    tma_load_2d(&sm.in[0][0], &in_map, &sm.bar, (int32_t)k0, (int32_t)m0);
+  }
+  if (!mbar_wait_bounded(&sm.bar, 0, &sm.abort_flag, a.status, DS_QUANT_WAIT)) return;
+
+  // ---- row pass: thread <-> (row, 1x32 block); 4 blocks per tile row ----
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int r = it * 64 + (tid >> 2);
+    const int b = tid & 3;
+    uint4 w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const uint4*>(&sm.in[r][b * 32 + i * 8]);
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m = absmax2(m, absmax2(absmax2(w[i].x, w[i].y), absmax2(w[i].z, w[i].w)));
+    const int e = e8m0_exponent(absmax2_to_float(m));
+    const float enc = exp2_neg(e);
+    uint4 out[2];
+    uint32_t* o = reinterpret_cast<uint32_t*>(out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] = e4m3x4(bf16_lo(w[i].x), bf16_hi(w[i].x), bf16_lo(w[i].y), bf16_hi(w[i].y), enc);
+      o[2 * i + 1] = e4m3x4(bf16_lo(w[i].z), bf16_hi(w[i].z), bf16_lo(w[i].w), bf16_hi(w[i].w), enc);
+    }
+    const int64_t gr = m0 + r, gc = k0 + b * 32;
+    if (gr < a.rows && gc < a.cols) {
+      uint4* dst = reinterpret_cast<uint4*>(a.q + gr * a.cols + gc);
+      dst[0] = out[0];
+      dst[1] = out[1];
+    }
+    const uint8_t sbyte = static_cast<uint8_t>(e + 127);
+    sm.s_lin[r][b] = sbyte;
+    sm.s_swz[sf_chunk_offset(r, b)] = sbyte;
+  }
+
+  // ---- column pass: lane <-> 2 adjacent columns, warp <-> (32-row group, column half) ----
+  if (kTranspose) {
+    const int grp = warp & 3, half = warp >> 2;
+    const int cbase = half * 64 + lane * 2;
+    uint32_t w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) w[j] = *reinterpret_cast<const uint32_t*>(&sm.in[grp * 32 + j][cbase]);
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) m = absmax2(m, w[j]);  // still per-lane-half: lo = column 0, hi = column 1
+    // absmax2(0, w) leaves |w|; the two halves are the two columns' abs-max
+    const float amax0 = bf16_lo(m), amax1 = bf16_hi(m);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int e = e8m0_exponent(c ? amax1 : amax0);
+      const float enc = exp2_neg(e);
+      uint4 out[2];
+      uint32_t* o = reinterpret_cast<uint32_t*>(out);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float f0 = c ? bf16_hi(w[4 * i]) : bf16_lo(w[4 * i]);
+        float f1 = c ? bf16_hi(w[4 * i + 1]) : bf16_lo(w[4 * i + 1]);
+        float f2 = c ? bf16_hi(w[4 * i + 2]) : bf16_lo(w[4 * i + 2]);
+        float f3 = c ? bf16_hi(w[4 * i + 3]) : bf16_lo(w[4 * i + 3]);
+        o[i] = e4m3x4(f0, f1, f2, f3, enc);
+      }
+      const int col = cbase + c;
+      const int swz = (col >> 1) & 7;
+      *reinterpret_cast<uint4*>(&sm.out_t[col][((2 * grp) ^ swz) * 16]) = out[0];
+      *reinterpret_cast<uint4*>(&sm.out_t[col][((2 * grp + 1) ^ swz) * 16]) = out[1];
+      const uint8_t sbyte = static_cast<uint8_t>(e + 127);
+      sm.st_lin[col][grp] = sbyte;
+      sm.st_swz[sf_chunk_offset(col, grp)] = sbyte;
+    }
+  }
+  __syncthreads();
+
+  if (tid < QT_ROWS) {
+    const int64_t gr = m0 + tid;
+    const int64_t kb0 = k0 >> 5;
+    const int nvalid = (int)min((int64_t)4, (a.cols >> 5) - kb0);
+    if (gr < a.rows) {
+      uint8_t* dst = a.s + gr * a.s_stride + kb0;
+      if (nvalid == 4 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0)
+        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(sm.s_lin[tid]);
+      else
+        for (int i = 0; i < nvalid; ++i) dst[i] = sm.s_lin[tid][i];
+    }
+  }
+  if (a.s_swz != nullptr) {
+    uint8_t* base = a.s_swz + ((m0 >> 7) * a.kc_row + (k0 >> 7)) * 512;
+    if (tid < 32) *reinterpret_cast<uint4*>(base + tid * 16) = *reinterpret_cast<const uint4*>(sm.s_swz + tid * 16);
+    if (k0 + QT_COLS >= a.cols) {
+      const int64_t extra = a.kc_row - ((k0 >> 7) + 1);
+      for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
+        *reinterpret_cast<uint4*>(base + 512 + i * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  if (kTranspose) {
+    // Transposed codes: 128 feature rows x 128 bytes (128 tokens), 8 chunks of 16 bytes.
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int row = it * 32 + (tid >> 3);
+      const int ch = tid & 7;
+      const int64_t gk = k0 + row;
+      const int swz = (row >> 1) & 7;
+      const uint4 val = *reinterpret_cast<const uint4*>(&sm.out_t[row][(ch ^ swz) * 16]);
+      const int64_t byte0 = m0 + ch * 16;
+      const int n = (int)max((int64_t)0, min((int64_t)16, a.rows - byte0));
+      if (gk < a.cols && n > 0) {
+        uint8_t* dst = a.q_t + gk * a.rows + byte0;
+        if (n == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          *reinterpret_cast<uint4*>(dst) = val;
+        } else {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(&val);
+          for (int i = 0; i < n; ++i) dst[i] = src[i];
+        }
+      }
+    }
+    if (tid < QT_COLS) {
+      const int64_t gk = k0 + tid;
+      const int64_t mb0 = m0 >> 5;
+      const int nvalid = (int)min((int64_t)4, ((a.rows + 31) >> 5) - mb0);
+      if (gk < a.cols) {
+        uint8_t* dst = a.s_t + gk * a.s_t_stride + mb0;
+        if (nvalid == 4 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0)
+          *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(sm.st_lin[tid]);
+        else
+          for (int i = 0; i < nvalid; ++i) dst[i] = sm.st_lin[tid][i];
+      }
+    }
+    if (a.s_t_swz != nullptr) {
+      uint8_t* base = a.s_t_swz + ((k0 >> 7) * a.kc_col + (m0 >> 7)) * 512;
+      if (tid < 32) *reinterpret_cast<uint4*>(base + tid * 16) = *reinterpret_cast<const uint4*>(sm.st_swz + tid * 16);
+      if (m0 + QT_ROWS >= a.rows) {
+        const int64_t extra = a.kc_col - ((m0 >> 7) + 1);
+        for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
+          *reinterpret_cast<uint4*>(base + 512 + i * 16) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+}
+
+static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
+
+template <bool T>
+static int launch_mxfp8(const CUtensorMap& map, const Mxfp8Args& args, dim3 grid, cudaStream_t st) {
+  static bool attr_set = false;
+  auto kern = quantize_mxfp8_kernel<T>;
+  const int smem = (int)sizeof(Mxfp8Smem) + 128;
+  if (!attr_set) {
+    MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  kern<<<grid, Q_THREADS, smem, st>>>(map, args);
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
+}  // namespace mt
+
+extern "C" int mt_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, uint8_t* q, uint8_t* s, int64_t s_stride,
+                                 uint8_t* s_swz, uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                                 mt_stream_t stream) {
+  using namespace mt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MT_REQUIRE(x && q && s, "mt_quantize_mxfp8: null x/q/s");
+  MT_REQUIRE(rows >= 0 && cols >= 0, "mt_quantize_mxfp8: negative shape");
+  MT_REQUIRE(cols % 32 == 0, "mt_quantize_mxfp8: cols (%lld) must be a multiple of 32", (long long)cols);
+  MT_REQUIRE(aligned16(x) && aligned16(q), "mt_quantize_mxfp8: x and q must be 16-byte aligned");
+  const bool transpose = q_t != nullptr;
+  MT_REQUIRE(!transpose || s_t, "mt_quantize_mxfp8: q_t given without s_t");
+  MT_REQUIRE(s_stride >= cols / 32 && (!transpose || s_t_stride >= (rows + 31) / 32), "mt_quantize_mxfp8: scale stride too small");
+  MT_REQUIRE((!s_swz || aligned16(s_swz)) && (!s_t_swz || aligned16(s_t_swz)), "mt_quantize_mxfp8: swizzled scale buffers must be 16-byte aligned");
+  if (rows == 0 || cols == 0) return MT_OK;
+
+  Mxfp8Args args;
+  args.rows = rows; args.cols = cols;
+  args.s_stride = s_stride; args.s_t_stride = s_t_stride;
+  args.kc_row = padded_chunks(cols / 32);
+  args.kc_col = padded_chunks((rows + 31) / 32);
+  args.q = q; args.s = s; args.s_swz = s_swz; args.q_t = q_t; args.s_t = s_t; args.s_t_swz = s_t_swz;
+  args.status = device_status_ptr();
+  if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+  CUtensorMap map;
+  int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)cols, (uint64_t)rows,
+                              (uint64_t)cols * 2, QT_COLS, QT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != MT_OK) return rc;
+  dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
+  return transpose ? launch_mxfp8<true>(map, args, grid, st) : launch_mxfp8<false>(map, args, grid, st);
+}

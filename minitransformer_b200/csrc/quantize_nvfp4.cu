@@ -1,0 +1,411 @@
+// NVFP4 block quantize for sm_100a: per-tensor abs-max, then cast (+ transpose) of a bf16
+// matrix to packed E2M1 codes with one E4M3 scale per 1x16 (or 16x16) block.
+//
+// One CTA handles one 128x128 tile. The tile arrives in shared memory through a single TMA
+// load (out-of-range rows/columns are zero-filled, which is exactly the zero padding the
+// emulation applies to ragged shapes). A row pass quantizes 1x16 blocks straight from
+// shared memory to global memory; a column pass reads 16-row strips, optionally applies
+// the 16-point Hadamard transform, and stages the transposed codes in shared memory so the
+// global stores are 16-byte and row-contiguous. All scale bytes are staged and written
+// twice: row-major (the tensor the operator API returns) and in the 128x4-chunk layout the
+// tensor-core GEMM copies into tensor memory.
+#include "quantize_common.cuh"
+
+namespace mt {
+
+struct __align__(128) Nvfp4Smem {
+  uint16_t in[QT_ROWS][QT_COLS];         // 32 KiB, TMA destination
+  uint8_t out_t[QT_COLS][QT_ROWS / 2];   // 8 KiB, transposed codes (8-byte slots XOR-swizzled)
+  uint8_t s_lin[QT_ROWS][8];             // row-wise scales, row-major
+  uint8_t s_swz[2][512];                 // row-wise scales, chunk layout
+  uint8_t st_lin[QT_COLS][8];            // column-wise scales, row-major ([feature][token block])
+  uint8_t st_swz[2][512];
+  float blk_amax[8][8];                  // 16x16 block abs-max (2-D mode)
+  uint64_t bar;
+  int abort_flag;
+};
+
+// ------------------------------------------------------------------------------------------
+// abs-max
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) amax_plain_kernel(const uint4* __restrict__ x, int64_t n_vec,
+                                                         float* __restrict__ amax_row) {
+  uint32_t m = 0;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    uint4 v = __ldg(x + i);
+    m = absmax2(m, absmax2(absmax2(v.x, v.y), absmax2(v.z, v.w)));
+  }
+  float f = absmax2_to_float(m);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, o));
+  __shared__ float red[8];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = f;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) f = fmaxf(f, red[i]);
+    atomicMax(reinterpret_cast<unsigned int*>(amax_row), __float_as_uint(f));
+  }
+}
+
+// Row abs-max and abs-max of the Hadamard-transformed transpose in one read of x.
+// Lane <-> 4 adjacent columns, warp <-> 16 consecutive rows, CTA <-> 128x128 tile.
+__global__ void __launch_bounds__(256) amax_rht_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
+                                                       float* __restrict__ amax_row, float* __restrict__ amax_col) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t c0 = (int64_t)blockIdx.x * QT_COLS + lane * 4;
+  const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS + warp * 16;
+  float frow = 0.f, fcol = 0.f;
+  if (c0 < cols && r0 < rows) {  // rows % 16 == 0, cols % 4 == 0: the strip is all-in or all-out
+    uint2 w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = __ldg(reinterpret_cast<const uint2*>(x + (r0 + j) * cols + c0));
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) m = absmax2(m, absmax2(w[j].x, w[j].y));
+    frow = absmax2_to_float(m);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        uint32_t word = (c < 2) ? w[j].x : w[j].y;
+        v[j] = (c & 1) ? bf16_hi(word) : bf16_lo(word);
+      }
+      rht16(v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) fcol = fmaxf(fcol, fabsf(v[j]));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    frow = fmaxf(frow, __shfl_xor_sync(0xffffffffu, frow, o));
+    fcol = fmaxf(fcol, __shfl_xor_sync(0xffffffffu, fcol, o));
+  }
+  __shared__ float red[2][8];
+  if (lane == 0) { red[0][warp] = frow; red[1][warp] = fcol; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) { frow = fmaxf(frow, red[0][i]); fcol = fmaxf(fcol, red[1][i]); }
+    atomicMax(reinterpret_cast<unsigned int*>(amax_row), __float_as_uint(frow));
+    atomicMax(reinterpret_cast<unsigned int*>(amax_col), __float_as_uint(fcol));
+  }
+}
+
+__global__ void copy_scalar_kernel(const float* src, float* dst) { *dst = *src; }
+
+// ------------------------------------------------------------------------------------------
+// cast + transpose
+// ------------------------------------------------------------------------------------------
+struct Nvfp4Args {
+  int64_t rows, cols;
+  int64_t rows_s;       // rows of the row-major scale tensor s (>= rows)
+  int64_t cols_s;       // rows of the row-major scale tensor s_t (>= cols)
+  int64_t s_stride, s_t_stride;
+  int64_t kc_row;       // K-chunks per row block in s_swz   (multiple of 4)
+  int64_t kc_col;       // K-chunks per row block in s_t_swz (multiple of 4)
+  const float* amax_row;
+  const float* amax_col;
+  uint8_t *q, *s, *s_swz, *q_t, *s_t, *s_t_swz;
+  int* status;
+};
+
+template <bool kTranspose, bool k2D, bool kRHT>
+__global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_constant__ CUtensorMap in_map,
+                                                                   const Nvfp4Args a) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  Nvfp4Smem& sm = *reinterpret_cast<Nvfp4Smem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t k0 = (int64_t)blockIdx.x * QT_COLS;
+  const int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
+
+  if (tid == 0) {
+    sm.abort_flag = 0;
+    mbar_init(&sm.bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar, QT_ROWS * QT_COLS * 2);
+    tma_load_2d(&sm.in[0][0], &in_map, &sm.bar, (int32_t)k0, (int32_t)m0);
+  }
+  const Nvfp4Global g_row = nvfp4_global(*a.amax_row);
+  const Nvfp4Global g_col = kTranspose ? nvfp4_global(*a.amax_col) : g_row;
+
+  const bool ok = mbar_wait_bounded(&sm.bar, 0, &sm.abort_flag, a.status, DS_QUANT_WAIT);
+  if (!ok) return;  // no copy of ours can still be in flight only if it never started; status is raised
+
+  // ---- 2-D mode: abs-max of every 16x16 block, shared by both passes ----
+  if (k2D) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint2 w = *reinterpret_cast<const uint2*>(&sm.in[warp * 16 + j][lane * 4]);
+      m = absmax2(m, absmax2(w.x, w.y));
+    }
+    float f = absmax2_to_float(m);
+    f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, 1));
+    f = fmaxf(f, __shfl_xor_sync(0xffffffffu, f, 2));
+    // All four lanes of a block hold the same value and all store it. (Guarding the store
+    // with lane % 4 == 0 made nvcc 12.9 reuse the guarded address, byte offset = lane, for
+    // the unguarded loads below: a misaligned fp32 load.)
+    sm.blk_amax[warp][lane >> 2] = f;
+    __syncthreads();
+  }
+
+  // ---- row pass: thread <-> (row, 1x16 block) ----
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int r = it * 32 + (tid >> 3);
+    const int b = tid & 7;
+    const uint4 w0 = *reinterpret_cast<const uint4*>(&sm.in[r][b * 16]);
+    const uint4 w1 = *reinterpret_cast<const uint4*>(&sm.in[r][b * 16 + 8]);
+    float vmax;
+    if (k2D) {
+      vmax = sm.blk_amax[r >> 4][b];
+    } else {
+      uint32_t m = absmax2(absmax2(absmax2(w0.x, w0.y), absmax2(w0.z, w0.w)),
+                           absmax2(absmax2(w1.x, w1.y), absmax2(w1.z, w1.w)));
+      vmax = absmax2_to_float(m);
+    }
+    uint8_t sbyte;
+    float enc;
+    nvfp4_block_scale(vmax, g_row, sbyte, enc);
+    float v[16];
+    const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(ws[i]); v[2 * i + 1] = bf16_hi(ws[i]); }
+    uint2 codes;
+    codes.x = e2m1x8(v, enc);
+    codes.y = e2m1x8(v + 8, enc);
+    const int64_t gr = m0 + r, gc = k0 + b * 16;
+    if (gr < a.rows && gc < a.cols)
+      *reinterpret_cast<uint2*>(a.q + gr * (a.cols >> 1) + (gc >> 1)) = codes;
+    sm.s_lin[r][b] = sbyte;
+    sm.s_swz[b >> 2][sf_chunk_offset(r, b)] = sbyte;
+  }
+
+  // ---- column pass: lane <-> 4 adjacent columns, warp <-> 16 rows ----
+  if (kTranspose) {
+    uint2 w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = *reinterpret_cast<const uint2*>(&sm.in[warp * 16 + j][lane * 4]);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        uint32_t word = (c < 2) ? w[j].x : w[j].y;
+        v[j] = (c & 1) ? bf16_hi(word) : bf16_lo(word);
+      }
+      if (kRHT) rht16(v);
+      float vmax;
+      if (k2D) {
+        vmax = sm.blk_amax[warp][lane >> 2];
+      } else {
+        vmax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
+      }
+      uint8_t sbyte;
+      float enc;
+      nvfp4_block_scale(vmax, g_col, sbyte, enc);
+      uint2 codes;
+      codes.x = e2m1x8(v, enc);
+      codes.y = e2m1x8(v + 8, enc);
+      const int col = lane * 4 + c;
+      const int slot = warp ^ (lane & 7);
+      *reinterpret_cast<uint2*>(&sm.out_t[col][slot * 8]) = codes;
+      sm.st_lin[col][warp] = sbyte;
+      sm.st_swz[warp >> 2][sf_chunk_offset(col, warp)] = sbyte;
+    }
+  }
+  __syncthreads();
+
+  // ---- cooperative, row-contiguous global stores of the staged outputs ----
+  // Row-wise scales, row-major: 128 rows x 8 bytes.
+  if (tid < QT_ROWS) {
+    const int64_t gr = m0 + tid;
+    const int64_t kb0 = k0 >> 4;
+    const int nvalid = (int)min((int64_t)8, (a.cols >> 4) - kb0);
+    if (gr < a.rows_s) store_bytes(a.s + gr * a.s_stride + kb0, sm.s_lin[tid], nvalid);
+  }
+  // Row-wise scales, chunk layout: two 512-byte chunks (+ zero chunks up to the padded count
+  // when this is the last tile along K).
+  if (a.s_swz != nullptr) {
+    uint8_t* base = a.s_swz + ((m0 >> 7) * a.kc_row + (k0 >> 6)) * 512;
+    if (tid < 64) *reinterpret_cast<uint4*>(base + tid * 16) = *reinterpret_cast<const uint4*>(&sm.s_swz[0][0] + tid * 16);
+    if (k0 + QT_COLS >= a.cols) {
+      const int64_t extra = a.kc_row - ((k0 >> 6) + 2);
+      for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
+        *reinterpret_cast<uint4*>(base + 1024 + i * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  if (kTranspose) {
+    // Transposed codes: 128 feature rows x 64 bytes (128 tokens).
+    const int64_t row_bytes = a.rows >> 1;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int row = it * 64 + (tid >> 2);
+      const int ch = tid & 3;
+      const int64_t gk = k0 + row;
+      const int swz = (row >> 2) & 7;
+      // the two 8-byte slots 2ch, 2ch+1 sit in one 16-byte chunk, possibly swapped
+      const int p0 = (2 * ch) ^ swz;
+      uint4 val = *reinterpret_cast<const uint4*>(&sm.out_t[row][(p0 & ~1) * 8]);
+      if (p0 & 1) val = make_uint4(val.z, val.w, val.x, val.y);
+      const int64_t byte0 = (m0 >> 1) + ch * 16;
+      const int n = (int)max((int64_t)0, min((int64_t)16, row_bytes - byte0));
+      if (gk < a.cols && n > 0) {
+        uint8_t* dst = a.q_t + gk * row_bytes + byte0;
+        if (n == 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          *reinterpret_cast<uint4*>(dst) = val;
+        } else {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(&val);
+          for (int i = 0; i < n; ++i) dst[i] = src[i];
+        }
+      }
+    }
+    if (tid < QT_COLS) {
+      const int64_t gk = k0 + tid;
+      const int64_t mb0 = m0 >> 4;
+      const int nvalid = (int)min((int64_t)8, ((a.rows + 15) >> 4) - mb0);
+      if (gk < a.cols_s) store_bytes(a.s_t + gk * a.s_t_stride + mb0, sm.st_lin[tid], nvalid);
+    }
+    if (a.s_t_swz != nullptr) {
+      uint8_t* base = a.s_t_swz + ((k0 >> 7) * a.kc_col + (m0 >> 6)) * 512;
+      if (tid < 64) *reinterpret_cast<uint4*>(base + tid * 16) = *reinterpret_cast<const uint4*>(&sm.st_swz[0][0] + tid * 16);
+      if (m0 + QT_ROWS >= a.rows) {
+        const int64_t extra = a.kc_col - ((m0 >> 6) + 2);
+        for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
+          *reinterpret_cast<uint4*>(base + 1024 + i * 16) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+}
+
+// Row-major scale bytes -> chunk layout (for callers that only hold the row-major tensor).
+__global__ void swizzle_scales_kernel(const uint8_t* __restrict__ s, int64_t rows, int64_t k_blocks, int64_t s_stride,
+                                      uint8_t* __restrict__ out, int64_t kc_pad) {
+  // one CTA per (row block, chunk): 128 threads <-> 128 rows, 4 bytes each
+  const int64_t rb = blockIdx.y, kc = blockIdx.x;
+  const int r = threadIdx.x;
+  const int64_t gr = rb * 128 + r;
+  uint32_t word = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t kb = kc * 4 + i;
+    uint32_t b = (gr < rows && kb < k_blocks) ? s[gr * s_stride + kb] : 0u;
+    word |= b << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(out + (rb * kc_pad + kc) * 512 + (r & 31) * 16 + (r >> 5) * 4) = word;
+}
+
+static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
+
+template <bool T, bool D2, bool R>
+static int launch_nvfp4(const CUtensorMap& map, const Nvfp4Args& args, dim3 grid, cudaStream_t st) {
+  static bool attr_set = false;
+  auto kern = quantize_nvfp4_kernel<T, D2, R>;
+  const int smem = (int)sizeof(Nvfp4Smem) + 128;
+  if (!attr_set) {
+    MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  kern<<<grid, Q_THREADS, smem, st>>>(map, args);
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
+}  // namespace mt
+
+extern "C" {
+
+int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* amax_row, float* amax_col,
+                 mt_stream_t stream) {
+  using namespace mt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MT_REQUIRE(x && amax_row, "mt_amax_bf16: null pointer");
+  MT_REQUIRE(rows >= 0 && cols >= 0 && cols % 8 == 0, "mt_amax_bf16: cols (%lld) must be a multiple of 8", (long long)cols);
+  MT_REQUIRE(aligned16(x), "mt_amax_bf16: x must be 16-byte aligned");
+  const bool rht = (flags & MT_Q_RHT) && amax_col != nullptr;
+  MT_REQUIRE(!rht || rows % 16 == 0, "mt_amax_bf16: the Hadamard transform needs rows %% 16 == 0 (rows=%lld)", (long long)rows);
+  MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
+  if (rht) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+  if (rows == 0 || cols == 0) {
+    if (amax_col && !rht) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+    return MT_OK;
+  }
+  if (rht) {
+    dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
+    amax_rht_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x), rows, cols, amax_row, amax_col);
+  } else {
+    const int64_t n_vec = rows * cols / 8;
+    int blocks = (int)std::min<int64_t>((n_vec + 255) / 256, 148 * 8);
+    amax_plain_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), n_vec, amax_row);
+    if (amax_col) copy_scalar_kernel<<<1, 1, 0, st>>>(amax_row, amax_col);
+  }
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
+int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
+                      const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz, uint8_t* q_t,
+                      uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, mt_stream_t stream) {
+  using namespace mt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MT_REQUIRE(x && q && s && amax_row, "mt_quantize_nvfp4: null x/q/s/amax_row");
+  MT_REQUIRE(rows >= 0 && cols >= 0, "mt_quantize_nvfp4: negative shape");
+  MT_REQUIRE(cols % 16 == 0, "mt_quantize_nvfp4: cols (%lld) must be a multiple of 16", (long long)cols);
+  MT_REQUIRE(rows % 2 == 0, "mt_quantize_nvfp4: rows (%lld) must be even", (long long)rows);
+  MT_REQUIRE(aligned16(x) && aligned16(q), "mt_quantize_nvfp4: x and q must be 16-byte aligned");
+  const bool transpose = q_t != nullptr;
+  const bool d2 = (flags & MT_Q_2D) != 0, rht = (flags & MT_Q_RHT) != 0;
+  const bool pad16 = d2 || (flags & MT_Q_ROWPAD16);
+  MT_REQUIRE(!transpose || (s_t && amax_col), "mt_quantize_nvfp4: q_t given without s_t / amax_col");
+  MT_REQUIRE(!(d2 && rht), "mt_quantize_nvfp4: 2-D scaling together with the Hadamard transform is not supported");
+  MT_REQUIRE(!rht || rows % 16 == 0, "mt_quantize_nvfp4: the Hadamard transform needs rows %% 16 == 0");
+  MT_REQUIRE(s_stride >= cols / 16 && (!transpose || s_t_stride >= (rows + 15) / 16), "mt_quantize_nvfp4: scale stride too small");
+  MT_REQUIRE((!s_swz || aligned16(s_swz)) && (!s_t_swz || aligned16(s_t_swz)), "mt_quantize_nvfp4: swizzled scale buffers must be 16-byte aligned");
+  if (rows == 0 || cols == 0) return MT_OK;
+
+  Nvfp4Args args;
+  args.rows = rows; args.cols = cols;
+  args.rows_s = pad16 ? (rows + 15) / 16 * 16 : rows;
+  args.cols_s = pad16 ? (cols + 15) / 16 * 16 : cols;
+  args.s_stride = s_stride; args.s_t_stride = s_t_stride;
+  args.kc_row = padded_chunks(cols / 16);
+  args.kc_col = padded_chunks((rows + 15) / 16);
+  args.amax_row = amax_row; args.amax_col = transpose ? amax_col : amax_row;
+  args.q = q; args.s = s; args.s_swz = s_swz; args.q_t = q_t; args.s_t = s_t; args.s_t_swz = s_t_swz;
+  args.status = device_status_ptr();
+  if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+
+  CUtensorMap map;
+  int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)cols, (uint64_t)rows,
+                              (uint64_t)cols * 2, QT_COLS, QT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != MT_OK) return rc;
+  dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
+  if (!transpose) {
+    return d2 ? launch_nvfp4<false, true, false>(map, args, grid, st) : launch_nvfp4<false, false, false>(map, args, grid, st);
+  }
+  if (d2) return launch_nvfp4<true, true, false>(map, args, grid, st);
+  if (rht) return launch_nvfp4<true, false, true>(map, args, grid, st);
+  return launch_nvfp4<true, false, false>(map, args, grid, st);
+}
+
+int mt_swizzle_scales(const uint8_t* s, int64_t rows, int64_t k_blocks, int64_t s_stride, uint8_t* s_swz,
+                      mt_stream_t stream) {
+  using namespace mt;
+  MT_REQUIRE(s && s_swz, "mt_swizzle_scales: null pointer");
+  MT_REQUIRE(rows >= 0 && k_blocks >= 0 && s_stride >= k_blocks, "mt_swizzle_scales: bad shape");
+  MT_REQUIRE(aligned16(s_swz), "mt_swizzle_scales: output must be 16-byte aligned");
+  if (rows == 0 || k_blocks == 0) return MT_OK;
+  const int64_t kc = padded_chunks(k_blocks);
+  dim3 grid((unsigned)kc, (unsigned)((rows + 127) / 128));
+  swizzle_scales_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(s, rows, k_blocks, s_stride, s_swz, kc);
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,176 @@
+"""Thin torch-tensor front end over the C-ABI kernels: allocates outputs with torch, passes
+raw pointers and the current CUDA stream, raises on any error. No arithmetic happens here."""
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import MT_BF16, MT_F32, MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16  # noqa: F401
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str):
+    if not t.is_cuda:
+        raise _lib.MtError(f"{name} must be a CUDA tensor: these kernels have no CPU path")
+
+
+def swizzled_scale_bytes(rows: int, k_blocks: int) -> int:
+    return int(_lib.load().mt_swizzled_scale_bytes(rows, k_blocks))
+
+
+@dataclass
+class Quantized:
+    """Outputs of one quantize call. `scale*` are row-major byte tensors (E4M3 or E8M0 bit
+    patterns), `scale*_swz` the same values in the layout the GEMM reads."""
+    data: torch.Tensor
+    scale: torch.Tensor
+    scale_swz: torch.Tensor
+    data_t: Optional[torch.Tensor] = None
+    scale_t: Optional[torch.Tensor] = None
+    scale_t_swz: Optional[torch.Tensor] = None
+    amax_row: Optional[torch.Tensor] = None
+    amax_col: Optional[torch.Tensor] = None
+
+
+def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True):
+    """Per-tensor abs-max (and abs-max of the Hadamard-transformed transpose) as device scalars."""
+    _require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    amax = torch.empty(2, dtype=torch.float32, device=x.device)
+    flags = MT_Q_RHT if with_rht else 0
+    _lib.call("mt_amax_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
+              amax[1:2].data_ptr() if need_col else None, _stream())
+    return amax[0:1], (amax[1:2] if need_col else amax[0:1])
+
+
+def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with_rht: bool = False,
+                   return_transpose: bool = True, amax_row: Optional[torch.Tensor] = None,
+                   amax_col: Optional[torch.Tensor] = None) -> Quantized:
+    _require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    M, K = x.shape
+    dev = x.device
+    if amax_row is None:
+        amax_row, amax_col = amax_bf16(x, with_rht=with_rht and return_transpose, need_col=return_transpose)
+    flags = (MT_Q_2D if with_2d else 0) | (MT_Q_RHT if with_rht else 0)
+    pad16 = with_2d or tile[0] == 16
+    if pad16:
+        flags |= MT_Q_ROWPAD16
+    rows_s = (M + 15) // 16 * 16 if pad16 else M
+    cols_s = (K + 15) // 16 * 16 if pad16 else K
+    u8 = torch.uint8
+    q = torch.empty((M, K // 2), dtype=u8, device=dev)
+    s = torch.empty((rows_s, K // 16), dtype=u8, device=dev)
+    s_swz = torch.empty(swizzled_scale_bytes(M, K // 16), dtype=u8, device=dev)
+    q_t = s_t = s_t_swz = None
+    mb = (M + 15) // 16
+    if return_transpose:
+        q_t = torch.empty((K, M // 2), dtype=u8, device=dev)
+        s_t = torch.empty((cols_s, mb), dtype=u8, device=dev)
+        s_t_swz = torch.empty(swizzled_scale_bytes(K, mb), dtype=u8, device=dev)
+    _lib.call("mt_quantize_nvfp4", x.data_ptr(), M, K, flags, amax_row.data_ptr(), _ptr(amax_col),
+              q.data_ptr(), s.data_ptr(), K // 16, s_swz.data_ptr(),
+              _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
+    return Quantized(q, s, s_swz, q_t, s_t, s_t_swz, amax_row, amax_col if return_transpose else amax_row)
+
+
+def quantize_mxfp8(x: torch.Tensor, *, return_transpose: bool = True) -> Quantized:
+    _require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    M, K = x.shape
+    dev = x.device
+    u8 = torch.uint8
+    q = torch.empty((M, K), dtype=u8, device=dev)
+    s = torch.empty((M, K // 32), dtype=u8, device=dev)
+    s_swz = torch.empty(swizzled_scale_bytes(M, K // 32), dtype=u8, device=dev)
+    q_t = s_t = s_t_swz = None
+    mb = (M + 31) // 32
+    if return_transpose:
+        q_t = torch.empty((K, M), dtype=u8, device=dev)
+        s_t = torch.empty((K, mb), dtype=u8, device=dev)
+        s_t_swz = torch.empty(swizzled_scale_bytes(K, mb), dtype=u8, device=dev)
+    _lib.call("mt_quantize_mxfp8", x.data_ptr(), M, K, q.data_ptr(), s.data_ptr(), K // 32, s_swz.data_ptr(),
+              _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
+    return Quantized(q, s, s_swz, q_t, s_t, s_t_swz)
+
+
+def swizzle_scales(s: torch.Tensor, rows: Optional[int] = None) -> torch.Tensor:
+    """Row-major scale bytes [R, KB] -> GEMM layout. `rows` limits the rows taken from s."""
+    _require_cuda(s, "s")
+    s = s.view(torch.uint8) if s.dtype != torch.uint8 else s
+    assert s.dim() == 2 and s.stride(1) == 1
+    R = s.shape[0] if rows is None else rows
+    out = torch.empty(swizzled_scale_bytes(R, s.shape[1]), dtype=torch.uint8, device=s.device)
+    _lib.call("mt_swizzle_scales", s.data_ptr(), R, s.shape[1], s.stride(0), out.data_ptr(), _stream())
+    return out
+
+
+def _out_dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return MT_BF16
+    if dt == torch.float32:
+        return MT_F32
+    raise _lib.MtError(f"GEMM output dtype {dt} is not supported (bf16 or fp32)")
+
+
+def _gemm_out(M, N, out_dtype, out, accumulate, device):
+    if out is None:
+        if accumulate:
+            raise _lib.MtError("accumulate=True needs an output tensor")
+        out = torch.empty((M, N), dtype=out_dtype, device=device)
+    else:
+        assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1
+    return out
+
+
+def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat16, out=None,
+               accumulate=False, bias=None, check_kernel=False, sa_lin=None, sb_lin=None):
+    """D[M,N] = alpha * qa[M,K/2] . qb[N,K/2]^T. With check_kernel=True the CUDA-core
+    checker runs instead (it takes the row-major scales sa_lin / sb_lin)."""
+    _require_cuda(qa, "qa")
+    M, N, K = qa.shape[0], qb.shape[0], qa.shape[1] * 2
+    assert qb.shape[1] * 2 == K
+    out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
+    if check_kernel:
+        _lib.call("mt_gemm_nvfp4_check", qa.data_ptr(), sa_lin.data_ptr(), sa_lin.stride(0), amax_a.data_ptr(),
+                  qb.data_ptr(), sb_lin.data_ptr(), sb_lin.stride(0), amax_b.data_ptr(), M, N, K,
+                  out.data_ptr(), _out_dtype_code(out_dtype), out.stride(0), int(accumulate), _stream())
+        return out
+    _lib.call("mt_gemm_nvfp4", qa.data_ptr(), sa_swz.data_ptr(), amax_a.data_ptr(), qb.data_ptr(),
+              sb_swz.data_ptr(), amax_b.data_ptr(), M, N, K, out.data_ptr(), _out_dtype_code(out_dtype),
+              out.stride(0), _ptr(bias), 0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate),
+              _stream())
+    return out
+
+
+def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, accumulate=False, bias=None,
+               check_kernel=False, sa_lin=None, sb_lin=None):
+    _require_cuda(qa, "qa")
+    M, N, K = qa.shape[0], qb.shape[0], qa.shape[1]
+    assert qb.shape[1] == K
+    out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
+    if check_kernel:
+        _lib.call("mt_gemm_mxfp8_check", qa.data_ptr(), sa_lin.data_ptr(), sa_lin.stride(0), qb.data_ptr(),
+                  sb_lin.data_ptr(), sb_lin.stride(0), M, N, K, out.data_ptr(), _out_dtype_code(out_dtype),
+                  out.stride(0), int(accumulate), _stream())
+        return out
+    _lib.call("mt_gemm_mxfp8", qa.data_ptr(), sa_swz.data_ptr(), qb.data_ptr(), sb_swz.data_ptr(), M, N, K,
+              out.data_ptr(), _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
+              0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+    return out
+
+
+def read_device_status() -> int:
+    """Status word raised by bounded device-side waits (0 = clean); clears it."""
+    import ctypes
+    v = ctypes.c_int(0)
+    _lib.check(_lib.load().mt_read_device_status(ctypes.byref(v), _stream()), "mt_read_device_status")
+    return v.value
