@@ -1,0 +1,379 @@
+"""Benchmark of the quantized-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one forward + backward of the NVFP4 Linear of the reference recipe (Hadamard
+transform on the transposed activation / gradient copies) on synthetic data:
+quantize x, quantize w (every step: the "first microbatch" case), fprop GEMM, quantize dy,
+dgrad GEMM, wgrad GEMM (fp32). At N = 1 the shape is the Llama-style MLP up-projection of
+the benchmark configuration (tokens 8192, in 4096, out 14336); at N > 1 it is the
+tensor-parallel MLP (tokens 8192, hidden 8192, ffn 28672; column-parallel fc1 then
+row-parallel fc2, sequence parallel, quantized all-gather) strong-scaled over N ranks.
+
+`value` = GEMM flops of the step (2*M*N*K per GEMM, all ranks) / device time of the step
+with inputs resident in HBM. `e2e` = the same metric through the public `Linear` module with
+pinned host inputs copied to the device and a checksum read back inside every timed step.
+`--impl reference` times the CPU restatement of the reference's PyTorch emulation on a
+bounded sample of the same workload on the host cores.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "nvfp4_linear_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+
+C2 = dict(tokens=8192, in_features=4096, out_features=14336)
+C4 = dict(tokens=8192, hidden=8192, ffn=28672)
+CPU_SAMPLE = dict(tokens=512, in_features=4096, out_features=3584)
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=float(p["hbm_gbs"]), bf16_burst=float(p["bf16_tflops"]),
+                    bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: numpy restatement of the reference emulation on a bounded sample
+# ---------------------------------------------------------------------------------------------
+def _cpu_step_inputs(seed=0):
+    import numpy as np
+    from oracle import formats as F
+    rng = np.random.default_rng(seed)
+    s = CPU_SAMPLE
+    x = F.bf16_round(rng.standard_normal((s["tokens"], s["in_features"])).astype(np.float32))
+    w = F.bf16_round((rng.standard_normal((s["out_features"], s["in_features"])) * 0.02).astype(np.float32))
+    dy = F.bf16_round((rng.standard_normal((s["tokens"], s["out_features"])) * 1e-3).astype(np.float32))
+    return x, w, dy
+
+
+def _cpu_sample_flops():
+    s = CPU_SAMPLE
+    return 3 * 2.0 * s["tokens"] * s["in_features"] * s["out_features"]
+
+
+def cpu_run(steps, warmup):
+    """Times `steps` passes of the oracle's NVFP4 linear fwd+bwd on the sample; returns TFLOP/s."""
+    from oracle import linear
+    x, w, dy = _cpu_step_inputs()
+    for _ in range(warmup):
+        linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
+    dt = (time.perf_counter() - t0) / max(1, steps)
+    return _cpu_sample_flops() / dt / 1e12, dt
+
+
+def _cpu_sample_text():
+    s = CPU_SAMPLE
+    return (f"NVFP4 linear fwd+bwd on tokens={s['tokens']} in={s['in_features']} out={s['out_features']} "
+            f"(1/64 of the GEMM flops of the 8192x4096x14336 workload), numpy restatement of the reference emulation, "
+            f"single-sgemm GEMM variant")
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    tf, dt = cpu_run(args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+        "config": _workload_config(args.gpus),
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": _cpu_sample_text()},
+        "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def _workload_config(n):
+    if n == 1:
+        return {"workload": "NVFP4 Linear fwd+bwd (fprop, dgrad, wgrad), Llama-style MLP up-projection",
+                **C2, "recipe": "1x16 E2M1 + E4M3 block scales + fp32 per-tensor scale, RHT on x^T/dy^T, "
+                                "weights re-quantized every step",
+                "l2": "inputs (x 64 MiB, w 112 MiB, dy 224 MiB) exceed the 126 MB L2"}
+    return {"workload": "tensor-parallel NVFP4 MLP fwd+bwd: column-parallel fc1 -> row-parallel fc2, "
+                        "sequence parallel, quantized all-gather, bf16 reduce-scatter",
+            **C4, "parallelism": f"tp{n}", "l2": "per-rank operands exceed the 126 MB L2"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                 nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.05)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def _physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from minitransformer_b200 import kernels
+    from minitransformer_b200.module import config as mt_config
+    from minitransformer_b200.module.linear import Linear
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    tp_group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        tp_group = dist.group.WORLD
+    n = world
+    assert n == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+
+    params = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.FP4_SUB_CHANNEL)
+    op = params.quantize_op
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+
+    def randn_bf16(shape, std, pin=False):
+        t = (torch.randn(*shape, generator=g, dtype=torch.float32) * std).to(torch.bfloat16)
+        return t.pin_memory() if pin else t
+
+    gemm_ms, quant_ms = [], []
+
+    if n == 1:
+        T, K_in, N_out = C2["tokens"], C2["in_features"], C2["out_features"]
+        x_h, dy_h = randn_bf16((T, K_in), 1.0, pin=True), randn_bf16((T, N_out), 1e-3, pin=True)
+        w = randn_bf16((N_out, K_in), 0.02).to(dev)
+        x, dy = x_h.to(dev), dy_h.to(dev)
+        flops_step = 3 * 2.0 * T * K_in * N_out
+        gemm_flops_each = 2.0 * T * K_in * N_out
+        dw = torch.empty((N_out, K_in), dtype=torch.float32, device=dev)
+
+        def timed(fn, bucket):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            bucket.append((e0, e1))
+            return r
+
+        def step(record):
+            tq = (lambda fn: timed(fn, quant_ms)) if record else (lambda fn: fn())
+            tg = (lambda fn: timed(fn, gemm_ms)) if record else (lambda fn: fn())
+            qx = op.quantize(x, params.x_params, return_transpose=True)
+            qw = op.quantize(w, params.w_params, return_transpose=True)
+            y = tg(lambda: op.qgemm(qx.data, qw.data, params.mm_fprop, torch.bfloat16, qx.scale, qw.scale,
+                                    global_amax_qx=qx.global_amax_row, global_amax_qw=qw.global_amax_row))
+            qg = tq(lambda: op.quantize(dy, params.g_params, return_transpose=True))
+            dx = tg(lambda: op.qgemm(qg.data, qw.data_t, params.mm_dgrad, torch.bfloat16, qg.scale, qw.scale_t,
+                                     global_amax_qx=qg.global_amax_row, global_amax_qw=qw.global_amax_col))
+            tg(lambda: op.qgemm(qg.data_t, qx.data_t, params.mm_wgrad, torch.float32, qg.scale_t, qx.scale_t,
+                                out=dw, global_amax_qx=qg.global_amax_col, global_amax_qw=qx.global_amax_col))
+            return y, dx
+
+        lin = Linear(K_in, N_out, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
+                     fuse_wgrad_accumulation=True)
+        with torch.no_grad():
+            lin.weight.copy_(w)
+        lin.weight.main_grad = torch.zeros((N_out, K_in), dtype=torch.float32, device=dev)
+
+        def e2e_step():
+            xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+            dyd = dy_h.to(dev, non_blocking=True)
+            y = lin(xd, is_first_microbatch=True)
+            y.backward(dyd)
+            chk = torch.stack([y.float().sum(), xd.grad.float().sum(), lin.weight.main_grad.sum()])
+            return chk.cpu()
+
+        h2d = x_h.numel() * 2 + dy_h.numel() * 2
+        d2h = 12
+        launches_per_step = None
+    else:
+        T, H, Fd = C4["tokens"], C4["hidden"], C4["ffn"]
+        assert T % n == 0 and Fd % n == 0
+        x_h, dy_h = randn_bf16((T // n, H), 1.0, pin=True), randn_bf16((T // n, H), 1e-3, pin=True)
+        fc1 = Linear(H, Fd, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
+                     parallel_mode="column", sequence_parallel=True, tp_group=tp_group, fuse_wgrad_accumulation=True,
+                     init_method=lambda t: torch.nn.init.normal_(t, std=0.02))
+        fc2 = Linear(Fd, H, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
+                     parallel_mode="row", sequence_parallel=True, tp_group=tp_group, fuse_wgrad_accumulation=True,
+                     init_method=lambda t: torch.nn.init.normal_(t, std=0.02))
+        for m in (fc1, fc2):
+            m.weight.main_grad = torch.zeros_like(m.weight, dtype=torch.float32)
+        x, dy = x_h.to(dev), dy_h.to(dev)
+        flops_step = 6 * 2.0 * T * H * Fd  # whole job: fc1 + fc2, fprop + dgrad + wgrad
+        gemm_flops_each = 2.0 * T * H * Fd / n
+
+        def mlp(xd, dyd):
+            # no activation between fc1 and fc2: the benchmark configuration names none
+            y = fc2(fc1(xd, is_first_microbatch=True), is_first_microbatch=True)
+            y.backward(dyd)
+            return y
+
+        def step(record):
+            xd = x.detach().requires_grad_(True)
+            y = mlp(xd, dy)
+            return y, xd.grad
+
+        def e2e_step():
+            xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+            dyd = dy_h.to(dev, non_blocking=True)
+            y = mlp(xd, dyd)
+            chk = torch.stack([y.float().sum(), xd.grad.float().sum()])
+            return chk.cpu()
+
+        h2d = x_h.numel() * 2 + dy_h.numel() * 2
+        d2h = 8
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run_timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        kernels.LAUNCH_COUNT = 0
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = kernels.LAUNCH_COUNT
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, launches
+
+    sampler = ClockSampler(_physical_gpu_index(local_rank)) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_step, launches = run_timed(lambda: step(True), args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    # only the events recorded during the timed region count
+    torch.cuda.synchronize()
+    g_ms = [a.elapsed_time(b) for a, b in gemm_ms[-3 * args.steps:]] if n == 1 else []
+    q_ms = [a.elapsed_time(b) for a, b in quant_ms[-args.steps:]] if n == 1 else []
+    e2e_ms, _ = run_timed(e2e_step, max(2, min(args.steps, 10)), 2)
+
+    status = kernels.read_device_status()
+    if status != 0:
+        raise SystemExit(f"device status word is {status}: a bounded device-side wait expired")
+
+    if rank == 0:
+        peaks = _peaks()
+        value = flops_step / (ms_step * 1e-3) / 1e12
+        e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak" if n == 1 else "strong",
+            "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic", "config": _workload_config(n),
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+        }
+        if n == 1:
+            g_avg = sum(g_ms) / len(g_ms)
+            achieved = gemm_flops_each / (g_avg * 1e-3) / 1e12
+            peak = 4.0 * peaks["bf16_sustained"]
+            line["roofline"] = {
+                "bound": "tensor", "kernel": "gemm_blockscaled_kernel<NVFP4> (fprop/dgrad/wgrad average)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": f"4 x {peaks['source']} sustained bf16 cuBLAS rate ({peaks['bf16_sustained']} TFLOP/s); "
+                               "no FP4 figure is measured on this pool",
+                "frac_of_nominal_9000": achieved / 9000.0, "avg_launch_ms": g_avg,
+            }
+            q_avg = sum(q_ms) / len(q_ms)
+            q_bytes = C2["tokens"] * C2["out_features"] * 3.125
+            q_gbs = q_bytes / (q_avg * 1e-3) / 1e9
+            line["roofline_quantize"] = {
+                "bound": "hbm", "kernel": "amax_rht_kernel + quantize_nvfp4_kernel on dy (row + transposed, RHT)",
+                "achieved": q_gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": q_gbs / peaks["hbm"],
+                "algorithmic_bytes": q_bytes, "avg_sequence_ms": q_avg,
+                "peak_source": f"{peaks['source']} copy bandwidth"}
+            tf, dt = cpu_run(4, 1)
+            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": _cpu_sample_text(), "s_per_sample_step": dt}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

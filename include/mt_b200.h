@@ -63,7 +63,7 @@ int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags,
  * nibble), one E4M3 scale per 1x16 block (or per 16x16 block with MT_Q_2D), using the
  * per-tensor abs-max values already on the device (mt_amax_bf16, optionally max-reduced
  * across ranks by the caller).
- *   x        bf16 [rows, cols], cols % 16 == 0, rows % 2 == 0
+ *   x        bf16 [rows, cols], cols % 16 == 0 (rows % 2 == 0 when q_t is requested)
  *   q        u8 [rows, cols/2]
  *   s        u8 (E4M3) [rows_s, cols/16], row stride s_stride bytes; rows_s = rows, or rows
  *            rounded up to 16 with MT_Q_ROWPAD16 / MT_Q_2D (padded rows are written as 0)

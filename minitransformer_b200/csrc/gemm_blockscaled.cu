@@ -61,6 +61,7 @@ struct GemmArgs {
   int64_t b_group_rows;          // rows of B per group (MODE_GROUPED_ROWS): N
   int64_t d_group_stride;        // elements between consecutive group outputs (MODE_GROUPED_K)
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
+  int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
 };
 
 template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
@@ -119,6 +120,64 @@ __device__ __forceinline__ void issue_mma(uint32_t tmem_d, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
+  }
+}
+
+// One thread's 32 consecutive fp32 accumulators of one output row -> alpha / bias /
+// accumulate -> global memory (bf16 or fp32), vectorised when aligned and in range.
+__device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_t (&r)[32], float alpha, bool has_k,
+                                                int64_t off, int64_t col0) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = has_k ? __fmul_rn(alpha, __uint_as_float(r[i])) : 0.0f;
+  const int nvalid = (int)min((int64_t)32, a.N - col0);
+  if (a.bias != nullptr) {
+    for (int i = 0; i < nvalid; ++i)
+      v[i] += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col0 + i]
+                                       : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col0 + i]);
+  }
+  if (a.d_dtype == MT_F32) {
+    float* dst = static_cast<float*>(a.d) + off;
+    if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        if (a.accumulate) { float4 p = d4[i]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
+        d4[i] = o;
+      }
+    } else {
+      for (int i = 0; i < nvalid; ++i) dst[i] = a.accumulate ? dst[i] + v[i] : v[i];
+    }
+  } else {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + off;
+    if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (a.accumulate) {
+          uint4 p = d4[i];
+          const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[8 * i + 2 * j] += __uint_as_float(pw[j] << 16);
+            v[8 * i + 2 * j + 1] += __uint_as_float(pw[j] & 0xFFFF0000u);
+          }
+        }
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+          ow[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        d4[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
+    } else {
+      for (int i = 0; i < nvalid; ++i) {
+        float o = a.accumulate ? __bfloat162float(dst[i]) + v[i] : v[i];
+        dst[i] = __float2bfloat16_rn(o);
+      }
+    }
   }
 }
 
@@ -323,61 +382,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
         tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + as * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
         tc_wait_ld();
         const int64_t col0 = t.d_col0 + c * 32;
-        if (row_ok && col0 < a.N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = (t.num_k > 0) ? __fmul_rn(alpha, __uint_as_float(r[i])) : 0.0f;
-          const int nvalid = (int)min((int64_t)32, a.N - col0);
-          if (a.bias != nullptr) {
-            for (int i = 0; i < nvalid; ++i)
-              v[i] += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col0 + i]
-                                               : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col0 + i]);
-          }
-          const int64_t off = t.d_base + row * a.ldd + col0;
-          if (a.d_dtype == MT_F32) {
-            float* dst = static_cast<float*>(a.d) + off;
-            if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-              float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                if (a.accumulate) { float4 p = d4[i]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
-                d4[i] = o;
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) dst[i] = a.accumulate ? dst[i] + v[i] : v[i];
-            }
-          } else {
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + off;
-            if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-              uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                if (a.accumulate) {
-                  uint4 p = d4[i];
-                  const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    v[8 * i + 2 * j] += __uint_as_float(pw[j] << 16);
-                    v[8 * i + 2 * j + 1] += __uint_as_float(pw[j] & 0xFFFF0000u);
-                  }
-                }
-                uint32_t ow[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-                  ow[j] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                d4[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-              }
-            } else {
-              for (int i = 0; i < nvalid; ++i) {
-                float o = a.accumulate ? __bfloat162float(dst[i]) + v[i] : v[i];
-                dst[i] = __float2bfloat16_rn(o);
-              }
-            }
-          }
-        }
+        if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, t.num_k > 0, t.d_base + row * a.ldd + col0, col0);
       }
       tc_fence_before();
       __syncwarp();
@@ -392,6 +397,319 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
     tmem_dealloc(tmem_base, G_TMEM_COLS);
   }
 }
+
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair kernel (cta_group::2): a cluster of two CTAs computes a 256 x 256 output tile.
+// CTA r of the pair owns rows [128 r, 128 r + 128) of the tile (its A rows, its half of the
+// accumulator in its own tensor memory) and loads rows [128 r, +128) of the B tile; the
+// tensor cores of both SMs read both halves of B, so each byte of B is fetched from L2 and
+// written to shared memory once per pair. Scale factors: each CTA loads the A scales of its
+// own rows and the B scales of all 256 columns. The leader (rank 0) waits on one "full"
+// barrier that both CTAs' TMA loads signal, copies scale factors and issues the MMAs for
+// both SMs; tcgen05.commit signals the "empty" and "accumulator full" barriers in both CTAs.
+// No load is multicast.
+// ------------------------------------------------------------------------------------------
+constexpr int P_EPI_WARPS = 8;                       // two warps per tensor-memory lane quarter
+constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;     // producer warp + MMA warp + epilogue warps
+constexpr int P_BLOCK_N = 256;
+
+template <int kFormat, int STAGES>
+struct PairCfg {
+  static constexpr int CH = (kFormat == FMT_NVFP4) ? 4 : 1;
+  static constexpr int A_BYTES = G_BLOCK_M * G_BLOCK_KB;       // 128 rows of A
+  static constexpr int B_BYTES = 128 * G_BLOCK_KB;             // this CTA's 128 rows of B
+  static constexpr int SFA_BYTES = CH * 512;
+  static constexpr int SFB_BYTES = 2 * CH * 512;               // all 256 columns
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = STAGES * A_BYTES;
+  static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
+  static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
+  // 4 KiB output staging per epilogue warp; 1024-byte aligned so the 128-byte swizzle pattern
+  // of the TMA store lines up with the row index used when filling it
+  static constexpr int OFF_EPI = (OFF_SFB + STAGES * SFB_BYTES + 1023) / 1024 * 1024;
+  static constexpr int EPI_BYTES = P_EPI_WARPS * 4096;
+  static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2;
+  static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16;
+  static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+  static constexpr int TMEM_ACC = 0;
+  static constexpr int TMEM_SFA = P_BLOCK_N;
+  static constexpr int TMEM_SFB = TMEM_SFA + 4 * CH;
+  static_assert(TMEM_SFB + 8 * CH <= G_TMEM_COLS, "tensor memory over-subscribed");
+  static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory over-subscribed");
+};
+
+template <int kFormat>
+__device__ __forceinline__ void issue_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if (kFormat == FMT_NVFP4) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ uint32_t make_idesc_pair(int format, int sf_id) {
+  uint32_t d = 0;
+  if (format == FMT_NVFP4) {
+    d |= 1u << 7;
+    d |= 1u << 10;
+  } else {
+    d |= 1u << 23;
+    d |= static_cast<uint32_t>(sf_id) << 4;
+    d |= static_cast<uint32_t>(sf_id) << 29;
+  }
+  d |= static_cast<uint32_t>(P_BLOCK_N >> 3) << 17;
+  d |= static_cast<uint32_t>(256 >> 4) << 24;  // M = 256 across the pair
+  return d;
+}
+
+template <int kFormat, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+    gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                 const __grid_constant__ CUtensorMap map_sfa,
+                                 const __grid_constant__ CUtensorMap map_sfb,
+                                 const __grid_constant__ CUtensorMap map_d, const GemmArgs a) {
+  using Cfg = PairCfg<kFormat, STAGES>;
+  constexpr int CH = Cfg::CH;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* full_bar = bars;                 // used in the leader only (both CTAs' loads signal it)
+  uint64_t* empty_bar = bars + STAGES;       // one set per CTA, signalled by the leader's commit
+  uint64_t* acc_full = bars + 2 * STAGES;    // one per CTA, signalled by the leader's commit
+  uint64_t* acc_empty = bars + 2 * STAGES + 1;  // leader only: 2 x P_EPI_WARPS arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 2 * P_EPI_WARPS);
+    mbar_fence_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_sfa);
+    prefetch_tensormap(&map_sfb);
+    if (a.tma_store) prefetch_tensormap(&map_d);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, G_TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers must exist before either CTA signals the other
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_k = (int)((a.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB);
+
+  if (warp == 0) {
+    // ================= TMA producer (one per CTA) =================
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs) {
+        const int nb = tile / a.tiles_m, mb = tile - nb * a.tiles_m;
+        const int32_t a_row = mb * 256 + (int)rank * 128;
+        const int32_t b_row = nb * 256 + (int)rank * 128;
+        const int32_t sfa_chunk0 = (int32_t)((int64_t)(mb * 2 + (int)rank) * a.kc_a);
+        const int32_t sfb_chunk0 = (int32_t)((int64_t)(nb * 2) * a.kc_b);
+        for (int k = 0; k < num_k; ++k, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.status, DS_EMPTY_WAIT)) { alive = false; break; }
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+          const int32_t kx = k * G_BLOCK_KB;
+          tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, kx, a_row);
+          tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, kx, b_row);
+          tma_load_2d_pair(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, &map_sfa, bar, 0, sfa_chunk0 + k * CH);
+          tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES, &map_sfb, bar, 0, sfb_chunk0 + k * CH);
+          tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + CH * 512, &map_sfb, bar, 0,
+                           sfb_chunk0 + (int32_t)a.kc_b + k * CH);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issuer (leader CTA only) =================
+    if (leader && elect_one()) {
+      uint32_t it = 0, tile_it = 0;
+      bool alive = true;
+      const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
+      const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
+      for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
+        if (!mbar_wait_bounded(acc_empty, (tile_it & 1) ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC;
+        for (int k = 0; k < num_k; ++k, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+              tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFB + 4 * (c * 2 + h),
+                              umma_desc_sf(sfb_base + s * Cfg::SFB_BYTES + (h * CH + c) * 512));
+          const uint64_t adesc = umma_desc_sw128(a_base + s * Cfg::A_BYTES);
+          const uint64_t bdesc = umma_desc_sw128(b_base + s * Cfg::B_BYTES);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t idesc = make_idesc_pair(kFormat, j);
+            const uint32_t sfa_t = tmem_base + Cfg::TMEM_SFA + (kFormat == FMT_NVFP4 ? 4 * j : 0);
+            const uint32_t sfb_t = tmem_base + Cfg::TMEM_SFB + (kFormat == FMT_NVFP4 ? 8 * j : 0);
+            issue_mma_pair<kFormat>(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, (k > 0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(&empty_bar[s], 3);
+        }
+        if (alive) tc_commit_pair(acc_full, 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================= epilogue (both CTAs): warp e handles lane quarter e % 4, column half e / 4 =================
+    const int e = warp - 2;
+    const int q = warp & 3;          // hardware rule: a warp reads the lane quarter warp_id % 4
+    const int half = (e >> 2) & 1;   // with 8 warps, quarters repeat after 4 warps
+    float alpha = 1.0f;
+    if (a.amax_a != nullptr && a.amax_b != nullptr)
+      alpha = __fdiv_rn(__fmul_rn(*a.amax_a, *a.amax_b), 6.0f * 6.0f * 448.0f * 448.0f);
+    const uint32_t acc_empty_leader = map_to_cta(smem_u32(acc_empty), 0);
+    uint32_t tile_it = 0;
+    bool alive = true;
+    for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
+      const int nb = tile / a.tiles_m, mb = tile - nb * a.tiles_m;
+      if (!mbar_wait_bounded(acc_full, tile_it & 1, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
+      tc_fence_after();
+      const int64_t row0 = (int64_t)mb * 256 + rank * 128 + q * 32;
+      const int64_t row = row0 + lane;
+      const bool row_ok = row < a.M;
+      const int64_t colw = (int64_t)nb * P_BLOCK_N + half * 128;  // first of this warp's 128 columns
+      if (!a.tma_store) {
+        // direct path (unaligned outputs, bf16 accumulate): registers -> global, 32 columns at a time
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + (static_cast<uint32_t>(q * 32) << 16) + half * 128 + c * 32, r);
+          tc_wait_ld();
+          const int64_t col0 = colw + c * 32;
+          if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, num_k > 0, row * a.ldd + col0, col0);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        continue;
+      }
+      // Pull this warp's 32 x 128 accumulator block into registers and hand tensor memory
+      // back to the MMA issuer at once; conversion and stores overlap the next tile's MMAs.
+      uint32_t acc[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + (static_cast<uint32_t>(q * 32) << 16) + half * 128 + c * 32, acc[c]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+
+      uint8_t* stage = smem + Cfg::OFF_EPI + e * 4096;   // 32 rows x 128 bytes, 128-byte swizzle
+      const uint32_t swz = lane & 7;
+      const bool has_k = num_k > 0;
+      if (a.d_dtype == MT_BF16) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {           // 64 columns = 128 bytes per row
+          if (lane == 0) bulk_wait_read_all();     // the previous store has drained the buffer
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {            // 16-byte chunk j = columns 8j .. 8j+7
+            uint32_t w[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const int col = ch * 64 + j * 8 + t * 2;
+              float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
+              float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
+              if (a.bias != nullptr) {
+                const int64_t gc = colw + col;
+                if (gc < a.N) v0 += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[gc] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[gc]);
+                if (gc + 1 < a.N) v1 += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[gc + 1] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[gc + 1]);
+              }
+              __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+              w[t] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < a.M && colw + ch * 64 < a.N) {
+            tma_store_2d(&map_d, stage, (int32_t)(colw + ch * 64), (int32_t)row0);
+            bulk_commit_group();
+          }
+        }
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {           // 32 fp32 columns = 128 bytes per row
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float v[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[ch][j * 4 + t])) : 0.0f;
+              if (a.bias != nullptr) {
+                const int64_t gc = colw + ch * 32 + j * 4 + t;
+                if (gc < a.N) v[t] += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[gc] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[gc]);
+              }
+            }
+            *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < a.M && colw + ch * 32 < a.N) {
+            if (a.accumulate) tma_reduce_add_2d(&map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
+            else tma_store_2d(&map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
+            bulk_commit_group();
+          }
+        }
+      }
+    }
+  }
+
+  if (warp >= 2 && lane == 0) bulk_wait_all();  // output stores issued by this lane are complete
+  tc_fence_before();
+  __syncthreads();
+  // neither CTA may exit (or free tensor memory) while its peer can still touch it
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, G_TMEM_COLS);
+  }
+}
+
 
 // ------------------------------------------------------------------------------------------
 // host side
@@ -424,6 +742,33 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
 
 static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
 
+template <int kFormat, int STAGES>
+static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa,
+                            const CUtensorMap& msb, const CUtensorMap& md, const GemmArgs& args, cudaStream_t st) {
+  using Cfg = PairCfg<kFormat, STAGES>;
+  auto kern = gemm_blockscaled_pair_kernel<kFormat, STAGES>;
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+    // how many 2-CTA clusters can be resident at once (SMs pair up inside a GPC)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(P_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_ALLOC;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
+    max_pairs = n;
+  }
+  const int pairs = std::min(args.num_tiles, max_pairs);
+  kern<<<2 * pairs, P_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, msa, msb, md, args);
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
 // Environment override used while tuning: MT_GEMM_BLOCK_N = 128 or 256.
 static int pick_block_n(int64_t N) {
   static int forced = -1;
@@ -439,8 +784,18 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
                        const uint8_t* sb, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,
                        int64_t ldd, const void* bias, int bias_dtype, int accumulate, cudaStream_t st) {
   const char* name = format == FMT_NVFP4 ? "mt_gemm_nvfp4" : "mt_gemm_mxfp8";
-  MT_REQUIRE(a && sa && b && sb && d, "%s: null pointer", name);
+  MT_REQUIRE(d != nullptr, "%s: null output pointer", name);
   MT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative shape", name);
+  if (K == 0) {
+    // empty contraction: the product is all zeros (bias and previous contents are kept out of
+    // this corner: the emulation returns plain zeros for it as well)
+    if (M > 0 && N > 0 && !accumulate) {
+      const size_t es = d_dtype == MT_F32 ? 4 : 2;
+      MT_CUDA(cudaMemset2DAsync(d, (size_t)ldd * es, 0, (size_t)N * es, (size_t)M, st));
+    }
+    return MT_OK;
+  }
+  MT_REQUIRE(a && sa && b && sb, "%s: null pointer", name);
   MT_REQUIRE(d_dtype == MT_BF16 || d_dtype == MT_F32, "%s: output dtype %d not supported", name, d_dtype);
   MT_REQUIRE(bias == nullptr || bias_dtype == MT_BF16 || bias_dtype == MT_F32, "%s: bias dtype %d not supported", name, bias_dtype);
   MT_REQUIRE(ldd >= N, "%s: ldd (%lld) smaller than N (%lld)", name, (long long)ldd, (long long)N);
@@ -465,6 +820,46 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
   args.mode = MODE_DENSE;
   args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
+  static int use_pair = -1;  // MT_GEMM_PAIR=0 forces the single-CTA kernel (tuning aid)
+  if (use_pair < 0) {
+    const char* e = getenv("MT_GEMM_PAIR");
+    use_pair = e ? atoi(e) : 1;
+  }
+  // K == 0 never reaches this point; tensor maps below need K_bytes >= 16
+  if (use_pair && M > G_BLOCK_M && N > 128) {
+    args.tiles_m = (int)((M + 255) / 256);
+    args.tiles_n = (int)((N + 255) / 256);
+    args.num_tiles = args.tiles_m * args.tiles_n;
+    CUtensorMap ma, mb, msa, msb;
+    int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K_bytes, (uint64_t)M, (uint64_t)K_bytes,
+                                G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != MT_OK) return rc;
+    rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)K_bytes, (uint64_t)N, (uint64_t)K_bytes,
+                            G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != MT_OK) return rc;
+    const uint32_t ch = format == FMT_NVFP4 ? 4 : 1;
+    rc = make_tensor_map_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sa, 128, (uint64_t)(args.rb_a * args.kc_a), 512, 128, ch,
+                            CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != MT_OK) return rc;
+    rc = make_tensor_map_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sb, 128, (uint64_t)(args.rb_b * args.kc_b), 512, 128, ch,
+                            CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != MT_OK) return rc;
+    // Output through shared memory + TMA stores when the output rows are 16-byte aligned;
+    // fp32 accumulation uses the TMA add-reduction, bf16 accumulation the direct path.
+    const size_t es = d_dtype == MT_F32 ? 4 : 2;
+    static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
+    if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
+    CUtensorMap md = ma;
+    args.tma_store = allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16);
+    if (args.tma_store) {
+      rc = make_tensor_map_2d(&md, d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                              (int)es, d, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * es, d_dtype == MT_F32 ? 32 : 64, 32,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != MT_OK) return rc;
+    }
+    return format == FMT_NVFP4 ? launch_gemm_pair<FMT_NVFP4, 5>(ma, mb, msa, msb, md, args, st)
+                               : launch_gemm_pair<FMT_MXFP8, 5>(ma, mb, msa, msb, md, args, st);
+  }
   const int bn = pick_block_n(N);
   args.tiles_m = (int)((M + G_BLOCK_M - 1) / G_BLOCK_M);
   args.tiles_n = (int)((N + bn - 1) / bn);

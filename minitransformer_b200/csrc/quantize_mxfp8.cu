@@ -208,8 +208,9 @@ extern "C" int mt_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, uint
                                  mt_stream_t stream) {
   using namespace mt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MT_REQUIRE(x && q && s, "mt_quantize_mxfp8: null x/q/s");
   MT_REQUIRE(rows >= 0 && cols >= 0, "mt_quantize_mxfp8: negative shape");
+  if (rows == 0 || cols == 0) return MT_OK;  // nothing to write; pointers may be null
+  MT_REQUIRE(x && q && s, "mt_quantize_mxfp8: null x/q/s");
   MT_REQUIRE(cols % 32 == 0, "mt_quantize_mxfp8: cols (%lld) must be a multiple of 32", (long long)cols);
   MT_REQUIRE(aligned16(x) && aligned16(q), "mt_quantize_mxfp8: x and q must be 16-byte aligned");
   const bool transpose = q_t != nullptr;

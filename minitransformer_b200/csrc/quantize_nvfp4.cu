@@ -325,17 +325,19 @@ int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* am
                  mt_stream_t stream) {
   using namespace mt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MT_REQUIRE(x && amax_row, "mt_amax_bf16: null pointer");
+  MT_REQUIRE(amax_row != nullptr, "mt_amax_bf16: null amax_row");
   MT_REQUIRE(rows >= 0 && cols >= 0 && cols % 8 == 0, "mt_amax_bf16: cols (%lld) must be a multiple of 8", (long long)cols);
+  if (rows == 0 || cols == 0) {  // an empty tensor has abs-max 0 and may come with a null pointer
+    MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
+    if (amax_col) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+    return MT_OK;
+  }
+  MT_REQUIRE(x != nullptr, "mt_amax_bf16: null x");
   MT_REQUIRE(aligned16(x), "mt_amax_bf16: x must be 16-byte aligned");
   const bool rht = (flags & MT_Q_RHT) && amax_col != nullptr;
   MT_REQUIRE(!rht || rows % 16 == 0, "mt_amax_bf16: the Hadamard transform needs rows %% 16 == 0 (rows=%lld)", (long long)rows);
   MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
   if (rht) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
-  if (rows == 0 || cols == 0) {
-    if (amax_col && !rht) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
-    return MT_OK;
-  }
   if (rht) {
     dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
     amax_rht_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x), rows, cols, amax_row, amax_col);
@@ -354,15 +356,16 @@ int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, cons
                       uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, mt_stream_t stream) {
   using namespace mt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  MT_REQUIRE(x && q && s && amax_row, "mt_quantize_nvfp4: null x/q/s/amax_row");
   MT_REQUIRE(rows >= 0 && cols >= 0, "mt_quantize_nvfp4: negative shape");
+  if (rows == 0 || cols == 0) return MT_OK;  // nothing to write; pointers may be null
+  MT_REQUIRE(x && q && s && amax_row, "mt_quantize_nvfp4: null x/q/s/amax_row");
   MT_REQUIRE(cols % 16 == 0, "mt_quantize_nvfp4: cols (%lld) must be a multiple of 16", (long long)cols);
-  MT_REQUIRE(rows % 2 == 0, "mt_quantize_nvfp4: rows (%lld) must be even", (long long)rows);
   MT_REQUIRE(aligned16(x) && aligned16(q), "mt_quantize_nvfp4: x and q must be 16-byte aligned");
   const bool transpose = q_t != nullptr;
   const bool d2 = (flags & MT_Q_2D) != 0, rht = (flags & MT_Q_RHT) != 0;
   const bool pad16 = d2 || (flags & MT_Q_ROWPAD16);
   MT_REQUIRE(!transpose || (s_t && amax_col), "mt_quantize_nvfp4: q_t given without s_t / amax_col");
+  MT_REQUIRE(!transpose || rows % 2 == 0, "mt_quantize_nvfp4: the transposed copy needs an even row count (rows=%lld)", (long long)rows);
   MT_REQUIRE(!(d2 && rht), "mt_quantize_nvfp4: 2-D scaling together with the Hadamard transform is not supported");
   MT_REQUIRE(!rht || rows % 16 == 0, "mt_quantize_nvfp4: the Hadamard transform needs rows %% 16 == 0");
   MT_REQUIRE(s_stride >= cols / 16 && (!transpose || s_t_stride >= (rows + 15) / 16), "mt_quantize_nvfp4: scale stride too small");

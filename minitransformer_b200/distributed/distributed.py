@@ -1,0 +1,86 @@
+"""Tensor-parallel collectives used by the linear modules: thin wrappers over
+torch.distributed on the caller's process group (NCCL over NVLink on GPUs, gloo in the CPU
+tests). Same entry points as miniTransformer/distributed/distributed.py:13-121, plus the
+packed quantized all-gather this implementation adds."""
+from typing import Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..utils.utils import FP8_DTYPES
+
+_TP_ATTRS = {"tensor_model_parallel": False, "partition_dim": -1, "partition_stride": 1}
+
+
+def get_distributed_world_size(group=None) -> int:
+    return dist.get_world_size(group=group) if dist.is_initialized() else 1
+
+
+def get_distributed_rank(group=None) -> int:
+    return dist.get_rank(group=group) if dist.is_initialized() else 0
+
+
+def set_tensor_model_parallel_attributes(tensor: torch.Tensor, is_parallel: bool, dim: int, stride: int) -> None:
+    for name in _TP_ATTRS:
+        assert not hasattr(tensor, name), f"{name} already set"
+    tensor.tensor_model_parallel = is_parallel
+    tensor.partition_dim = dim
+    tensor.partition_stride = stride
+
+
+def reduce_scatter_along_first_dim(input: torch.Tensor, tp_group, async_op: bool = False):
+    world = get_distributed_world_size(tp_group)
+    if world == 1:
+        return input, None
+    assert input.shape[0] % world == 0, "first dimension must divide by the tensor-parallel size"
+    out = torch.empty((input.shape[0] // world, *input.shape[1:]), dtype=input.dtype, device=input.device)
+    handle = dist.reduce_scatter_tensor(out, input.contiguous(), group=tp_group, async_op=async_op)
+    return out, handle
+
+
+def gather_along_first_dim(input: torch.Tensor, process_group, async_op: bool = False):
+    world = get_distributed_world_size(process_group)
+    if world == 1:
+        return input, None
+    out = torch.empty((input.shape[0] * world, *input.shape[1:]), dtype=input.dtype, device=input.device)
+    src, dst = input.contiguous(), out
+    if input.dtype in FP8_DTYPES:  # byte view: collectives need not know the 8-bit float types
+        src, dst = src.view(torch.uint8), dst.view(torch.uint8)
+    handle = dist.all_gather_into_tensor(dst, src, group=process_group, async_op=async_op)
+    return out, handle
+
+
+def allreduce(input_: torch.Tensor, tp_group=None, async_op: bool = False):
+    if get_distributed_world_size(tp_group) == 1:
+        return input_, None
+    handle = dist.all_reduce(input_, group=tp_group, async_op=async_op)
+    return input_, handle
+
+
+def allreduce_max_(scalars: torch.Tensor, tp_group) -> torch.Tensor:
+    """In-place MAX all-reduce of a few fp32 scalars (the per-tensor abs-max values), so that
+    every rank quantizes its shard with the scale of the gathered tensor."""
+    if get_distributed_world_size(tp_group) > 1:
+        dist.all_reduce(scalars, op=dist.ReduceOp.MAX, group=tp_group)
+    return scalars
+
+
+def gather_packed_along_first_dim(parts: Sequence[torch.Tensor], process_group) -> Tuple[torch.Tensor, ...]:
+    """All-gathers several byte tensors that share their first-dim sharding with ONE collective:
+    each rank packs [codes | scales | ...] of its shard into one buffer; after the gather the
+    pieces are re-assembled per tensor in rank order along dim 0."""
+    world = get_distributed_world_size(process_group)
+    if world == 1:
+        return tuple(parts)
+    flat = [p.contiguous().view(torch.uint8).reshape(-1) for p in parts]
+    sizes = [f.numel() for f in flat]
+    packed = torch.cat(flat)
+    out = torch.empty(world * packed.numel(), dtype=torch.uint8, device=packed.device)
+    dist.all_gather_into_tensor(out, packed, group=process_group)
+    out = out.view(world, packed.numel())
+    res, off = [], 0
+    for p, n in zip(parts, sizes):
+        piece = out[:, off:off + n].reshape(world * p.shape[0], *p.shape[1:]) if p.dim() > 0 else out[:, off:off + n]
+        res.append(piece.contiguous().view(p.dtype) if p.dtype != torch.uint8 else piece.contiguous())
+        off += n
+    return tuple(res)

@@ -9,6 +9,16 @@ from . import _lib
 from ._lib import MT_BF16, MT_F32, MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16  # noqa: F401
 
 
+# Number of kernels of this library launched through this module since it was last reset
+# (the benchmark reports it; memsets are not counted).
+LAUNCH_COUNT = 0
+
+
+def _count(n: int) -> None:
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += n
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
@@ -48,6 +58,8 @@ def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True):
     flags = MT_Q_RHT if with_rht else 0
     _lib.call("mt_amax_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
               amax[1:2].data_ptr() if need_col else None, _stream())
+    if x.numel():
+        _count(1 if with_rht else (2 if need_col else 1))
     return amax[0:1], (amax[1:2] if need_col else amax[0:1])
 
 
@@ -79,6 +91,7 @@ def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with
     _lib.call("mt_quantize_nvfp4", x.data_ptr(), M, K, flags, amax_row.data_ptr(), _ptr(amax_col),
               q.data_ptr(), s.data_ptr(), K // 16, s_swz.data_ptr(),
               _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
+    _count(1 if x.numel() else 0)
     return Quantized(q, s, s_swz, q_t, s_t, s_t_swz, amax_row, amax_col if return_transpose else amax_row)
 
 
@@ -99,6 +112,7 @@ def quantize_mxfp8(x: torch.Tensor, *, return_transpose: bool = True) -> Quantiz
         s_t_swz = torch.empty(swizzled_scale_bytes(K, mb), dtype=u8, device=dev)
     _lib.call("mt_quantize_mxfp8", x.data_ptr(), M, K, q.data_ptr(), s.data_ptr(), K // 32, s_swz.data_ptr(),
               _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
+    _count(1 if x.numel() else 0)
     return Quantized(q, s, s_swz, q_t, s_t, s_t_swz)
 
 
@@ -110,6 +124,7 @@ def swizzle_scales(s: torch.Tensor, rows: Optional[int] = None) -> torch.Tensor:
     R = s.shape[0] if rows is None else rows
     out = torch.empty(swizzled_scale_bytes(R, s.shape[1]), dtype=torch.uint8, device=s.device)
     _lib.call("mt_swizzle_scales", s.data_ptr(), R, s.shape[1], s.stride(0), out.data_ptr(), _stream())
+    _count(1 if R and s.shape[1] else 0)
     return out
 
 
@@ -139,6 +154,7 @@ def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1] * 2
     assert qb.shape[1] * 2 == K
     out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
+    _count(1 if M and N and K else 0)
     if check_kernel:
         _lib.call("mt_gemm_nvfp4_check", qa.data_ptr(), sa_lin.data_ptr(), sa_lin.stride(0), amax_a.data_ptr(),
                   qb.data_ptr(), sb_lin.data_ptr(), sb_lin.stride(0), amax_b.data_ptr(), M, N, K,
@@ -157,6 +173,7 @@ def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, ac
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1]
     assert qb.shape[1] == K
     out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
+    _count(1 if M and N and K else 0)
     if check_kernel:
         _lib.call("mt_gemm_mxfp8_check", qa.data_ptr(), sa_lin.data_ptr(), sa_lin.stride(0), qb.data_ptr(),
                   sb_lin.data_ptr(), sb_lin.stride(0), M, N, K, out.data_ptr(), _out_dtype_code(out_dtype),

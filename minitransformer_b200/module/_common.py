@@ -1,0 +1,47 @@
+"""Concatenation of parameter views that avoids a copy when the views already sit back to
+back in one buffer (what `parameters_split` creates). Same role as
+miniTransformer/module/_common.py:98-113."""
+from typing import Sequence
+
+import torch
+
+
+class _NoopCat(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, dim, *tensors):
+        first = tensors[0]
+        ctx.dim = dim
+        ctx.sizes = [t.shape[dim] for t in tensors]
+        if dim != 0 or not _adjacent(tensors):
+            return torch.cat(tensors, dim=dim)
+        shape = list(first.shape)
+        shape[0] = sum(ctx.sizes)
+        out = first.new_empty(0)
+        out.set_(first.untyped_storage(), first.storage_offset(), shape, first.stride())
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        return (None, *torch.split(grad, ctx.sizes, dim=ctx.dim))
+
+
+def _adjacent(tensors: Sequence[torch.Tensor]) -> bool:
+    first = tensors[0]
+    if not first.is_contiguous():
+        return False
+    ptr = first.data_ptr()
+    for t in tensors:
+        if (not t.is_contiguous() or t.dtype != first.dtype or t.device != first.device
+                or t.shape[1:] != first.shape[1:] or t.data_ptr() != ptr
+                or t.untyped_storage().data_ptr() != first.untyped_storage().data_ptr()):
+            return False
+        ptr += t.numel() * t.element_size()
+    return True
+
+
+def noop_cat(tensors: Sequence[torch.Tensor], dim: int = 0) -> torch.Tensor:
+    if not tensors:
+        raise ValueError("noop_cat needs at least one tensor")
+    if len(tensors) == 1:
+        return tensors[0]
+    return _NoopCat.apply(dim, *tensors)

@@ -1,0 +1,408 @@
+"""Drop-in `Linear` with block-quantized forward, dgrad and wgrad GEMMs.
+
+API, parameter naming, tensor-/sequence-parallel behaviour, the weight-quantization cache
+across microbatches and the Megatron `main_grad` protocol follow the reference module
+(miniTransformer/module/linear.py:27-949), so `class TELinear(Linear)` keeps working. What
+is new underneath: the quantize backend in `QLinearParams.quantize_op` runs the sm_100a
+kernels, sequence-parallel inputs can be gathered in quantized form (codes + scales, one
+packed collective, after a MAX all-reduce of the per-tensor abs-max), and
+`fuse_wgrad_accumulation` really accumulates into `weight.main_grad` in place.
+"""
+import logging
+from typing import Any, Callable, Dict, List, Optional, Tuple, Union
+
+import torch
+
+from . import config
+from ._common import noop_cat
+from .base import LayerLinearBaseModule
+from ..distributed.distributed import (allreduce, gather_along_first_dim, gather_packed_along_first_dim,
+                                       get_distributed_rank, get_distributed_world_size,
+                                       reduce_scatter_along_first_dim, set_tensor_model_parallel_attributes)
+from ..ops import quantization
+from ..utils.utils import cast_if_needed, divide, init_method_constant, is_rank_0
+
+logger = logging.getLogger(__name__)
+
+_NUM_FN_ARGS = 14
+
+
+class _NonQuantizedLinear(torch.autograd.Function):
+    """High-precision path: y = x w^T, dx = dy w, dw = dy^T x, with the same collectives."""
+
+    @staticmethod
+    def forward(ctx, x, x_meta, w, weight_qresult_cache, bias, sequence_parallel, tp_group, tp_size,
+                parallel_mode, qlinear_params, activation_dtype, is_grad_enabled, is_first_microbatch,
+                fuse_wgrad_accumulation):
+        x_shape = x.shape
+        x = cast_if_needed(x.reshape(-1, x_shape[-1]), activation_dtype)
+        bias = cast_if_needed(bias, activation_dtype)
+        if parallel_mode == "column" and sequence_parallel:
+            x, _ = gather_along_first_dim(x, tp_group)
+        y = torch.nn.functional.linear(x, w, bias)
+        if is_grad_enabled:
+            ctx.use_bias = bias is not None
+            ctx.sequence_parallel, ctx.tp_group, ctx.tp_size = sequence_parallel, tp_group, tp_size
+            ctx.parallel_mode, ctx.x_shape = parallel_mode, x_shape
+            ctx.save_for_backward(x, w)
+        if parallel_mode == "row" and sequence_parallel:
+            y, _ = reduce_scatter_along_first_dim(y, tp_group)
+        elif parallel_mode == "row" and tp_size > 1:
+            y, _ = allreduce(y, tp_group)
+        return y.view(-1, *x_shape[1:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous().view(-1, dy.shape[-1])
+        b_grad = dy.sum(dim=0) if ctx.use_bias else None
+        if ctx.parallel_mode == "row" and ctx.sequence_parallel:
+            dy, _ = gather_along_first_dim(dy, ctx.tp_group)
+        dgrad = dy @ w
+        handle = None
+        if ctx.parallel_mode == "column" and ctx.sequence_parallel:
+            dgrad, handle = reduce_scatter_along_first_dim(dgrad, ctx.tp_group, True)
+        elif ctx.parallel_mode == "column" and ctx.tp_size > 1:
+            dgrad, handle = allreduce(dgrad, ctx.tp_group, True)
+        wgrad = dy.t() @ x
+        if handle is not None:
+            handle.wait()
+        dgrad = dgrad.view(-1, *ctx.x_shape[1:])
+        return (dgrad, None, wgrad, None, b_grad) + (None,) * (_NUM_FN_ARGS - 5)
+
+
+def _interleave_gathered_transpose(stacked: torch.Tensor, world: int) -> torch.Tensor:
+    """[world * R, C_local] (rank-major stack of per-rank transposed shards) -> [R, world * C_local]."""
+    r = stacked.shape[0] // world
+    return stacked.view(world, r, stacked.shape[1]).permute(1, 0, 2).reshape(r, world * stacked.shape[1])
+
+
+class _QuantizedLinear(torch.autograd.Function):
+    """Quantized path. All three GEMMs take K-major operands:
+         fprop  y  = q(x)       . q(w)^T           contraction over in_features
+         dgrad  dx = q(dy)      . q(w^T copy)^T    contraction over out_features
+         wgrad  dw = q(dy^T copy) . q(x^T copy)^T  contraction over tokens (fp32 output)
+    """
+
+    @staticmethod
+    def forward(ctx, x, x_meta, w, weight_qresult_cache, bias, sequence_parallel, tp_group, tp_size,
+                parallel_mode, qlinear_params, activation_dtype, is_grad_enabled, is_first_microbatch,
+                fuse_wgrad_accumulation):
+        op: quantization.QuantizeOpBase = qlinear_params.quantize_op
+        assert op is not None, "QLinearParams.quantize_op is not set"
+        x_shape = x.shape
+        out_dtype = qlinear_params.mm_fprop.out_dtype or x.dtype
+        x = cast_if_needed(x.reshape(-1, x_shape[-1]), activation_dtype)
+        bias = cast_if_needed(bias, activation_dtype)
+
+        gather_required = parallel_mode == "column" and sequence_parallel
+        qres_x = _QuantizedLinear.quantize_optionally_allgather(
+            op, x, qlinear_params.x_params, transpose_required=is_grad_enabled,
+            allgather_required=gather_required, allgather_quantize=qlinear_params.allgather_quantize,
+            tp_group=tp_group, keep_transpose_local=qlinear_params.memory_saving and gather_required)
+
+        # weights are re-quantized on the first microbatch (or when the caller gives no hint)
+        if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
+            qres_w = op.quantize(w, qlinear_params.w_params, return_transpose=True)
+            weight_qresult_cache.store(qres_w)
+        else:
+            qres_w = weight_qresult_cache.to_qresult()
+
+        y = op.qgemm(qres_x.data, qres_w.data, qlinear_params.mm_fprop, out_dtype, qres_x.scale, qres_w.scale,
+                     bias, accumulate=False, global_amax_qx=qres_x.global_amax_row,
+                     global_amax_qw=qres_w.global_amax_row, qparams_x=qlinear_params.x_params,
+                     qparams_w=qlinear_params.w_params)
+
+        if is_grad_enabled:
+            ctx.use_bias = bias is not None
+            ctx.sequence_parallel, ctx.tp_group, ctx.tp_size = sequence_parallel, tp_group, tp_size
+            ctx.tp_rank = get_distributed_rank(tp_group)
+            ctx.x_gather_required = gather_required
+            ctx.parallel_mode, ctx.x_shape = parallel_mode, x_shape
+            ctx.qlinear_params, ctx.quantize_op = qlinear_params, op
+            ctx.is_first_microbatch = is_first_microbatch
+            ctx.fuse_wgrad_accumulation = fuse_wgrad_accumulation
+            ctx.activation_dtype = activation_dtype
+            ctx.x_t_is_local_shard = bool(getattr(qres_x, "_t_is_local_shard", False))
+            # transposed copies only; their GEMM-layout scales travel as plain attributes
+            ctx.sx_t_swz, ctx.sw_t_swz = qres_x.scale_t_swz, qres_w.scale_t_swz
+            ctx.save_for_backward(qres_x.data_t, qres_x.scale_t, qres_x.global_amax_col,
+                                  qres_w.data_t, qres_w.scale_t, qres_w.global_amax_col, w)
+
+        if parallel_mode == "row" and sequence_parallel:
+            y, _ = reduce_scatter_along_first_dim(y, tp_group)
+        elif parallel_mode == "row" and tp_size > 1:
+            y, _ = allreduce(y, tp_group)
+        return y.view(-1, *x_shape[1:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        qx_t, sx_t, amax_x_col, qw_t, sw_t, amax_w_col, w = ctx.saved_tensors
+        p, op = ctx.qlinear_params, ctx.quantize_op
+        if sx_t is not None and ctx.sx_t_swz is not None:
+            sx_t._mt_swz = ctx.sx_t_swz
+        if ctx.sw_t_swz is not None:
+            sw_t._mt_swz = ctx.sw_t_swz
+        out_dtype_dgrad = p.mm_dgrad.out_dtype or dy.dtype
+        dy = dy.contiguous().view(-1, dy.shape[-1])
+        b_grad = dy.sum(dim=0) if ctx.use_bias else None
+
+        gather_required = ctx.parallel_mode == "row" and ctx.sequence_parallel
+        qres_dy = _QuantizedLinear.quantize_optionally_allgather(
+            op, dy, p.g_params, transpose_required=True, allgather_required=gather_required,
+            allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group)
+
+        # memory-saving mode kept only this rank's token shard of x^T: gather it back while
+        # the dgrad GEMM runs
+        pending_x_t = None
+        if ctx.x_t_is_local_shard:
+            pending_x_t = _QuantizedLinear._start_gather_transposed(qx_t, sx_t, ctx.tp_group)
+
+        dgrad = op.qgemm(qres_dy.data, qw_t, p.mm_dgrad, out_dtype_dgrad, qres_dy.scale, sw_t, None, None,
+                         accumulate=False, global_amax_qx=qres_dy.global_amax_row, global_amax_qw=amax_w_col,
+                         qparams_x=p.g_params, qparams_w=p.w_params)
+
+        if pending_x_t is not None:
+            qx_t, sx_t = _QuantizedLinear._finish_gather_transposed(pending_x_t, ctx.tp_group)
+
+        handle = None
+        if ctx.parallel_mode == "column" and ctx.sequence_parallel:
+            dgrad, handle = reduce_scatter_along_first_dim(dgrad, ctx.tp_group, True)
+        elif ctx.parallel_mode == "column" and ctx.tp_size > 1:
+            dgrad, handle = allreduce(dgrad, ctx.tp_group, True)
+
+        wgrad = None
+        if w.requires_grad:
+            if ctx.is_first_microbatch is not None:
+                accumulate = ctx.fuse_wgrad_accumulation and not ctx.is_first_microbatch
+            else:
+                accumulate = ctx.fuse_wgrad_accumulation
+            main_grad = w.main_grad if ctx.fuse_wgrad_accumulation else None
+            wgrad = op.qgemm(qres_dy.data_t, qx_t, p.mm_wgrad,
+                             main_grad.dtype if main_grad is not None else torch.float32,
+                             qres_dy.scale_t, sx_t, None, out=main_grad, accumulate=accumulate,
+                             global_amax_qx=qres_dy.global_amax_col, global_amax_qw=amax_x_col,
+                             qparams_x=p.g_params, qparams_w=p.x_params)
+            wgrad = _QuantizedLinear.reset_wgrad_if_needed(ctx, w, wgrad)
+
+        if handle is not None:
+            handle.wait()
+        dgrad = dgrad.view(-1, *ctx.x_shape[1:])
+        return (dgrad, None, wgrad, None, b_grad) + (None,) * (_NUM_FN_ARGS - 5)
+
+    # -- helpers ------------------------------------------------------------------------------
+    @staticmethod
+    def quantize_optionally_allgather(quantize_op, x, qparams, transpose_required, allgather_required,
+                                      allgather_quantize, tp_group, keep_transpose_local=False):
+        """Quantizes x, gathering it across the tensor-parallel group first (bf16) or after
+        (quantized) when the layer is sequence-parallel.
+
+        Quantized gather: every rank quantizes its token shard with the MAX-all-reduced
+        per-tensor abs-max, then ONE collective moves [codes | scales | codes^T | scales^T].
+        Row-wise blocks run along features, so the gathered codes and scales are bit-identical
+        to quantizing the gathered tensor. The transposed copy of each shard is a K-slice of
+        the global transposed copy (shard length is a multiple of the block), re-interleaved
+        after the gather."""
+        if not allgather_required:
+            return quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=False,
+                                        tp_group=tp_group)
+        assert tp_group is not None
+        if not (allgather_quantize and quantize_op.supports_allgather):
+            x, _ = gather_along_first_dim(x, tp_group)
+            return quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=False,
+                                        tp_group=tp_group)
+        world = get_distributed_world_size(tp_group)
+        block = qparams.quant_tile_shape[1] if qparams.quant_tile_shape else 32
+        assert x.shape[0] % block == 0, "token shard must be a multiple of the quantization block"
+        r = quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=True,
+                                 tp_group=tp_group)
+        rows = x.shape[0]
+        parts = [r.data, r.scale[:rows]]
+        gather_t = transpose_required and not keep_transpose_local
+        if gather_t:
+            parts += [r.data_t, r.scale_t[: x.shape[1]]]
+        g = gather_packed_along_first_dim(parts, tp_group)
+        out = quantization.QuantizeResult(g[0], g[1], None, None, r.global_amax_row, r.global_amax_col)
+        if gather_t:
+            out.data_t = _interleave_gathered_transpose(g[2], world)
+            out.scale_t = _interleave_gathered_transpose(g[3], world)
+        elif transpose_required:
+            out.data_t, out.scale_t = r.data_t, r.scale_t[: x.shape[1]]
+            out._t_is_local_shard = True
+        return out
+
+    @staticmethod
+    def _start_gather_transposed(qx_t, sx_t, tp_group):
+        world = get_distributed_world_size(tp_group)
+        flat = torch.cat([qx_t.contiguous().view(torch.uint8).reshape(-1),
+                          sx_t.contiguous().view(torch.uint8).reshape(-1)])
+        out = torch.empty(world * flat.numel(), dtype=torch.uint8, device=flat.device)
+        handle = torch.distributed.all_gather_into_tensor(out, flat, group=tp_group, async_op=True)
+        return out, handle, qx_t, sx_t
+
+    @staticmethod
+    def _finish_gather_transposed(pending, tp_group):
+        out, handle, qx_t, sx_t = pending
+        handle.wait()
+        world = get_distributed_world_size(tp_group)
+        out = out.view(world, -1)
+        nq = qx_t.numel()
+        q = out[:, :nq].reshape(world * qx_t.shape[0], qx_t.shape[1])
+        s = out[:, nq:].reshape(world * sx_t.shape[0], sx_t.shape[1])
+        return (_interleave_gathered_transpose(q, world).view(qx_t.dtype),
+                _interleave_gathered_transpose(s, world).view(sx_t.dtype))
+
+    @staticmethod
+    def reset_wgrad_if_needed(ctx, w, wgrad):
+        """Megatron's main_grad protocol (miniTransformer/module/linear.py:515-550): once the
+        gradient sits in w.main_grad, autograd gets a dummy of the weight's shape (zeros when
+        the parameter asks for it) or nothing at all."""
+        if not w.requires_grad:
+            return None
+        if not ctx.fuse_wgrad_accumulation:
+            return wgrad
+        if hasattr(w, "grad_added_to_main_grad"):
+            make = torch.zeros if getattr(w, "zero_out_wgrad", False) else torch.empty
+            w.grad_added_to_main_grad = True
+            return make(w.main_grad.shape, dtype=w.dtype, device=w.device, requires_grad=False)
+        return None
+
+
+class Linear(LayerLinearBaseModule):
+    """y = x A^T + b with optional block-quantized GEMMs; drop-in for `torch.nn.Linear` /
+    TransformerEngine's `Linear` (constructor and forward signature of
+    miniTransformer/module/linear.py:632-655, 864-870).
+
+    parallel_mode: None | "column" | "row" (Megatron tensor parallelism; `in_features` /
+    `out_features` are divided accordingly). sequence_parallel: all-gather before a column
+    layer, reduce-scatter after a row layer. fuse_wgrad_accumulation: accumulate the weight
+    gradient into `weight.main_grad`. return_bias: hand the bias back instead of adding it.
+    parameters_split: names (or name -> size) of several parameters carved out of one weight
+    buffer along dim 0. qlinear_params: the recipe; if None it is taken from QAT_PARAMS.
+    """
+
+    def __init__(self, in_features: int, out_features: int, sequence_parallel: bool = False,
+                 fuse_wgrad_accumulation: bool = False, tp_group=None, tp_size: int = 1,
+                 get_rng_state_tracker: Optional[Callable] = None, rng_tracker_name: Optional[str] = None,
+                 init_method: Optional[Callable] = None, bias: bool = True, return_bias: bool = False,
+                 params_dtype: Optional[torch.dtype] = None, parallel_mode: Optional[str] = None,
+                 parameters_split: Optional[Union[Tuple[str, ...], Dict[str, int]]] = None,
+                 device: Union[torch.device, str] = "cuda", ub_overlap_rs: bool = False,
+                 ub_overlap_ag: bool = False, ub_name: Optional[str] = None,
+                 layer_number: Optional[int] = None,
+                 qlinear_params: Optional[config.QLinearParams] = None) -> None:
+        super().__init__(tp_group, tp_size, sequence_parallel)
+        params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
+        self.in_features, self.out_features = in_features, out_features
+        self.fuse_wgrad_accumulation = fuse_wgrad_accumulation
+        self.use_bias, self.return_bias = bias, return_bias
+        self.apply_bias = bias and not return_bias
+        self.ub_overlap_rs, self.ub_overlap_ag = ub_overlap_rs, ub_overlap_ag
+        if ub_overlap_rs or ub_overlap_ag:
+            assert ub_name is not None, "Userbuffer name [string] is not set."
+        self.ub_name = self.layer_name = ub_name
+        self.get_rng_state_tracker, self.rng_tracker_name = get_rng_state_tracker, rng_tracker_name
+        self.layer_number = layer_number
+        self.qlinear_params = self.set_qlinear_params(qlinear_params=qlinear_params, layer_number=layer_number,
+                                                      layer_name=self.layer_name)
+        if is_rank_0():
+            logger.info("layer %s linear %s uses %s", layer_number, self.layer_name, self.qlinear_params)
+        if device == "meta":
+            assert parameters_split is None, "Cannot split module parameters on 'meta' device."
+        assert parallel_mode in ("row", "column", None), f"parallel_mode {parallel_mode} not supported"
+        self.parallel_mode = parallel_mode
+        if parallel_mode == "column":
+            self.out_features = divide(out_features, self.tp_size)
+        elif parallel_mode == "row":
+            self.in_features = divide(in_features, self.tp_size)
+
+        weight_buf = torch.empty(self.out_features, self.in_features, device=device, dtype=params_dtype)
+        bias_buf = torch.empty(self.out_features, device=device, dtype=params_dtype) if bias else None
+
+        # names and sizes of the parameters carved out of the buffers
+        if parameters_split is None:
+            names, sizes = [""], [out_features]
+        elif not parameters_split:
+            raise ValueError("Cannot split weight buffer into 0 parameters")
+        elif isinstance(parameters_split, dict):
+            names, sizes = [n.rstrip("_") for n in parameters_split], list(parameters_split.values())
+        elif all(isinstance(n, str) for n in parameters_split):
+            assert out_features % len(parameters_split) == 0, "Invalid split size"
+            names = [n.rstrip("_") for n in parameters_split]
+            sizes = [out_features // len(names)] * len(names)
+        else:
+            raise TypeError("Invalid configuration for parameters split")
+        if sum(sizes) != out_features:
+            raise ValueError(f"Trying to split weight buffer ({out_features=}) with split sizes {sizes}")
+        if parallel_mode == "column":
+            for s in sizes:
+                if s % self.tp_size != 0:
+                    raise RuntimeError(f"Attempting to distribute a parameter with out_features={s} "
+                                       f"between {self.tp_size} tensor-parallel processes")
+            sizes = [s // self.tp_size for s in sizes]
+        self.weight_names = [f"{n}_weight" if n else "weight" for n in names]
+        self.bias_names = [f"{n}_bias" if n else "bias" for n in names]
+        self.parameter_split_sizes = sizes
+
+        # weights first, so they stay adjacent in parameters(); then biases
+        off = 0
+        for name, size in zip(self.weight_names, sizes):
+            self.register_parameter(name, torch.nn.Parameter(weight_buf[off:off + size]), init_fn=init_method,
+                                    get_rng_state_tracker=get_rng_state_tracker)
+            off += size
+        off = 0
+        for name, size in zip(self.bias_names, sizes):
+            if bias:
+                self.register_parameter(name, torch.nn.Parameter(bias_buf[off:off + size]),
+                                        init_fn=init_method_constant(0.0))
+            else:
+                setattr(self, name, torch.empty(0, dtype=params_dtype, device=device))
+            off += size
+
+        self.reset_parameters(defer_init=(device == "meta"))
+        self.weight_qresult_cache = quantization.QuantizeResultCache()
+        # a row-parallel bias can only be added after the collective
+        self.gemm_bias_unfused_add = parallel_mode == "row" and self.apply_bias
+
+    def reset_parameters(self, defer_init=False):
+        super().reset_parameters(defer_init=defer_init)
+        if defer_init:
+            return
+        for name in self.weight_names:
+            set_tensor_model_parallel_attributes(getattr(self, name), True, 1 if self.parallel_mode == "row" else 0, 1)
+        if self.use_bias:
+            for name in self.bias_names:
+                if self.parallel_mode == "row":
+                    getattr(self, name).sequence_parallel = self.sequence_parallel
+                elif self.parallel_mode == "column":
+                    set_tensor_model_parallel_attributes(getattr(self, name), True, 0, 1)
+
+    @torch._dynamo.disable(recursive=True)
+    def forward(self, inp: torch.Tensor, is_first_microbatch: Optional[bool] = None,
+                fp8_output: Optional[bool] = False,
+                inp_meta: Optional[quantization.QuantizeInputMetaBase] = None):
+        """is_first_microbatch: True / False let the layer cache the quantized weight across
+        the microbatches of a step and skip the wgrad accumulation on the first one; None
+        re-quantizes every call."""
+        self.set_activation_dtype(inp)
+        inp = inp.contiguous()
+        assert self.tp_group_initialized, "TP group not initialized"
+        assert inp.dtype in (torch.float32, torch.float16, torch.bfloat16), f"Input dtype {inp.dtype} not supported"
+        assert fp8_output is False, "FP8 output is not supported yet"
+
+        weight = noop_cat([getattr(self, n) for n in self.weight_names])
+        bias = noop_cat([getattr(self, n) for n in self.bias_names]) if self.use_bias else getattr(self, self.bias_names[0])
+
+        fn = _QuantizedLinear if self.qlinear_params.quantize else _NonQuantizedLinear
+        grad = torch.is_grad_enabled()
+        args: List[Any] = [] if grad else [None]
+        args += [inp, inp_meta, weight, self.weight_qresult_cache,
+                 bias if self.apply_bias and not self.gemm_bias_unfused_add else None,
+                 self.sequence_parallel, self.tp_group, self.tp_size, self.parallel_mode, self.qlinear_params,
+                 self.activation_dtype, grad, is_first_microbatch, self.fuse_wgrad_accumulation]
+        out = (fn.apply if grad else fn.forward)(*args)
+        if self.gemm_bias_unfused_add:
+            out = out + cast_if_needed(bias, self.activation_dtype)
+        if self.return_bias:
+            return out, cast_if_needed(bias, self.activation_dtype)
+        return out

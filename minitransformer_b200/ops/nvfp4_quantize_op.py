@@ -1,0 +1,76 @@
+"""NVFP4 backend on the sm_100a kernels.
+
+Takes the place of both reference operators: the native wrapper whose GEMM is a stub
+(miniTransformer/ops/nvfp4_quantize_op.py:97-178) and the PyTorch emulation
+(miniTransformer/ops/nvfp4_quantize_op_ref.py:160-596), whose numerics the kernels
+reproduce (codes, scale bytes and abs-max bit for bit; GEMM within 1e-3 relative
+Frobenius error on the same operands). There is no CPU path.
+"""
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..distributed.distributed import allreduce_max_
+from . import quantization as Q
+
+nvfp4_output_t = torch.uint8
+nvfp4_scale_t = torch.float8_e4m3fn
+
+
+def _as_2d_bf16(x: torch.Tensor) -> torch.Tensor:
+    if x.dim() > 2:
+        x = x.reshape(-1, x.shape[-1])
+    if x.dtype != torch.bfloat16:
+        raise kernels._lib.MtError(
+            f"the sm_100a quantize kernels take bf16 inputs, got {x.dtype}; cast explicitly if that is intended")
+    return x.contiguous()
+
+
+def _swizzled(scale: torch.Tensor, rows: int) -> torch.Tensor:
+    """GEMM-layout copy of a row-major scale tensor: the one attached by quantize() when the
+    same tensor object is passed back, otherwise produced by the swizzle kernel."""
+    swz = getattr(scale, "_mt_swz", None)
+    if swz is not None:
+        return swz
+    return kernels.swizzle_scales(scale.view(torch.uint8), rows)
+
+
+class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
+    @property
+    def supports_allgather(self) -> bool:
+        # Row-wise 1x16 blocks never cross a token shard, so quantizing shards with the
+        # MAX-all-reduced abs-max and gathering codes + scales equals quantizing the gathered
+        # tensor.
+        return True
+
+    def quantize(self, x, qparams, return_transpose=False, reduce_amax=False, tp_group=None, input_meta=None):
+        assert qparams.quant_tile_shape in ((1, 16), (16, 16)), "NVFP4 uses 1x16 or 16x16 tiles"
+        assert not qparams.pow_2_scales, "NVFP4 block scales are E4M3, not powers of two"
+        x = _as_2d_bf16(x)
+        rht = bool(qparams.with_rht) and return_transpose
+        amax_row, amax_col = kernels.amax_bf16(x, with_rht=rht, need_col=return_transpose)
+        if reduce_amax:
+            # both scalars live in one 2-element buffer: one tiny collective
+            allreduce_max_(amax_row._base if amax_row._base is not None else amax_row, tp_group)
+        r = kernels.quantize_nvfp4(x, tile=qparams.quant_tile_shape, with_2d=qparams.with_2d_quantization,
+                                   with_rht=rht, return_transpose=return_transpose,
+                                   amax_row=amax_row, amax_col=amax_col)
+        scale = r.scale.view(nvfp4_scale_t)
+        scale._mt_swz = r.scale_swz
+        scale_t = None
+        if return_transpose:
+            scale_t = r.scale_t.view(nvfp4_scale_t)
+            scale_t._mt_swz = r.scale_t_swz
+        return Q.QuantizeResult(r.data, scale, r.data_t, scale_t, r.amax_row, r.amax_col,
+                                r.scale_swz, r.scale_t_swz)
+
+    def qgemm(self, qx, qw, m_params, out_dtype, sx, sw, bias=None, out=None, accumulate=False,
+              global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):
+        assert global_amax_qx is not None and global_amax_qw is not None, "NVFP4 needs the per-tensor abs-max"
+        if out is not None:
+            assert out.dtype == out_dtype, "output dtype mismatch"
+        M, N = qx.shape[0], qw.shape[0]
+        return kernels.gemm_nvfp4(qx, _swizzled(sx, M), global_amax_qx, qw, _swizzled(sw, N), global_amax_qw,
+                                  out_dtype=out_dtype, out=out, accumulate=accumulate,
+                                  bias=bias if bias is not None and bias.numel() else None)

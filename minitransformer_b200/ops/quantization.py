@@ -1,0 +1,127 @@
+"""Operator interface between the linear modules and a quantize/GEMM implementation.
+
+Mirrors the plugin slot of the reference (miniTransformer/ops/quantization.py:11-182): a
+`QuantizeOpBase` instance sits in `QLinearParams.quantize_op`; the autograd functions call
+its `quantize` and `qgemm`. Names, fields and argument meaning are kept so that existing
+recipes and callers keep working; the implementations behind them are the sm_100a kernels.
+"""
+import dataclasses
+from typing import Optional, Tuple
+
+import torch
+
+from ..utils import utils
+
+
+@dataclasses.dataclass(frozen=True)
+class QParams:
+    """How one tensor is quantized.
+
+    scaling_dtype: dtype of the block scales (float8_e4m3fn for NVFP4, uint8 holding E8M0
+        bytes for MXFP8). output_dtype: container dtype of the codes. eps: unused lower bound
+        on amax. pow_2_scales: block scales are powers of two (MXFP8). quant_tile_shape:
+        (rows, cols) of one scale block. with_2d_quantization: one scale per 16x16 block.
+        with_rht: 16-point randomized Hadamard transform on the transposed copy.
+    """
+    scaling_dtype: Optional[torch.dtype] = None
+    output_dtype: Optional[torch.dtype] = None
+    eps: float = 0.0
+    pow_2_scales: bool = False
+    quant_tile_shape: Optional[Tuple[int, int]] = None
+    with_2d_quantization: bool = False
+    with_rht: bool = False
+
+
+@dataclasses.dataclass(frozen=True)
+class MMParams:
+    out_dtype: Optional[torch.dtype] = None
+    use_split_accumulator: bool = True
+
+
+@dataclasses.dataclass
+class QuantizeResult:
+    """Codes and decode scales of a tensor, optionally also of its transpose, plus the
+    per-tensor abs-max values NVFP4 needs. `scale_swz` / `scale_t_swz` (an addition of this
+    implementation) hold the same scale bytes in the layout the tensor-core GEMM reads."""
+    data: torch.Tensor
+    scale: torch.Tensor
+    data_t: Optional[torch.Tensor] = None
+    scale_t: Optional[torch.Tensor] = None
+    global_amax_row: Optional[torch.Tensor] = None
+    global_amax_col: Optional[torch.Tensor] = None
+    scale_swz: Optional[torch.Tensor] = None
+    scale_t_swz: Optional[torch.Tensor] = None
+
+
+@dataclasses.dataclass
+class QuantizeResultCache:
+    """Quantized weight kept between the microbatches of one step."""
+    data: Optional[torch.Tensor] = None
+    scale: Optional[torch.Tensor] = None
+    data_t: Optional[torch.Tensor] = None
+    scale_t: Optional[torch.Tensor] = None
+    global_amax_row: Optional[torch.Tensor] = None
+    global_amax_col: Optional[torch.Tensor] = None
+    scale_swz: Optional[torch.Tensor] = None
+    scale_t_swz: Optional[torch.Tensor] = None
+
+    def store(self, r: QuantizeResult) -> None:
+        for f in dataclasses.fields(QuantizeResult):
+            setattr(self, f.name, getattr(r, f.name))
+
+    def to_qresult(self) -> QuantizeResult:
+        assert self.data is not None and self.scale is not None, "weight cache is empty"
+        return QuantizeResult(**{f.name: getattr(self, f.name) for f in dataclasses.fields(QuantizeResult)})
+
+
+@dataclasses.dataclass
+class QuantizeInputMetaBase:
+    """Side information about a quantize input (e.g. an abs-max computed by the producer)."""
+    amax: Optional[torch.Tensor] = None
+
+
+class QuantizeOpBase:
+    """Interface of a quantize + GEMM backend."""
+
+    def quantize(self, x: torch.Tensor, qparams: QParams, return_transpose: bool = False,
+                 reduce_amax: bool = False, tp_group=None,
+                 input_meta: Optional[QuantizeInputMetaBase] = None) -> QuantizeResult:
+        raise NotImplementedError
+
+    def qgemm(self, qx: torch.Tensor, qw: torch.Tensor, m_params: MMParams, out_dtype: torch.dtype,
+              sx: torch.Tensor, sw: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              out: Optional[torch.Tensor] = None, accumulate: bool = False,
+              global_amax_qx: Optional[torch.Tensor] = None, global_amax_qw: Optional[torch.Tensor] = None,
+              qparams_x: Optional[QParams] = None, qparams_w: Optional[QParams] = None) -> torch.Tensor:
+        """y[M,N] = qx[M,K] . qw[N,K]^T (+ bias); with accumulate the result is added into
+        `out` in place and `out` is returned."""
+        raise NotImplementedError
+
+    @property
+    def supports_allgather(self) -> bool:
+        """True if a token-sharded input may be quantized per shard and the quantized shards
+        all-gathered (bit-identical to quantizing the gathered tensor)."""
+        raise NotImplementedError
+
+
+class QuantizeOpNonQuantize(QuantizeOpBase):
+    """Pass-through backend: keeps tensors in high precision and multiplies with torch."""
+
+    @property
+    def supports_allgather(self) -> bool:
+        return False
+
+    def quantize(self, x, qparams, return_transpose=False, reduce_amax=False, tp_group=None, input_meta=None):
+        assert x.dtype in utils.HIGH_PRECISION_FLOAT_DTYPES and not reduce_amax
+        qx = x if qparams.output_dtype is None else x.to(qparams.output_dtype)
+        empty = torch.empty(0, device=x.device)
+        return QuantizeResult(qx, empty, qx.t() if return_transpose else None, empty if return_transpose else None)
+
+    def qgemm(self, qx, qw, m_params, out_dtype, sx, sw, bias=None, out=None, accumulate=False,
+              global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):
+        y = torch.nn.functional.linear(qx, qw, bias if bias is not None and bias.numel() else None)
+        if accumulate:
+            assert out is not None
+            out.add_(y)
+            return out
+        return y.to(out_dtype) if y.dtype != out_dtype else y

@@ -38,3 +38,10 @@ def swizzle_scales_ref(s: np.ndarray, rows: int) -> np.ndarray:
 def mismatch(a: np.ndarray, b: np.ndarray) -> int:
     assert a.shape == b.shape, (a.shape, b.shape)
     return int((a != b).sum())
+
+
+def unswizzle_scales_ref(swz: np.ndarray, rows: int, k_blocks: int) -> np.ndarray:
+    """Inverse of swizzle_scales_ref restricted to the valid [rows, k_blocks] region."""
+    rb, kc = (rows + 127) // 128, padded_chunks(k_blocks)
+    v = swz.reshape(rb, kc, 32, 4, 4).transpose(0, 3, 2, 1, 4)
+    return np.ascontiguousarray(v).reshape(rb * 128, kc * 4)[:rows, :k_blocks]

@@ -1,0 +1,50 @@
+"""CPU-side checks of the drop-in boundary: the shared library loads and exports every
+function the public header declares, and argument validation fails loudly without a GPU."""
+import ctypes
+import os
+
+import pytest
+
+from minitransformer_b200 import _lib
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _lib.declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/mt_b200.h but not exported"
+    assert set(names) == set(_lib._SIGNATURES), "ctypes signatures out of sync with the header"
+    assert lib.mt_version() >= 100
+
+
+def test_swizzled_scale_bytes():
+    lib = _lib.load()
+    assert lib.mt_swizzled_scale_bytes(128, 4) == 4 * 512      # one chunk, padded to four
+    assert lib.mt_swizzled_scale_bytes(8192, 256) == 64 * 64 * 512
+    assert lib.mt_swizzled_scale_bytes(130, 17) == 2 * 8 * 512
+
+
+def test_invalid_arguments_are_rejected_with_a_message():
+    lib = _lib.load()
+    rc = lib.mt_quantize_nvfp4(None, 16, 16, 0, None, None, None, None, 1, None, None, None, 1, None, None)
+    assert rc == -1
+    assert b"null" in lib.mt_last_error_string()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p = (p + 15) // 16 * 16
+    rc = lib.mt_quantize_nvfp4(p, 16, 24, 0, p, p, p, p, 1, None, None, None, 1, None, None)
+    assert rc == -1 and b"multiple of 16" in lib.mt_last_error_string()
+    rc = lib.mt_gemm_nvfp4(p, p, p, p, p, p, 128, 128, 40, p, 0, 128, None, 0, 0, None)
+    assert rc == -1 and b"multiple of 32" in lib.mt_last_error_string()
+    rc = lib.mt_gemm_mxfp8(p, p, p, p, 128, 128, 64, p, 7, 128, None, 0, 0, None)
+    assert rc == -1 and b"dtype" in lib.mt_last_error_string()
+    with pytest.raises(_lib.MtError):
+        _lib.call("mt_swizzle_scales", None, 1, 1, 1, None, None)
+
+
+def test_front_end_refuses_cpu_tensors():
+    import torch
+    from minitransformer_b200 import kernels
+    with pytest.raises(_lib.MtError):
+        kernels.quantize_nvfp4(torch.zeros(16, 16, dtype=torch.bfloat16))

@@ -1,0 +1,143 @@
+"""GPU parity of the tcgen05 block-scaled GEMM kernels through the C ABI: relative
+Frobenius error <= 1e-3 (the stated tolerance) against the oracle GEMM on the SAME
+quantized operands; at full configuration sizes against the CUDA-core checker."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_bits_to_f32
+from helpers import from_bits, seeded_bf16
+from minitransformer_b200 import kernels as K
+from oracle import formats as F, gemm, mxfp8, nvfp4
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3  # relative Frobenius error against the reference GEMM on identical operands
+
+
+def _operands_nvfp4(M, N, Kd, seed=1):
+    ta, a = seeded_bf16((M, Kd), seed)
+    tb, b = seeded_bf16((N, Kd), seed + 1, 0.02)
+    return (nvfp4.quantize(a, return_transpose=False), nvfp4.quantize(b, return_transpose=False),
+            K.quantize_nvfp4(ta.cuda(), return_transpose=False), K.quantize_nvfp4(tb.cuda(), return_transpose=False))
+
+
+def _operands_mxfp8(M, N, Kd, seed=1):
+    ta, a = seeded_bf16((M, Kd), seed)
+    tb, b = seeded_bf16((N, Kd), seed + 1, 0.02)
+    return (mxfp8.quantize(a, return_transpose=False), mxfp8.quantize(b, return_transpose=False),
+            K.quantize_mxfp8(ta.cuda(), return_transpose=False), K.quantize_mxfp8(tb.cuda(), return_transpose=False))
+
+
+SHAPES = [(128, 128, 256), (128, 256, 256), (128, 128, 32), (256, 512, 1024), (100, 72, 96), (384, 640, 2048),
+          (1, 8, 64), (129, 257, 288), (512, 128, 4096)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_nvfp4_matches_oracle(shape, out_dtype):
+    M, N, Kd = shape
+    oa, ob, ra, rb = _operands_nvfp4(M, N, Kd)
+    ref = gemm.qgemm_nvfp4(oa["data"], oa["scale"], oa["amax_row"], ob["data"], ob["scale"], ob["amax_row"],
+                           out_bf16=out_dtype == torch.bfloat16, fused=M * N * Kd > 5e7)
+    y = K.gemm_nvfp4(ra.data, ra.scale_swz, ra.amax_row, rb.data, rb.scale_swz, rb.amax_row, out_dtype=out_dtype)
+    assert gemm.rel_frobenius(y.float().cpu().numpy(), ref) <= TOL
+    chk = K.gemm_nvfp4(ra.data, None, ra.amax_row, rb.data, None, rb.amax_row, out_dtype=out_dtype,
+                       check_kernel=True, sa_lin=ra.scale, sb_lin=rb.scale)
+    assert gemm.rel_frobenius(chk.float().cpu().numpy(), ref) <= TOL
+    assert K.read_device_status() == 0
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_mxfp8_matches_oracle(shape):
+    M, N, Kd = shape
+    Kd = max(32, Kd // 32 * 32)
+    oa, ob, ra, rb = _operands_mxfp8(M, N, Kd)
+    ref = gemm.qgemm_mxfp8(oa["data"], oa["scale"], ob["data"], ob["scale"], out_bf16=False, fused=M * N * Kd > 5e7)
+    y = K.gemm_mxfp8(ra.data, ra.scale_swz, rb.data, rb.scale_swz, out_dtype=torch.float32)
+    assert gemm.rel_frobenius(y.cpu().numpy(), ref) <= TOL
+    chk = K.gemm_mxfp8(ra.data, None, rb.data, None, out_dtype=torch.float32, check_kernel=True,
+                       sa_lin=ra.scale, sb_lin=rb.scale)
+    assert gemm.rel_frobenius(chk.cpu().numpy(), ref) <= TOL
+    assert K.read_device_status() == 0
+
+
+def test_gemm_matches_reference_fixture(golden_nvfp4_linear):
+    """Operands quantized on the GPU from the fixture inputs, GEMM against the reference's own
+    qgemm output stored in the fixture."""
+    g = golden_nvfp4_linear
+    for tag in ("a", "b"):
+        x, w = from_bits(g[f"{tag}/x"]).cuda(), from_bits(g[f"{tag}/w"]).cuda()
+        rx = K.quantize_nvfp4(x, with_rht=True)
+        rw = K.quantize_nvfp4(w, tile=(16, 16))
+        y = K.gemm_nvfp4(rx.data, rx.scale_swz, rx.amax_row, rw.data, rw.scale_swz, rw.amax_row)
+        ref = bf16_bits_to_f32(g[f"{tag}/gemm_y"])
+        assert gemm.rel_frobenius(y.float().cpu().numpy(), ref) <= TOL
+        acc = torch.from_numpy(g[f"{tag}/acc_in"]).cuda()
+        K.gemm_nvfp4(rx.data, rx.scale_swz, rx.amax_row, rw.data, rw.scale_swz, rw.amax_row,
+                     out_dtype=torch.float32, out=acc, accumulate=True)
+        assert gemm.rel_frobenius(acc.cpu().numpy(), g[f"{tag}/acc_out"]) <= TOL
+
+
+def test_gemm_accumulate_bias_and_strided_output():
+    M, N, Kd = 256, 384, 512
+    oa, ob, ra, rb = _operands_nvfp4(M, N, Kd, seed=11)
+    base = gemm.qgemm_nvfp4(oa["data"], oa["scale"], oa["amax_row"], ob["data"], ob["scale"], ob["amax_row"],
+                            out_bf16=False)
+    g = torch.Generator().manual_seed(5)
+    prev = torch.randn(M, N, generator=g)
+    bias = torch.randn(N, generator=g)
+    out = prev.clone().cuda()
+    K.gemm_nvfp4(ra.data, ra.scale_swz, ra.amax_row, rb.data, rb.scale_swz, rb.amax_row, out_dtype=torch.float32,
+                 out=out, accumulate=True)
+    assert gemm.rel_frobenius(out.cpu().numpy(), prev.numpy() + base) <= TOL
+    y = K.gemm_nvfp4(ra.data, ra.scale_swz, ra.amax_row, rb.data, rb.scale_swz, rb.amax_row,
+                     out_dtype=torch.float32, bias=bias.cuda())
+    assert gemm.rel_frobenius(y.cpu().numpy(), base + bias.numpy()[None, :]) <= TOL
+    # bf16 accumulate into a view with a row stride larger than N
+    big = torch.zeros(M, N + 64, dtype=torch.bfloat16, device="cuda")
+    view = big[:, :N]
+    view.copy_(prev.to(torch.bfloat16))
+    K.gemm_nvfp4(ra.data, ra.scale_swz, ra.amax_row, rb.data, rb.scale_swz, rb.amax_row, out=view, accumulate=True)
+    exp = F.bf16_round(F.bf16_round(prev.numpy()) + base)
+    assert gemm.rel_frobenius(view.float().cpu().numpy(), exp) <= 4e-3  # one bf16 ulp of slack
+    assert float(big[:, N:].abs().max()) == 0.0
+
+
+def test_gemm_zero_k_and_zero_operands():
+    a = torch.zeros(128, 0, dtype=torch.uint8, device="cuda")
+    one = torch.ones(1, device="cuda")
+    y = torch.full((128, 64), 7.0, device="cuda")
+    K.gemm_nvfp4(a, a, one, a[:64], a, one, out_dtype=torch.float32, out=y)
+    assert float(y.abs().max()) == 0.0
+    x = torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda")
+    r = K.quantize_nvfp4(x, return_transpose=False)
+    y = K.gemm_nvfp4(r.data, r.scale_swz, r.amax_row, r.data, r.scale_swz, r.amax_row, out_dtype=torch.float32)
+    assert float(y.abs().max()) == 0.0 and not bool(torch.isnan(y).any())
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp8"])
+def test_gemm_full_size_against_device_checker(fmt):
+    """Configuration 2 forward GEMM (8192 x 14336 x 4096): the tensor-core kernel against the
+    CUDA-core checker, which itself is pinned to the oracle at small sizes above."""
+    M, N, Kd = 8192, 14336, 4096
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(M, Kd, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    if fmt == "nvfp4":
+        ra, rb = K.quantize_nvfp4(x, return_transpose=False), K.quantize_nvfp4(w, return_transpose=False)
+        y = K.gemm_nvfp4(ra.data, ra.scale_swz, ra.amax_row, rb.data, rb.scale_swz, rb.amax_row, out_dtype=torch.float32)
+        c = K.gemm_nvfp4(ra.data, None, ra.amax_row, rb.data, None, rb.amax_row, out_dtype=torch.float32,
+                         check_kernel=True, sa_lin=ra.scale, sb_lin=rb.scale)
+    else:
+        ra, rb = K.quantize_mxfp8(x, return_transpose=False), K.quantize_mxfp8(w, return_transpose=False)
+        y = K.gemm_mxfp8(ra.data, ra.scale_swz, rb.data, rb.scale_swz, out_dtype=torch.float32)
+        c = K.gemm_mxfp8(ra.data, None, rb.data, None, out_dtype=torch.float32, check_kernel=True,
+                         sa_lin=ra.scale, sb_lin=rb.scale)
+    assert float((y - c).norm() / c.norm()) <= TOL
+    # linearity in the per-tensor scale (NVFP4): doubling amax_a doubles the output
+    if fmt == "nvfp4":
+        y2 = K.gemm_nvfp4(ra.data, ra.scale_swz, ra.amax_row * 2, rb.data, rb.scale_swz, rb.amax_row,
+                          out_dtype=torch.float32)
+        assert torch.equal(y2, y * 2)
+    assert K.read_device_status() == 0
