@@ -66,10 +66,11 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
     const float enc = exp2_neg(e);
     uint4 out[2];
     uint32_t* o = reinterpret_cast<uint32_t*>(out);
+    const f32x2_t enc2 = pack2(enc, enc);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      o[2 * i] = e4m3x4(bf16_lo(w[i].x), bf16_hi(w[i].x), bf16_lo(w[i].y), bf16_hi(w[i].y), enc);
-      o[2 * i + 1] = e4m3x4(bf16_lo(w[i].z), bf16_hi(w[i].z), bf16_lo(w[i].w), bf16_hi(w[i].w), enc);
+      o[2 * i] = e4m3x4_from_words(w[i].x, w[i].y, enc2);
+      o[2 * i + 1] = e4m3x4_from_words(w[i].z, w[i].w, enc2);
     }
     const int64_t gr = m0 + r, gc = k0 + b * 32;
     if (gr < a.rows && gc < a.cols) {
@@ -91,28 +92,22 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
     for (int j = 0; j < 32; ++j) w[j] = *reinterpret_cast<const uint32_t*>(&sm.in[grp * 32 + j][cbase]);
     uint32_t m = 0;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) m = absmax2(m, w[j]);  // still per-lane-half: lo = column 0, hi = column 1
-    // absmax2(0, w) leaves |w|; the two halves are the two columns' abs-max
-    const float amax0 = bf16_lo(m), amax1 = bf16_hi(m);
+    for (int j = 0; j < 32; ++j) m = absmax2(m, w[j]);
+    // the two halves of the accumulator are the two columns' abs-max
+    const int e0 = e8m0_exponent(absmax2_lo(m)), e1 = e8m0_exponent(absmax2_hi(m));
+    const f32x2_t enc2 = pack2(exp2_neg(e0), exp2_neg(e1));
+    uint4 out_lo[2], out_hi[2];
+    uint32_t* ol = reinterpret_cast<uint32_t*>(out_lo);
+    uint32_t* oh = reinterpret_cast<uint32_t*>(out_hi);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) e4m3x4_two_columns(&w[4 * i], enc2, ol[i], oh[i]);
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      const int e = e8m0_exponent(c ? amax1 : amax0);
-      const float enc = exp2_neg(e);
-      uint4 out[2];
-      uint32_t* o = reinterpret_cast<uint32_t*>(out);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float f0 = c ? bf16_hi(w[4 * i]) : bf16_lo(w[4 * i]);
-        float f1 = c ? bf16_hi(w[4 * i + 1]) : bf16_lo(w[4 * i + 1]);
-        float f2 = c ? bf16_hi(w[4 * i + 2]) : bf16_lo(w[4 * i + 2]);
-        float f3 = c ? bf16_hi(w[4 * i + 3]) : bf16_lo(w[4 * i + 3]);
-        o[i] = e4m3x4(f0, f1, f2, f3, enc);
-      }
       const int col = cbase + c;
       const int swz = (col >> 1) & 7;
-      *reinterpret_cast<uint4*>(&sm.out_t[col][((2 * grp) ^ swz) * 16]) = out[0];
-      *reinterpret_cast<uint4*>(&sm.out_t[col][((2 * grp + 1) ^ swz) * 16]) = out[1];
-      const uint8_t sbyte = static_cast<uint8_t>(e + 127);
+      *reinterpret_cast<uint4*>(&sm.out_t[col][((2 * grp) ^ swz) * 16]) = c ? out_hi[0] : out_lo[0];
+      *reinterpret_cast<uint4*>(&sm.out_t[col][((2 * grp + 1) ^ swz) * 16]) = c ? out_hi[1] : out_lo[1];
+      const uint8_t sbyte = static_cast<uint8_t>((c ? e1 : e0) + 127);
       sm.st_lin[col][grp] = sbyte;
       sm.st_swz[sf_chunk_offset(col, grp)] = sbyte;
     }

@@ -21,6 +21,8 @@ struct __align__(128) Nvfp4Smem {
   uint8_t st_lin[QT_COLS][8];            // column-wise scales, row-major ([feature][token block])
   uint8_t st_swz[2][512];
   float blk_amax[8][8];                  // 16x16 block abs-max (2-D mode)
+  float lut_row[128];                    // element factor per scale byte, row-wise copy
+  float lut_col[128];                    // same for the transposed copy (its own per-tensor scale)
   uint64_t bar;
   int abort_flag;
 };
@@ -56,25 +58,23 @@ __global__ void __launch_bounds__(256) amax_rht_kernel(const uint16_t* __restric
   const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS + warp * 16;
   float frow = 0.f, fcol = 0.f;
   if (c0 < cols && r0 < rows) {  // rows % 16 == 0, cols % 4 == 0: the strip is all-in or all-out
-    uint2 w[16];
+    uint32_t wa[16], wb[16];   // columns (c0, c0+1) and (c0+2, c0+3), one packed word per row
 #pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = __ldg(reinterpret_cast<const uint2*>(x + (r0 + j) * cols + c0));
+    for (int j = 0; j < 16; ++j) {
+      const uint2 t = __ldg(reinterpret_cast<const uint2*>(x + (r0 + j) * cols + c0));
+      wa[j] = t.x;
+      wb[j] = t.y;
+    }
     uint32_t m = 0;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) m = absmax2(m, absmax2(w[j].x, w[j].y));
+    for (int j = 0; j < 16; ++j) m = absmax2(absmax2(m, wa[j]), wb[j]);
     frow = absmax2_to_float(m);
+    rht16_x2(wa);
+    rht16_x2(wb);
+    m = 0;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        uint32_t word = (c < 2) ? w[j].x : w[j].y;
-        v[j] = (c & 1) ? bf16_hi(word) : bf16_lo(word);
-      }
-      rht16(v);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) fcol = fmaxf(fcol, fabsf(v[j]));
-    }
+    for (int j = 0; j < 16; ++j) m = absmax2(absmax2(m, wa[j]), wb[j]);
+    fcol = absmax2_to_float(m);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -131,6 +131,12 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
   }
   const Nvfp4Global g_row = nvfp4_global(*a.amax_row);
   const Nvfp4Global g_col = kTranspose ? nvfp4_global(*a.amax_col) : g_row;
+  const bool fuse_row = nvfp4_can_fuse_scaling(*a.amax_row);
+  const bool fuse_col = kTranspose ? nvfp4_can_fuse_scaling(*a.amax_col) : fuse_row;
+  // element-factor tables (one entry per non-negative E4M3 scale byte), filled while the tile loads
+  if (tid < 128) sm.lut_row[tid] = nvfp4_encode_for_byte(tid, g_row);
+  else if (kTranspose) sm.lut_col[tid - 128] = nvfp4_encode_for_byte(tid - 128, g_col);
+  __syncthreads();
 
   const bool ok = mbar_wait_bounded(&sm.bar, 0, &sm.abort_flag, a.status, DS_QUANT_WAIT);
   if (!ok) return;  // no copy of ours can still be in flight only if it never started; status is raised
@@ -164,60 +170,61 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
     if (k2D) {
       vmax = sm.blk_amax[r >> 4][b];
     } else {
-      uint32_t m = absmax2(absmax2(absmax2(w0.x, w0.y), absmax2(w0.z, w0.w)),
-                           absmax2(absmax2(w1.x, w1.y), absmax2(w1.z, w1.w)));
+      const uint32_t m = absmax2(absmax2(absmax2(w0.x, w0.y), absmax2(w0.z, w0.w)),
+                                 absmax2(absmax2(w1.x, w1.y), absmax2(w1.z, w1.w)));
       vmax = absmax2_to_float(m);
     }
-    uint8_t sbyte;
+    uint32_t sbyte;
     float enc;
-    nvfp4_block_scale(vmax, g_row, sbyte, enc);
-    float v[16];
-    const uint32_t ws[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { v[2 * i] = bf16_lo(ws[i]); v[2 * i + 1] = bf16_hi(ws[i]); }
+    nvfp4_block_scale_lut(vmax, g_row.ges, sm.lut_row, sbyte, enc);
     uint2 codes;
-    codes.x = e2m1x8(v, enc);
-    codes.y = e2m1x8(v + 8, enc);
+    codes.x = e2m1x8_from_words(w0.x, w0.y, w0.z, w0.w, enc, fuse_row);
+    codes.y = e2m1x8_from_words(w1.x, w1.y, w1.z, w1.w, enc, fuse_row);
     const int64_t gr = m0 + r, gc = k0 + b * 16;
     if (gr < a.rows && gc < a.cols)
       *reinterpret_cast<uint2*>(a.q + gr * (a.cols >> 1) + (gc >> 1)) = codes;
-    sm.s_lin[r][b] = sbyte;
-    sm.s_swz[b >> 2][sf_chunk_offset(r, b)] = sbyte;
+    sm.s_lin[r][b] = static_cast<uint8_t>(sbyte);
+    sm.s_swz[b >> 2][sf_chunk_offset(r, b)] = static_cast<uint8_t>(sbyte);
   }
 
   // ---- column pass: lane <-> 4 adjacent columns, warp <-> 16 rows ----
   if (kTranspose) {
-    uint2 w[16];
+    uint32_t wp[2][16];   // wp[p][j]: row j of column pair p (columns 4*lane + 2p, + 2p + 1)
 #pragma unroll
-    for (int j = 0; j < 16; ++j) w[j] = *reinterpret_cast<const uint2*>(&sm.in[warp * 16 + j][lane * 4]);
+    for (int j = 0; j < 16; ++j) {
+      const uint2 t = *reinterpret_cast<const uint2*>(&sm.in[warp * 16 + j][lane * 4]);
+      wp[0][j] = t.x;
+      wp[1][j] = t.y;
+    }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float v[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        uint32_t word = (c < 2) ? w[j].x : w[j].y;
-        v[j] = (c & 1) ? bf16_hi(word) : bf16_lo(word);
-      }
-      if (kRHT) rht16(v);
-      float vmax;
+    for (int p = 0; p < 2; ++p) {
+      if (kRHT) rht16_x2(wp[p]);
+      float vmax_lo, vmax_hi;
       if (k2D) {
-        vmax = sm.blk_amax[warp][lane >> 2];
+        vmax_lo = vmax_hi = sm.blk_amax[warp][lane >> 2];
       } else {
-        vmax = 0.f;
+        uint32_t m = 0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
+        for (int j = 0; j < 16; ++j) m = absmax2(m, wp[p][j]);
+        vmax_lo = absmax2_lo(m);
+        vmax_hi = absmax2_hi(m);
       }
-      uint8_t sbyte;
-      float enc;
-      nvfp4_block_scale(vmax, g_col, sbyte, enc);
-      uint2 codes;
-      codes.x = e2m1x8(v, enc);
-      codes.y = e2m1x8(v + 8, enc);
-      const int col = lane * 4 + c;
+      uint32_t sb_lo, sb_hi;
+      float enc_lo, enc_hi;
+      nvfp4_block_scale_lut(vmax_lo, g_col.ges, sm.lut_col, sb_lo, enc_lo);
+      nvfp4_block_scale_lut(vmax_hi, g_col.ges, sm.lut_col, sb_hi, enc_hi);
+      const f32x2_t enc2 = pack2(enc_lo, enc_hi);
+      uint2 c_lo, c_hi;
+      e2m1x8_two_columns(&wp[p][0], enc2, fuse_col, c_lo.x, c_hi.x);
+      e2m1x8_two_columns(&wp[p][8], enc2, fuse_col, c_lo.y, c_hi.y);
+      const int col = lane * 4 + 2 * p;
       const int slot = warp ^ (lane & 7);
-      *reinterpret_cast<uint2*>(&sm.out_t[col][slot * 8]) = codes;
-      sm.st_lin[col][warp] = sbyte;
-      sm.st_swz[warp >> 2][sf_chunk_offset(col, warp)] = sbyte;
+      *reinterpret_cast<uint2*>(&sm.out_t[col][slot * 8]) = c_lo;
+      *reinterpret_cast<uint2*>(&sm.out_t[col + 1][slot * 8]) = c_hi;
+      sm.st_lin[col][warp] = static_cast<uint8_t>(sb_lo);
+      sm.st_lin[col + 1][warp] = static_cast<uint8_t>(sb_hi);
+      sm.st_swz[warp >> 2][sf_chunk_offset(col, warp)] = static_cast<uint8_t>(sb_lo);
+      sm.st_swz[warp >> 2][sf_chunk_offset(col + 1, warp)] = static_cast<uint8_t>(sb_hi);
     }
   }
   __syncthreads();
