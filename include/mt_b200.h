@@ -131,6 +131,52 @@ int mt_gemm_mxfp8_check(const uint8_t* a, const uint8_t* sa, int64_t sa_stride,
                         int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
                         int accumulate, mt_stream_t stream);
 
+/* ---- Grouped (per-expert) MXFP8 path behind GroupedLinear ----
+ * Rows of the activation matrix are split into G consecutive groups by the host array
+ * m_offsets_host[G+1] (m_offsets_host[0] = 0, m_offsets_host[G] = rows; empty groups allowed);
+ * group g multiplies with its own weight. Replaces the calls the reference's GroupedLinear
+ * makes into modules that do not exist in its tree: grouped_qgemm
+ * (miniTransformer/module/group_linear.py:108-119, 198-209), grouped_transpose_quantize
+ * (:231-236) and cutlass_grouped_gemm_1d1d (:238-243).
+ * `scratch` is caller-owned device memory of at least mt_grouped_scratch_bytes(rows, G)
+ * bytes; the entry points copy small tile tables into it (the copy from pageable host
+ * memory makes these calls synchronise with the stream). */
+int64_t mt_grouped_scratch_bytes(int64_t rows, int64_t groups);
+
+/* Token offsets of the groups after padding every group to a multiple of 128 tokens.
+ * Writes G+1 values to pad_offsets_out (may be null) and returns the padded total. */
+int64_t mt_grouped_padded_rows(const int64_t* m_offsets_host, int64_t G, int64_t* pad_offsets_out);
+
+/* Transposed MXFP8 quantization with per-group blocks: q_t[cols, Rp] holds x^T with group g's
+ * tokens at columns pad_offset[g].., zero-padded to 128; 1x32 blocks start at each group's
+ * first token, so no block mixes two groups. s_t (optional, row-major [cols, Rp/32], stride
+ * s_t_stride) and s_t_swz (GEMM layout, mt_swizzled_scale_bytes(cols, Rp/32) bytes). */
+int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
+                                        const int64_t* m_offsets_host, int64_t G,
+                                        uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                                        void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+
+/* D[rows of g, 0:N] = A[rows of g, 0:K] . B_g^T for every group g. A, D and sa_swz use the
+ * plain (unpadded) row numbering. B is one matrix of b_rows rows of ldb bytes; group g uses
+ * its rows [g*b_group_rows, +N) and contraction bytes [g*b_group_k, +K):
+ *   forward: B = stacked weights [G*N, K]          -> b_group_rows = N, b_group_k = 0
+ *   dgrad:   B = transposed stacked weights [N, G*K] -> b_group_rows = 0, b_group_k = K
+ * N and K must be multiples of 128. */
+int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
+                          int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G,
+                          int64_t N, int64_t K, int64_t b_group_rows, int64_t b_group_k,
+                          void* d, int d_dtype, int64_t ldd,
+                          void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+
+/* Per-group weight gradients: D_g[N_out, K_out] (+)= A_t[:, cols_g] . B_t[:, cols_g]^T with
+ * cols_g = [pad_offsets_host[g], pad_offsets_host[g+1]) of the padded token axis (outputs of
+ * mt_grouped_transpose_quantize_mxfp8 on dy and x). The G outputs are stored back to back;
+ * an empty group yields zeros. */
+int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const uint8_t* b_t, const uint8_t* sb_t_swz,
+                           const int64_t* pad_offsets_host, int64_t G, int64_t N_out, int64_t K_out,
+                           void* d, int d_dtype, int accumulate,
+                           void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+
 /* Reads and clears the device-side status word the kernels raise when a bounded wait
  * expires (0 = clean). Synchronises the given stream. */
 int mt_read_device_status(int* status_out, mt_stream_t stream);

@@ -28,6 +28,12 @@ _SIGNATURES = {
     "mt_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
     "mt_gemm_nvfp4_check": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
     "mt_gemm_mxfp8_check": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
+    "mt_grouped_scratch_bytes": (_i64, [_i64, _i64]),
+    "mt_grouped_padded_rows": (_i64, [_c.POINTER(_i64), _i64, _c.POINTER(_i64)]),
+    "mt_grouped_transpose_quantize_mxfp8": (_int, [_vp, _i64, _i64, _c.POINTER(_i64), _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
+    "mt_grouped_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _c.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
+                                     _vp, _int, _i64, _vp, _i64, _vp]),
+    "mt_grouped_wgrad_mxfp8": (_int, [_vp, _vp, _vp, _vp, _c.POINTER(_i64), _i64, _i64, _i64, _vp, _int, _int, _vp, _i64, _vp]),
     "mt_read_device_status": (_int, [_c.POINTER(_int), _vp]),
 }
 

@@ -17,6 +17,7 @@
 // The grouped variants reuse the same kernel: a tile is described by (group, m block,
 // n block) and the operand / output bases are looked up per group.
 #include <algorithm>
+#include <vector>
 
 #include "mt_common.cuh"
 
@@ -29,8 +30,6 @@ constexpr int G_TMEM_COLS = 512;
 
 enum GemmFormat : int { FMT_NVFP4 = 0, FMT_MXFP8 = 1 };
 enum GemmMode : int { MODE_DENSE = 0, MODE_GROUPED_ROWS = 1, MODE_GROUPED_K = 2 };
-
-constexpr int kMaxGroups = 256;
 
 struct GemmArgs {
   // operands
@@ -54,12 +53,13 @@ struct GemmArgs {
   // grouping
   int mode;
   int num_groups;
-  const int64_t* group_offsets;  // device int64[G+1]: row (MODE_GROUPED_ROWS) or K-element
-                                 // (MODE_GROUPED_K) offsets, multiples of 128
-  const int32_t* tile_group;     // device int32[num_tiles]  (grouped modes)
-  const int32_t* tile_mblk;      // device int32[num_tiles]: m block inside the group (rows mode)
-  int64_t b_group_rows;          // rows of B per group (MODE_GROUPED_ROWS): N
-  int64_t d_group_stride;        // elements between consecutive group outputs (MODE_GROUPED_K)
+  const int64_t* group_offsets;  // device int64[G+1]: row offsets (MODE_GROUPED_ROWS, any values) or
+                                 // contraction-element offsets (MODE_GROUPED_K, multiples of 128)
+  const int32_t* tile_rb;        // MODE_GROUPED_ROWS: 128-row block of A / D handled by entry i
+  const int32_t* tile_group;     // MODE_GROUPED_ROWS: group of entry i
+  int64_t b_group_rows;          // MODE_GROUPED_ROWS: rows of B to skip per group
+  int64_t b_group_k_bytes;       // MODE_GROUPED_ROWS: contraction bytes of B to skip per group
+  int64_t d_group_stride;        // MODE_GROUPED_K: elements between consecutive group outputs
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
 };
@@ -184,14 +184,17 @@ __device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_
 struct TileCoord {
   int64_t a_row0;      // first row of the A tile (TMA y coordinate)
   int64_t b_row0;      // first row of the B tile
-  int64_t k_byte0;     // first K byte (TMA x coordinate) of the contraction range
+  int64_t a_k_byte0;   // first contraction byte (TMA x coordinate) in A
+  int64_t b_k_byte0;   // first contraction byte in B
   int num_k;           // K steps of 128 bytes
   int64_t sfa_rb;      // 128-row block index into sa
   int64_t sfb_rb;      // 128-row block index into sb (first half)
-  int64_t sf_kc0;      // first chunk index along K in sa / sb
-  int64_t d_row0;      // first output row
+  int64_t sfa_kc0;     // first chunk index along K in sa
+  int64_t sfb_kc0;     // first chunk index along K in sb
+  int64_t d_row0;      // output row of accumulator row 0
+  int64_t d_row_lo;    // rows outside [d_row_lo, d_row_hi) are not stored
+  int64_t d_row_hi;
   int64_t d_col0;      // first output column
-  int64_t d_rows_end;  // exclusive bound on output rows for this tile's group
   int64_t d_base;      // element offset of the group's output matrix
 };
 
@@ -199,49 +202,51 @@ template <int kFormat, int BLOCK_N>
 __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int tile) {
   constexpr int CH = (kFormat == FMT_NVFP4) ? 4 : 1;
   TileCoord t;
-  const int nb = tile / a.tiles_m;
-  int mb = tile - nb * a.tiles_m;
-  t.k_byte0 = 0;
+  t.a_k_byte0 = t.b_k_byte0 = 0;
   t.num_k = (int)((a.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB);
-  t.sf_kc0 = 0;
+  t.sfa_kc0 = t.sfb_kc0 = 0;
   t.d_base = 0;
   if (a.mode == MODE_DENSE) {
+    const int nb = tile / a.tiles_m, mb = tile - nb * a.tiles_m;
     t.a_row0 = (int64_t)mb * G_BLOCK_M;
     t.b_row0 = (int64_t)nb * BLOCK_N;
     t.d_row0 = t.a_row0;
-    t.d_rows_end = a.M;
+    t.d_row_lo = 0;
+    t.d_row_hi = a.M;
+    t.d_col0 = t.b_row0;
   } else if (a.mode == MODE_GROUPED_ROWS) {
-    // tiles are enumerated n-block major over a flattened list of (group, m block)
-    const int g = a.tile_group[mb];
-    const int64_t g0 = a.group_offsets[g];
-    t.a_row0 = g0 + (int64_t)a.tile_mblk[mb] * G_BLOCK_M;
+    // entries (row block, group) for every group that owns rows of the block; n-block major
+    const int nb = tile / a.tiles_m, e = tile - nb * a.tiles_m;
+    const int g = a.tile_group[e];
+    t.a_row0 = (int64_t)a.tile_rb[e] * G_BLOCK_M;
     t.b_row0 = (int64_t)g * a.b_group_rows + (int64_t)nb * BLOCK_N;
+    t.b_k_byte0 = (int64_t)g * a.b_group_k_bytes;
+    t.sfb_kc0 = t.b_k_byte0 / G_BLOCK_KB * CH;
     t.d_row0 = t.a_row0;
-    t.d_rows_end = a.group_offsets[g + 1];
+    t.d_row_lo = a.group_offsets[g];
+    t.d_row_hi = a.group_offsets[g + 1];
+    t.d_col0 = (int64_t)nb * BLOCK_N;
   } else {
-    // MODE_GROUPED_K: tile index = ((g * tiles_n) + nb) * tiles_m + mb, regrouped by the caller
+    // MODE_GROUPED_K: tile = (g * tiles_n + nb) * tiles_m + mb; group g contracts over its own
+    // (padded) range of the shared contraction dimension and writes its own output matrix
     const int per_group = a.tiles_m * a.tiles_n;
     const int g = tile / per_group;
     const int r = tile - g * per_group;
-    const int nb2 = r / a.tiles_m;
-    mb = r - nb2 * a.tiles_m;
+    const int nb = r / a.tiles_m, mb = r - nb * a.tiles_m;
     const int64_t e0 = a.group_offsets[g], e1 = a.group_offsets[g + 1];
     t.a_row0 = (int64_t)mb * G_BLOCK_M;
-    t.b_row0 = (int64_t)nb2 * BLOCK_N;
-    t.k_byte0 = e0 * 2 / a.k_elems_per_byte_x2;
+    t.b_row0 = (int64_t)nb * BLOCK_N;
+    t.a_k_byte0 = t.b_k_byte0 = e0 * 2 / a.k_elems_per_byte_x2;
     t.num_k = (int)(((e1 - e0) * 2 / a.k_elems_per_byte_x2 + G_BLOCK_KB - 1) / G_BLOCK_KB);
-    t.sf_kc0 = t.k_byte0 / G_BLOCK_KB * CH;
+    t.sfa_kc0 = t.sfb_kc0 = t.a_k_byte0 / G_BLOCK_KB * CH;
     t.d_row0 = t.a_row0;
-    t.d_rows_end = a.M;
-    t.d_base = (int64_t)g * a.d_group_stride;
-    t.sfa_rb = mb;
-    t.sfb_rb = (int64_t)nb2 * (BLOCK_N / 128);
+    t.d_row_lo = 0;
+    t.d_row_hi = a.M;
     t.d_col0 = t.b_row0;
-    return t;
+    t.d_base = (int64_t)g * a.d_group_stride;
   }
   t.sfa_rb = t.a_row0 / 128;
   t.sfb_rb = t.b_row0 / 128;
-  t.d_col0 = (int64_t)nb * BLOCK_N;
   return t;
 }
 
@@ -297,12 +302,13 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
           for (int h = 0; h < NH; ++h) nh_valid += (t.sfb_rb + h < a.rb_b) ? 1 : 0;
           bytes += nh_valid * CH * 512;
           mbar_expect_tx(&full_bar[s], bytes);
-          const int32_t kx = (int32_t)(t.k_byte0 + (int64_t)k * G_BLOCK_KB);
-          tma_load_2d(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, &full_bar[s], kx, (int32_t)t.a_row0);
-          tma_load_2d(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, &full_bar[s], kx, (int32_t)t.b_row0);
-          const int64_t kc = t.sf_kc0 + (int64_t)k * CH;
-          bulk_load_1d(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, a.sa + (t.sfa_rb * a.kc_a + kc) * 512, CH * 512,
-                       &full_bar[s]);
+          tma_load_2d(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, &full_bar[s],
+                      (int32_t)(t.a_k_byte0 + (int64_t)k * G_BLOCK_KB), (int32_t)t.a_row0);
+          tma_load_2d(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, &full_bar[s],
+                      (int32_t)(t.b_k_byte0 + (int64_t)k * G_BLOCK_KB), (int32_t)t.b_row0);
+          bulk_load_1d(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES,
+                       a.sa + (t.sfa_rb * a.kc_a + t.sfa_kc0 + (int64_t)k * CH) * 512, CH * 512, &full_bar[s]);
+          const int64_t kc = t.sfb_kc0 + (int64_t)k * CH;
 #pragma unroll
           for (int h = 0; h < NH; ++h) {
             if (t.sfb_rb + h < a.rb_b)
@@ -375,7 +381,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
       if (!mbar_wait_bounded(&acc_full[as], aph, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
       tc_fence_after();
       const int64_t row = t.d_row0 + q * 32 + lane;
-      const bool row_ok = row < t.d_rows_end;
+      const bool row_ok = row >= t.d_row_lo && row < t.d_row_hi;
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N / 32; ++c) {
         uint32_t r[32];
@@ -880,9 +886,160 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   return bn == 256 ? launch_gemm<FMT_MXFP8, 256, 4, 1>(ma, mb, args, st) : launch_gemm<FMT_MXFP8, 128, 6, 2>(ma, mb, args, st);
 }
 
+
+// ------------------------------------------------------------------------------------------
+// grouped GEMMs (per-expert weights), MXFP8
+// ------------------------------------------------------------------------------------------
+static int64_t grouped_entries_upper_bound(int64_t rows, int64_t groups) { return (rows + 127) / 128 + groups; }
+
+static int grouped_rows_gemm(const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb, int64_t b_rows,
+                             int64_t ldb_bytes, const int64_t* m_offsets_host, int64_t G, int64_t N_out, int64_t Kc,
+                             int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
+                             void* scratch, int64_t scratch_bytes, cudaStream_t st) {
+  const char* name = "mt_grouped_gemm_mxfp8";
+  MT_REQUIRE(m_offsets_host && G > 0 && G <= 65536, "%s: bad group description", name);
+  const int64_t R = m_offsets_host[G];
+  MT_REQUIRE(m_offsets_host[0] == 0 && R >= 0, "%s: offsets must start at 0", name);
+  for (int64_t g = 0; g < G; ++g)
+    MT_REQUIRE(m_offsets_host[g + 1] >= m_offsets_host[g], "%s: offsets must be non-decreasing", name);
+  MT_REQUIRE(d_dtype == MT_BF16 || d_dtype == MT_F32, "%s: output dtype %d not supported", name, d_dtype);
+  MT_REQUIRE(N_out % 128 == 0, "%s: N (%lld) must be a multiple of 128", name, (long long)N_out);
+  MT_REQUIRE(Kc % 128 == 0, "%s: K (%lld) must be a multiple of 128", name, (long long)Kc);
+  MT_REQUIRE(ldd >= N_out, "%s: ldd smaller than N", name);
+  if (R == 0) return MT_OK;
+  MT_REQUIRE(a && sa && b && sb && d && scratch, "%s: null pointer", name);
+  MT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sa) && aligned16(sb) && aligned16(scratch),
+             "%s: operands must be 16-byte aligned", name);
+
+  // entries: for every 128-row block, every group owning at least one of its rows
+  const int64_t rbs = (R + 127) / 128;
+  const int64_t max_entries = grouped_entries_upper_bound(R, G);
+  const int64_t need = (int64_t)sizeof(int64_t) * (G + 1) + 2 * (int64_t)sizeof(int32_t) * max_entries;
+  MT_REQUIRE(scratch_bytes >= need, "%s: scratch too small (%lld < %lld bytes)", name, (long long)scratch_bytes,
+             (long long)need);
+  std::vector<int32_t> table(2 * max_entries);
+  int64_t n = 0, g = 0;
+  for (int64_t rb = 0; rb < rbs; ++rb) {
+    const int64_t lo = rb * 128, hi = std::min<int64_t>(lo + 128, R);
+    while (g < G && m_offsets_host[g + 1] <= lo) ++g;  // skip groups that end before this block
+    for (int64_t gg = g; gg < G && m_offsets_host[gg] < hi; ++gg) {
+      if (m_offsets_host[gg + 1] <= m_offsets_host[gg]) continue;  // empty group
+      if (m_offsets_host[gg + 1] <= lo) continue;
+      table[n] = (int32_t)rb;
+      table[max_entries + n] = (int32_t)gg;
+      ++n;
+    }
+  }
+  uint8_t* sc = static_cast<uint8_t*>(scratch);
+  int64_t* d_offsets = reinterpret_cast<int64_t*>(sc);
+  int32_t* d_table = reinterpret_cast<int32_t*>(sc + sizeof(int64_t) * (G + 1));
+  MT_CUDA(cudaMemcpyAsync(d_offsets, m_offsets_host, sizeof(int64_t) * (G + 1), cudaMemcpyHostToDevice, st));
+  MT_CUDA(cudaMemcpyAsync(d_table, table.data(), sizeof(int32_t) * 2 * max_entries, cudaMemcpyHostToDevice, st));
+  if (n == 0) return MT_OK;
+
+  GemmArgs args{};
+  args.sa = sa; args.sb = sb;
+  args.kc_a = padded_chunks(Kc / 32);
+  args.kc_b = padded_chunks(ldb_bytes / 32);
+  args.rb_a = rbs; args.rb_b = (b_rows + 127) / 128;
+  args.M = R; args.N = N_out; args.K_bytes = Kc;
+  args.d = d; args.ldd = ldd; args.d_dtype = d_dtype;
+  args.status = device_status_ptr();
+  if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+  args.mode = MODE_GROUPED_ROWS;
+  args.num_groups = (int)G;
+  args.group_offsets = d_offsets;
+  args.tile_rb = d_table;
+  args.tile_group = d_table + max_entries;
+  args.b_group_rows = b_group_rows;
+  args.b_group_k_bytes = b_group_k;
+  args.k_elems_per_byte_x2 = 2;
+  const int bn = N_out % 256 == 0 ? 256 : 128;
+  args.tiles_m = (int)n;
+  args.tiles_n = (int)(N_out / bn);
+  args.num_tiles = args.tiles_m * args.tiles_n;
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)Kc, (uint64_t)R, (uint64_t)Kc, G_BLOCK_KB,
+                              G_BLOCK_M, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)ldb_bytes, (uint64_t)b_rows, (uint64_t)ldb_bytes,
+                          G_BLOCK_KB, (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  return bn == 256 ? launch_gemm<FMT_MXFP8, 256, 4, 1>(ma, mb, args, st) : launch_gemm<FMT_MXFP8, 128, 6, 2>(ma, mb, args, st);
+}
+
 }  // namespace mt
 
 extern "C" {
+
+int64_t mt_grouped_scratch_bytes(int64_t rows, int64_t groups) {
+  if (rows < 0 || groups < 0) return 0;
+  const int64_t e = mt::grouped_entries_upper_bound(rows, groups);
+  return ((int64_t)sizeof(int64_t) * (groups + 1) + 2 * (int64_t)sizeof(int32_t) * e + 255) / 256 * 256;
+}
+
+int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
+                          int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G, int64_t N, int64_t K,
+                          int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd, void* scratch,
+                          int64_t scratch_bytes, mt_stream_t stream) {
+  return mt::grouped_rows_gemm(a, sa_swz, b, sb_swz, b_rows, ldb, m_offsets_host, G, N, K, b_group_rows, b_group_k, d,
+                               d_dtype, ldd, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const uint8_t* b_t, const uint8_t* sb_t_swz,
+                           const int64_t* pad_offsets_host, int64_t G, int64_t N_out, int64_t K_out, void* d,
+                           int d_dtype, int accumulate, void* scratch, int64_t scratch_bytes, mt_stream_t stream) {
+  using namespace mt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* name = "mt_grouped_wgrad_mxfp8";
+  MT_REQUIRE(pad_offsets_host && G > 0 && G <= 65536, "%s: bad group description", name);
+  MT_REQUIRE(pad_offsets_host[0] == 0, "%s: offsets must start at 0", name);
+  for (int64_t g = 0; g < G; ++g)
+    MT_REQUIRE(pad_offsets_host[g + 1] >= pad_offsets_host[g] && pad_offsets_host[g + 1] % 128 == 0,
+               "%s: padded offsets must be non-decreasing multiples of 128", name);
+  MT_REQUIRE(d_dtype == MT_BF16 || d_dtype == MT_F32, "%s: output dtype %d not supported", name, d_dtype);
+  MT_REQUIRE(N_out > 0 && K_out > 0, "%s: empty output", name);
+  MT_REQUIRE(d && scratch && scratch_bytes >= (int64_t)sizeof(int64_t) * (G + 1), "%s: null output or scratch too small", name);
+  const int64_t Rp = pad_offsets_host[G];
+  if (Rp == 0) {
+    if (!accumulate) {
+      const size_t es = d_dtype == MT_F32 ? 4 : 2;
+      MT_CUDA(cudaMemsetAsync(d, 0, (size_t)G * N_out * K_out * es, st));
+    }
+    return MT_OK;
+  }
+  MT_REQUIRE(a_t && sa_t_swz && b_t && sb_t_swz, "%s: null pointer", name);
+  MT_REQUIRE(aligned16(a_t) && aligned16(b_t) && aligned16(sa_t_swz) && aligned16(sb_t_swz) && aligned16(scratch),
+             "%s: operands must be 16-byte aligned", name);
+  int64_t* d_offsets = static_cast<int64_t*>(scratch);
+  MT_CUDA(cudaMemcpyAsync(d_offsets, pad_offsets_host, sizeof(int64_t) * (G + 1), cudaMemcpyHostToDevice, st));
+
+  GemmArgs args{};
+  args.sa = sa_t_swz; args.sb = sb_t_swz;
+  args.kc_a = args.kc_b = padded_chunks(Rp / 32);
+  args.rb_a = (N_out + 127) / 128; args.rb_b = (K_out + 127) / 128;
+  args.M = N_out; args.N = K_out; args.K_bytes = Rp;
+  args.d = d; args.ldd = K_out; args.d_dtype = d_dtype; args.accumulate = accumulate;
+  args.status = device_status_ptr();
+  if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+  args.mode = MODE_GROUPED_K;
+  args.num_groups = (int)G;
+  args.group_offsets = d_offsets;
+  args.d_group_stride = N_out * K_out;
+  args.k_elems_per_byte_x2 = 2;
+  const int bn = K_out > 128 ? 256 : 128;
+  args.tiles_m = (int)((N_out + G_BLOCK_M - 1) / G_BLOCK_M);
+  args.tiles_n = (int)((K_out + bn - 1) / bn);
+  args.num_tiles = (int)(G * args.tiles_m * args.tiles_n);
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_t, (uint64_t)Rp, (uint64_t)N_out, (uint64_t)Rp, G_BLOCK_KB,
+                              G_BLOCK_M, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_t, (uint64_t)Rp, (uint64_t)K_out, (uint64_t)Rp, G_BLOCK_KB,
+                          (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  return bn == 256 ? launch_gemm<FMT_MXFP8, 256, 4, 1>(ma, mb, args, st) : launch_gemm<FMT_MXFP8, 128, 6, 2>(ma, mb, args, st);
+}
 
 int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, const uint8_t* b,
                   const uint8_t* sb_swz, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,

@@ -6,6 +6,9 @@
 // outside the tensor), a row pass from shared memory straight to global memory and a
 // column pass staged through shared memory so that global stores stay 16-byte and
 // row-contiguous. There is no per-tensor scale in this format, hence no abs-max pre-pass.
+#include <algorithm>
+#include <vector>
+
 #include "quantize_common.cuh"
 
 namespace mt {
@@ -27,9 +30,13 @@ struct Mxfp8Args {
   int64_t kc_row, kc_col;
   uint8_t *q, *s, *s_swz, *q_t, *s_t, *s_t_swz;
   int* status;
+  // grouped transposed mode: tile t covers input rows [tiles[t].row_start, +rows_valid) of one
+  // group and writes 128 zero-padded token columns starting at tiles[t].out_col
+  const int4* tiles;   // {row_start, rows_valid, out_col, last_tile}
+  int64_t out_cols;    // padded token count (row length of q_t)
 };
 
-template <bool kTranspose>
+template <bool kTranspose, bool kGrouped = false>
 __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_constant__ CUtensorMap in_map,
                                                                    const Mxfp8Args a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -37,7 +44,12 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
       (reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t k0 = (int64_t)blockIdx.x * QT_COLS;
-  const int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
+  int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
+  int4 gt = make_int4(0, QT_ROWS, 0, 0);
+  if (kGrouped) {
+    gt = a.tiles[blockIdx.y];
+    m0 = gt.x;
+  }
 
   if (tid == 0) {
     sm.abort_flag = 0;
@@ -50,10 +62,20 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
     tma_load_2d(&sm.in[0][0], &in_map, &sm.bar, (int32_t)k0, (int32_t)m0);
   }
   if (!mbar_wait_bounded(&sm.bar, 0, &sm.abort_flag, a.status, DS_QUANT_WAIT)) return;
+  if (kGrouped) {
+    // rows past the end of this group belong to the next one: they contribute zeros here
+    const int r = tid >> 1, h = tid & 1;
+    if (r >= gt.y) {
+      uint4* p = reinterpret_cast<uint4*>(&sm.in[r][h * 64]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) p[i] = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+  }
 
   // ---- row pass: thread <-> (row, 1x32 block); 4 blocks per tile row ----
 #pragma unroll
-  for (int it = 0; it < 2; ++it) {
+  for (int it = 0; it < (kGrouped ? 0 : 2); ++it) {
     const int r = it * 64 + (tid >> 2);
     const int b = tid & 3;
     uint4 w[4];
@@ -114,6 +136,30 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
   }
   __syncthreads();
 
+  if (kGrouped) {
+    // transposed codes: 128 feature rows x 128 token bytes at the group's padded position
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int row = it * 32 + (tid >> 3);
+      const int ch = tid & 7;
+      const int64_t gk = k0 + row;
+      const int swz = (row >> 1) & 7;
+      if (gk < a.cols)
+        *reinterpret_cast<uint4*>(a.q_t + gk * a.out_cols + gt.z + ch * 16) =
+            *reinterpret_cast<const uint4*>(&sm.out_t[row][(ch ^ swz) * 16]);
+    }
+    if (a.s_t != nullptr && tid < QT_COLS && k0 + tid < a.cols)
+      *reinterpret_cast<uint32_t*>(a.s_t + (k0 + tid) * a.s_t_stride + (gt.z >> 5)) =
+          *reinterpret_cast<const uint32_t*>(sm.st_lin[tid]);
+    uint8_t* base = a.s_t_swz + ((k0 >> 7) * a.kc_col + (gt.z >> 7)) * 512;
+    if (tid < 32) *reinterpret_cast<uint4*>(base + tid * 16) = *reinterpret_cast<const uint4*>(sm.st_swz + tid * 16);
+    if (gt.w) {  // last tile along the token axis: zero the chunks up to the padded count
+      const int64_t extra = a.kc_col - ((gt.z >> 7) + 1);
+      for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
+        *reinterpret_cast<uint4*>(base + 512 + i * 16) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
   if (tid < QT_ROWS) {
     const int64_t gr = m0 + tid;
     const int64_t kb0 = k0 >> 5;
@@ -182,10 +228,10 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
 
 static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
 
-template <bool T>
+template <bool T, bool GRP = false>
 static int launch_mxfp8(const CUtensorMap& map, const Mxfp8Args& args, dim3 grid, cudaStream_t st) {
   static bool attr_set = false;
-  auto kern = quantize_mxfp8_kernel<T>;
+  auto kern = quantize_mxfp8_kernel<T, GRP>;
   const int smem = (int)sizeof(Mxfp8Smem) + 128;
   if (!attr_set) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -228,4 +274,62 @@ extern "C" int mt_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, uint
   if (rc != MT_OK) return rc;
   dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
   return transpose ? launch_mxfp8<true>(map, args, grid, st) : launch_mxfp8<false>(map, args, grid, st);
+}
+
+
+extern "C" int64_t mt_grouped_padded_rows(const int64_t* m_offsets_host, int64_t G, int64_t* pad_offsets_out) {
+  if (!m_offsets_host || G <= 0) return 0;
+  int64_t off = 0;
+  if (pad_offsets_out) pad_offsets_out[0] = 0;
+  for (int64_t g = 0; g < G; ++g) {
+    const int64_t m = m_offsets_host[g + 1] - m_offsets_host[g];
+    off += (m + 127) / 128 * 128;
+    if (pad_offsets_out) pad_offsets_out[g + 1] = off;
+  }
+  return off;
+}
+
+extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
+                                                   const int64_t* m_offsets_host, int64_t G, uint8_t* q_t,
+                                                   uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, void* scratch,
+                                                   int64_t scratch_bytes, mt_stream_t stream) {
+  using namespace mt;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* name = "mt_grouped_transpose_quantize_mxfp8";
+  MT_REQUIRE(m_offsets_host && G > 0, "%s: bad group description", name);
+  MT_REQUIRE(m_offsets_host[0] == 0 && m_offsets_host[G] == rows, "%s: offsets must run from 0 to rows", name);
+  MT_REQUIRE(cols > 0 && cols % 32 == 0, "%s: cols (%lld) must be a positive multiple of 32", name, (long long)cols);
+  std::vector<int4> tiles;
+  int64_t out_col = 0;
+  for (int64_t g = 0; g < G; ++g) {
+    const int64_t m = m_offsets_host[g + 1] - m_offsets_host[g];
+    MT_REQUIRE(m >= 0, "%s: offsets must be non-decreasing", name);
+    for (int64_t i = 0; i < m; i += 128) {
+      tiles.push_back(make_int4((int)(m_offsets_host[g] + i), (int)std::min<int64_t>(128, m - i), (int)out_col, 0));
+      out_col += 128;
+    }
+  }
+  if (tiles.empty()) return MT_OK;
+  tiles.back().w = 1;
+  MT_REQUIRE(x && q_t && s_t_swz && scratch, "%s: null pointer", name);
+  MT_REQUIRE(aligned16(x) && aligned16(q_t) && aligned16(s_t_swz) && aligned16(scratch), "%s: pointers must be 16-byte aligned", name);
+  MT_REQUIRE(scratch_bytes >= (int64_t)(tiles.size() * sizeof(int4)), "%s: scratch too small", name);
+  MT_REQUIRE(!s_t || (s_t_stride >= out_col / 32 && s_t_stride % 4 == 0), "%s: bad s_t stride", name);
+  MT_CUDA(cudaMemcpyAsync(scratch, tiles.data(), tiles.size() * sizeof(int4), cudaMemcpyHostToDevice, st));
+
+  Mxfp8Args args{};
+  args.rows = rows; args.cols = cols;
+  args.s_t_stride = s_t_stride;
+  args.kc_col = padded_chunks(out_col / 32);
+  args.q_t = q_t; args.s_t = s_t; args.s_t_swz = s_t_swz;
+  args.status = device_status_ptr();
+  if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+  args.tiles = static_cast<const int4*>(scratch);
+  args.out_cols = out_col;
+  CUtensorMap map;
+  int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)cols, (uint64_t)rows,
+                              (uint64_t)cols * 2, QT_COLS, QT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != MT_OK) return rc;
+  dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)tiles.size());
+  return launch_mxfp8<true, true>(map, args, grid, st);
 }

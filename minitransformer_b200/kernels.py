@@ -153,6 +153,12 @@ def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat
     _require_cuda(qa, "qa")
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1] * 2
     assert qb.shape[1] * 2 == K
+    if K % 32 and not check_kernel:
+        # TMA rows must be multiples of 16 bytes: append one block of zero codes (value 0; its
+        # scale bytes in the GEMM layout are already zero padding)
+        qa = torch.nn.functional.pad(qa, (0, 8))
+        qb = torch.nn.functional.pad(qb, (0, 8))
+        K += 16
     out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
     _count(1 if M and N and K else 0)
     if check_kernel:
@@ -182,6 +188,95 @@ def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, ac
     _lib.call("mt_gemm_mxfp8", qa.data_ptr(), sa_swz.data_ptr(), qb.data_ptr(), sb_swz.data_ptr(), M, N, K,
               out.data_ptr(), _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
               0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+    return out
+
+
+# ---- grouped (per-expert) MXFP8 path ----
+def _offsets_array(m_splits):
+    import ctypes
+    off = [0]
+    for m in m_splits:
+        off.append(off[-1] + int(m))
+    return (ctypes.c_int64 * len(off))(*off), off
+
+
+def grouped_padded_offsets(m_splits):
+    """Token offsets after padding every group to a multiple of 128 tokens."""
+    off = [0]
+    for m in m_splits:
+        off.append(off[-1] + (int(m) + 127) // 128 * 128)
+    return off
+
+
+def _grouped_scratch(rows: int, groups: int, device) -> torch.Tensor:
+    n = int(_lib.load().mt_grouped_scratch_bytes(rows, groups))
+    return torch.empty(max(n, 256), dtype=torch.uint8, device=device)
+
+
+def grouped_transpose_quantize_mxfp8(x: torch.Tensor, m_splits, want_linear_scales: bool = False):
+    """x [R, K] bf16 -> (q_t [K, Rp] u8, s_t_swz, s_t or None, padded offsets)."""
+    _require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    R, K = x.shape
+    arr, off = _offsets_array(m_splits)
+    assert off[-1] == R, "m_splits must sum to the number of rows"
+    pad = grouped_padded_offsets(m_splits)
+    Rp = pad[-1]
+    dev = x.device
+    q_t = torch.empty((K, Rp), dtype=torch.uint8, device=dev)
+    s_t_swz = torch.empty(swizzled_scale_bytes(K, Rp // 32), dtype=torch.uint8, device=dev)
+    s_t = torch.empty((K, Rp // 32), dtype=torch.uint8, device=dev) if want_linear_scales else None
+    scratch = _grouped_scratch(R, len(m_splits), dev)
+    _lib.call("mt_grouped_transpose_quantize_mxfp8", x.data_ptr(), R, K, arr, len(m_splits), q_t.data_ptr(),
+              _ptr(s_t), Rp // 32, s_t_swz.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream())
+    _count(1 if Rp else 0)
+    return q_t, s_t_swz, s_t, pad
+
+
+def grouped_gemm_mxfp8(qa, sa_swz, qb, sb_swz, m_splits, *, n_out: int, transposed_weights: bool,
+                       out_dtype=torch.bfloat16):
+    """Rows of qa [R, K] are split by m_splits; group g uses its own weight.
+    transposed_weights=False: qb = stacked weights [G*n_out, K] (forward).
+    transposed_weights=True:  qb = transposed stacked weights [n_out, G*K] (dgrad)."""
+    _require_cuda(qa, "qa")
+    R, K = qa.shape
+    G = len(m_splits)
+    arr, off = _offsets_array(m_splits)
+    assert off[-1] == R
+    if transposed_weights:
+        assert qb.shape == (n_out, G * K)
+        b_rows, ldb, grp_rows, grp_k = n_out, G * K, 0, K
+    else:
+        assert qb.shape == (G * n_out, K)
+        b_rows, ldb, grp_rows, grp_k = G * n_out, K, n_out, 0
+    out = torch.empty((R, n_out), dtype=out_dtype, device=qa.device)
+    scratch = _grouped_scratch(R, G, qa.device)
+    _lib.call("mt_grouped_gemm_mxfp8", qa.data_ptr(), sa_swz.data_ptr(), qb.data_ptr(), sb_swz.data_ptr(), b_rows, ldb,
+              arr, G, n_out, K, grp_rows, grp_k, out.data_ptr(), _out_dtype_code(out_dtype), n_out,
+              scratch.data_ptr(), scratch.numel(), _stream())
+    _count(1 if R else 0)
+    return out
+
+
+def grouped_wgrad_mxfp8(qa_t, sa_t_swz, qb_t, sb_t_swz, pad_offsets, *, out_dtype=torch.float32, out=None,
+                        accumulate=False):
+    """Per-group D_g[N, K] = qa_t[N, cols_g] . qb_t[K, cols_g]^T; returns [G, N, K]."""
+    import ctypes
+    _require_cuda(qa_t, "qa_t")
+    G = len(pad_offsets) - 1
+    N, K = qa_t.shape[0], qb_t.shape[0]
+    assert qa_t.shape[1] == qb_t.shape[1] == pad_offsets[-1]
+    if out is None:
+        assert not accumulate
+        out = torch.empty((G, N, K), dtype=out_dtype, device=qa_t.device)
+    else:
+        assert out.shape == (G, N, K) and out.dtype == out_dtype and out.is_contiguous()
+    arr = (ctypes.c_int64 * (G + 1))(*pad_offsets)
+    scratch = _grouped_scratch(pad_offsets[-1], G, qa_t.device)
+    _lib.call("mt_grouped_wgrad_mxfp8", qa_t.data_ptr(), sa_t_swz.data_ptr(), qb_t.data_ptr(), sb_t_swz.data_ptr(),
+              arr, G, N, K, out.data_ptr(), _out_dtype_code(out_dtype), int(accumulate), scratch.data_ptr(),
+              scratch.numel(), _stream())
+    _count(1)
     return out
 
 

@@ -41,3 +41,40 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
         return kernels.gemm_mxfp8(qx.view(torch.uint8), _swizzled(sx, M), qw.view(torch.uint8), _swizzled(sw, N),
                                   out_dtype=out_dtype, out=out, accumulate=accumulate,
                                   bias=bias if bias is not None and bias.numel() else None)
+
+    # ---- grouped (per-expert) operations used by GroupedLinear ----
+    def grouped_quantize(self, w: torch.Tensor, qparams, return_transpose: bool = False) -> Q.QuantizeResult:
+        """w [G, N, K] (stacked expert weights) -> row-wise copy [G*N, K] and, optionally, the
+        transposed copy [K, G*N] (1x32 blocks along each expert's N, never across experts since
+        N is a multiple of 32). One kernel launch for all experts."""
+        assert w.dim() == 3 and w.shape[1] % 32 == 0
+        G, N, K = w.shape
+        return self.quantize(w.reshape(G * N, K), qparams, return_transpose=return_transpose)
+
+    def grouped_qgemm(self, qx, qw, m_params, out_dtype, sx, sw, m_splits=None, biases=None, qparams_x=None,
+                      qparams_w=None, weights_transposed: bool = False, n_out=None):
+        """Rows of qx are split by m_splits; group g multiplies with expert g.
+        weights_transposed=False: qw is the stacked row-wise copy [G*N, K]; y[R, N].
+        weights_transposed=True:  qw is the transposed stacked copy [K_in, G*N]; y[R, K_in]."""
+        assert biases is None, "biases are added by the module"
+        G = len(m_splits)
+        if n_out is None:
+            n_out = qw.shape[0] if weights_transposed else qw.shape[0] // G
+        return kernels.grouped_gemm_mxfp8(qx.view(torch.uint8), _swizzled(sx, qx.shape[0]), qw.view(torch.uint8),
+                                          _swizzled(sw, qw.shape[0]), m_splits, n_out=n_out,
+                                          transposed_weights=weights_transposed, out_dtype=out_dtype)
+
+    def grouped_transpose_quantize(self, t: torch.Tensor, m_splits, dtype=None):
+        """t [R, C] -> (q_t [C, Rp], s_t_swz, padded offsets): t^T with every group zero-padded
+        to 128 tokens and 1x32 blocks restarting at each group."""
+        q_t, s_t_swz, _, pad = kernels.grouped_transpose_quantize_mxfp8(_as_2d_bf16(t), m_splits)
+        return q_t, s_t_swz, pad
+
+    def grouped_gemm_1d1d(self, a, b, out_dtype=torch.float32, single_output: bool = True, out=None,
+                          accumulate: bool = False):
+        """a = grouped_transpose_quantize(dy), b = grouped_transpose_quantize(x) ->
+        per-expert weight gradients [G, N, K] (or a list of G views)."""
+        (qa, sa, pad), (qb, sb, pad_b) = a, b
+        assert pad == pad_b
+        w = kernels.grouped_wgrad_mxfp8(qa, sa, qb, sb, pad, out_dtype=out_dtype, out=out, accumulate=accumulate)
+        return w if single_output else list(w.unbind(0))

@@ -72,6 +72,12 @@ def qgemm_mxfp8(qx, sx_bytes, qw, sw_bytes, out_bf16=True, out=None, accumulate=
     wv = F.e4m3_decode(qw)
     sx = F.e8m0_decode(sx_bytes)
     sw = F.e8m0_decode(sw_bytes)
+    # a ragged contraction length was quantized with zero padding up to the block: the codes
+    # were sliced back, the scales kept the padded block; restore the zero elements
+    kpad = sx.shape[1] * 32 - xv.shape[1]
+    if kpad > 0:
+        xv = np.pad(xv, ((0, 0), (0, kpad)))
+        wv = np.pad(wv, ((0, 0), (0, kpad)))
     y = (_fused if fused else _blockwise)(xv, wv, sx, sw, 32)
     rnd = F.bf16_round if out_bf16 else (lambda a: a.astype(np.float32))
     return _finish(y.astype(np.float32), rnd, out, accumulate)

@@ -1,0 +1,184 @@
+"""GPU parity of the drop-in modules (Linear, GroupedLinear) against the reference fixtures
+and the numpy oracle: forward, dgrad and wgrad within 1e-3 relative Frobenius error, the
+quantized operands underneath bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_bits_to_f32
+from helpers import from_bits, mismatch, np_u8, seeded_bf16, unswizzle_scales_ref
+from minitransformer_b200 import kernels as K
+from minitransformer_b200.module import config
+from minitransformer_b200.module.group_linear import GroupedLinear
+from minitransformer_b200.module.linear import Linear
+from oracle import formats as F, gemm, linear as oracle_linear, mxfp8
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def _relf(t, ref):
+    return gemm.rel_frobenius(t.detach().float().cpu().numpy(), ref)
+
+
+def _make_linear(K_in, N_out, recipe, w, **kw):
+    params = config.get_qlinear_params_from_predefined(recipe)
+    lin = Linear(K_in, N_out, bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params, **kw)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+    return lin
+
+
+def test_linear_nvfp4_matches_reference_fixture(golden_nvfp4_linear):
+    """Same inputs as the reference's _QuantizedLinear run stored in the fixture."""
+    g = golden_nvfp4_linear
+    for tag in ("a", "b"):
+        x, w, dy = (from_bits(g[f"{tag}/{n}"]).cuda() for n in ("x", "w", "dy"))
+        lin = _make_linear(x.shape[1], w.shape[0], config.QuantizeRecipe.FP4_SUB_CHANNEL, w)
+        xd = x.clone().requires_grad_(True)
+        y = lin(xd)
+        y.backward(dy)
+        assert _relf(y, bf16_bits_to_f32(g[f"{tag}/lin_y"])) <= TOL
+        assert _relf(xd.grad, bf16_bits_to_f32(g[f"{tag}/lin_dx"])) <= TOL
+        assert _relf(lin.weight.grad, g[f"{tag}/lin_dw"]) <= TOL
+    assert K.read_device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 384), (32 * 128, 1024, 4096), (16, 1024, 4096)])
+@pytest.mark.parametrize("rht", [True, False])
+def test_linear_nvfp4_matches_oracle(shape, rht):
+    """Shapes from the reference's own module tests (batch 32 x seq 128 rows; 1024 -> 4096)."""
+    M, Kd, N = shape
+    tx, x = seeded_bf16((M, Kd), 1234)
+    tw, w = seeded_bf16((N, Kd), 1235, 0.02)
+    tdy, dy = seeded_bf16((M, N), 1236, 1e-3)
+    ref = oracle_linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=rht, fused=M * N * Kd > 5e7)
+    recipe = config.QuantizeRecipe.FP4_SUB_CHANNEL if rht else config.QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT
+    lin = _make_linear(Kd, N, recipe, tw.cuda(), fuse_wgrad_accumulation=True)
+    lin.weight.main_grad = torch.zeros(N, Kd, dtype=torch.float32, device="cuda")
+    xd = tx.cuda().requires_grad_(True)
+    y = lin(xd.view(M // 16, 16, Kd), is_first_microbatch=True)   # 3-D input, like [seq, batch, hidden]
+    assert y.shape == (M // 16, 16, N)
+    y.backward(tdy.cuda().view(M // 16, 16, N))
+    assert _relf(y.view(M, N), ref["y"]) <= TOL
+    assert _relf(xd.grad, ref["dx"]) <= TOL
+    assert _relf(lin.weight.main_grad, ref["dw"]) <= TOL
+    assert lin.weight.grad is None  # the gradient went to main_grad
+    # second microbatch: cached quantized weight, accumulation into main_grad
+    xd2 = tx.cuda().requires_grad_(True)
+    lin(xd2, is_first_microbatch=False).backward(tdy.cuda())
+    assert _relf(lin.weight.main_grad, 2 * ref["dw"]) <= TOL
+    assert K.read_device_status() == 0
+
+
+def test_linear_mxfp8_matches_oracle():
+    M, Kd, N = 512, 1024, 768
+    tx, x = seeded_bf16((M, Kd), 11)
+    tw, w = seeded_bf16((N, Kd), 12, 0.02)
+    tdy, dy = seeded_bf16((M, N), 13, 1e-3)
+    ref = oracle_linear.mxfp8_linear_fwd_bwd(x, w, dy, fused=True)
+    lin = _make_linear(Kd, N, config.QuantizeRecipe.MXFP8_SUB_CHANNEL, tw.cuda())
+    xd = tx.cuda().requires_grad_(True)
+    y = lin(xd)
+    y.backward(tdy.cuda())
+    assert _relf(y, ref["y"]) <= TOL
+    assert _relf(xd.grad, ref["dx"]) <= TOL
+    assert _relf(lin.weight.grad, F.bf16_round(ref["dw"])) <= TOL
+
+
+def test_linear_bias_and_return_bias():
+    M, Kd, N = 128, 256, 256
+    params = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT)
+    lin = Linear(Kd, N, bias=True, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params)
+    with torch.no_grad():
+        lin.bias.normal_()
+    x = torch.randn(M, Kd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = lin(x)
+    lin2 = Linear(Kd, N, bias=True, return_bias=True, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params)
+    with torch.no_grad():
+        lin2.weight.copy_(lin.weight)
+        lin2.bias.copy_(lin.bias)
+    y2, b2 = lin2(x)
+    assert torch.allclose(y.float(), (y2.float() + b2.float()), atol=2e-2, rtol=2e-2)
+    y.sum().backward()
+    assert torch.allclose(lin.bias.grad.float(), torch.full((N,), float(M), device="cuda"))
+
+
+def test_grouped_transpose_quantize_matches_oracle():
+    m_splits = [130, 0, 64, 1, 257, 60]
+    R, Kd = sum(m_splits), 256
+    t, x = seeded_bf16((R, Kd), 5)
+    q_t, s_swz, s_lin, pad = K.grouped_transpose_quantize_mxfp8(t.cuda(), m_splits, want_linear_scales=True)
+    q_t, s_lin = np_u8(q_t), np_u8(s_lin)
+    off = 0
+    for g, m in enumerate(m_splits):
+        p0, p1 = pad[g], pad[g + 1]
+        assert p1 - p0 == (m + 127) // 128 * 128
+        if m:
+            o = mxfp8.quantize(x[off:off + m])
+            assert mismatch(q_t[:, p0:p0 + m], o["data_t"]) == 0
+            nb = (m + 31) // 32
+            assert mismatch(s_lin[:, p0 // 32:p0 // 32 + nb], o["scale_t"]) == 0
+        assert not q_t[:, p0 + m:p1].any()   # zero padding
+        off += m
+    assert mismatch(unswizzle_scales_ref(np_u8(s_swz), Kd, pad[-1] // 32), s_lin) == 0
+
+
+@pytest.mark.parametrize("m_splits", [[128, 128, 128], [130, 0, 64, 1, 257, 60], [0, 0, 300], [5, 7, 9, 11]])
+def test_grouped_linear_mxfp8_matches_oracle(m_splits):
+    G, Kd, N = len(m_splits), 256, 384
+    R = sum(m_splits)
+    tx, x = seeded_bf16((R, Kd), 21)
+    tdy, dy = seeded_bf16((R, N), 22, 1e-3)
+    ws = [seeded_bf16((N, Kd), 30 + g, 0.02) for g in range(G)]
+    ref = oracle_linear.mxfp8_grouped_fwd_bwd(x, [w[1] for w in ws], dy, m_splits)
+    params = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    gl = GroupedLinear(G, Kd, N, bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params)
+    with torch.no_grad():
+        for g in range(G):
+            getattr(gl, f"weight{g}").copy_(ws[g][0])
+    xd = tx.cuda().requires_grad_(True)
+    y = gl(xd, m_splits)
+    y.backward(tdy.cuda())
+    assert _relf(y, ref["y"]) <= TOL
+    assert _relf(xd.grad, ref["dx"]) <= TOL
+    for g in range(G):
+        got = getattr(gl, f"weight{g}").grad
+        want = F.bf16_round(ref["dw"][g])
+        if m_splits[g] == 0:
+            assert float(got.abs().max()) == 0.0
+        else:
+            assert _relf(got, want) <= TOL
+    assert K.read_device_status() == 0
+
+
+def test_grouped_linear_full_size_spot_checks():
+    """Configuration-3 scale (128 experts, 131072 rows, seeded Zipf(1.1) group sizes with empty
+    groups, hidden 2048 -> 768): expert slices of the grouped output against the dense kernel
+    on the same slice; the padded transposed copies against per-group quantization."""
+    G, R, Kd, N = 128, 131072, 2048, 768
+    rng = np.random.default_rng(1234)
+    p = 1.0 / np.arange(1, G + 1) ** 1.1
+    ids = rng.choice(G, size=R, p=p / p.sum())
+    m_splits = np.bincount(ids, minlength=G).tolist()
+    assert sum(m_splits) == R
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn(R, Kd, device="cuda", generator=gen).to(torch.bfloat16)
+    w = (torch.randn(G, N, Kd, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    params = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    op = params.quantize_op
+    qx = op.quantize(x, params.x_params)
+    qw = op.grouped_quantize(w, params.w_params, return_transpose=True)
+    y = op.grouped_qgemm(qx.data, qw.data, params.mm_fprop, torch.bfloat16, qx.scale, qw.scale, m_splits=m_splits,
+                         weights_transposed=False, n_out=N)
+    off = np.concatenate([[0], np.cumsum(m_splits)])
+    for g in (0, 1, 17, 63, 127):
+        r0, r1 = int(off[g]), int(off[g + 1])
+        if r1 == r0:
+            continue
+        xs = K.quantize_mxfp8(x[r0:r1].contiguous(), return_transpose=False)
+        ws = K.quantize_mxfp8(w[g].contiguous(), return_transpose=False)
+        ref = K.gemm_mxfp8(xs.data, xs.scale_swz, ws.data, ws.scale_swz)
+        err = float((y[r0:r1].float() - ref.float()).norm() / ref.float().norm())
+        assert err <= TOL, (g, err)
+    assert K.read_device_status() == 0
