@@ -168,6 +168,31 @@ int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t
                           void* d, int d_dtype, int64_t ldd,
                           void* scratch, int64_t scratch_bytes, mt_stream_t stream);
 
+/* mt_grouped_gemm_mxfp8 without caller-provided scratch. No counterpart in the reference.
+ *
+ * Some callers have no way to hand over scratch memory: every free byte of the GPU already
+ * belongs to someone else's allocator (a training framework's caching pool, an inference
+ * server with a fixed memory plan), or they sit in a latency-critical loop where a
+ * cudaMalloc / cudaFree would synchronise the whole device. For them the tile tables of the
+ * grouped GEMM live in a fixed array inside the library image: about 82 KB of device memory
+ * on every GPU that loads the library, held until the process exits. The call allocates
+ * nothing, neither on the device nor through any library.
+ *
+ * Limits: at most MT_STATIC_MAX_GROUPS groups and MT_STATIC_MAX_ROWS rows; larger problems
+ * are rejected with MT_ERR_INVALID_ARG and a message naming the limit.
+ * All calls on one GPU share the one array. Each call rewrites the part it uses, so nothing
+ * needs clearing between calls, but two calls whose kernels can overlap on the GPU (different
+ * streams) race on it: serialise them.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ * make that first call before starting any stream capture.
+ * Arguments, results and tolerances are those of mt_grouped_gemm_mxfp8. */
+#define MT_STATIC_MAX_GROUPS 1024
+#define MT_STATIC_MAX_ROWS 1048576
+int mt_grouped_gemm_mxfp8_static(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
+                                 int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G,
+                                 int64_t N, int64_t K, int64_t b_group_rows, int64_t b_group_k,
+                                 void* d, int d_dtype, int64_t ldd, mt_stream_t stream);
+
 /* Per-group weight gradients: D_g[N_out, K_out] (+)= A_t[:, cols_g] . B_t[:, cols_g]^T with
  * cols_g = [pad_offsets_host[g], pad_offsets_host[g+1]) of the padded token axis (outputs of
  * mt_grouped_transpose_quantize_mxfp8 on dy and x). The G outputs are stored back to back;

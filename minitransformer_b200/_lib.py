@@ -33,6 +33,8 @@ _SIGNATURES = {
     "mt_grouped_transpose_quantize_mxfp8": (_int, [_vp, _i64, _i64, _c.POINTER(_i64), _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     "mt_grouped_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _c.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
                                      _vp, _int, _i64, _vp, _i64, _vp]),
+    "mt_grouped_gemm_mxfp8_static": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _c.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
+                                            _vp, _int, _i64, _vp]),
     "mt_grouped_wgrad_mxfp8": (_int, [_vp, _vp, _vp, _vp, _c.POINTER(_i64), _i64, _i64, _i64, _vp, _int, _int, _vp, _i64, _vp]),
     "mt_read_device_status": (_int, [_c.POINTER(_int), _vp]),
 }

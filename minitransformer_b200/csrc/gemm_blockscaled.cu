@@ -892,11 +892,12 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
 // ------------------------------------------------------------------------------------------
 static int64_t grouped_entries_upper_bound(int64_t rows, int64_t groups) { return (rows + 127) / 128 + groups; }
 
-static int grouped_rows_gemm(const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb, int64_t b_rows,
-                             int64_t ldb_bytes, const int64_t* m_offsets_host, int64_t G, int64_t N_out, int64_t Kc,
-                             int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
-                             void* scratch, int64_t scratch_bytes, cudaStream_t st) {
-  const char* name = "mt_grouped_gemm_mxfp8";
+// `host_table` is host memory for 2 * grouped_entries_upper_bound(rows, G) int32 values (the
+// tile table is assembled there before it is copied into `scratch`).
+static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb,
+                             int64_t b_rows, int64_t ldb_bytes, const int64_t* m_offsets_host, int64_t G, int64_t N_out,
+                             int64_t Kc, int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
+                             void* scratch, int64_t scratch_bytes, int32_t* host_table, cudaStream_t st) {
   MT_REQUIRE(m_offsets_host && G > 0 && G <= 65536, "%s: bad group description", name);
   const int64_t R = m_offsets_host[G];
   MT_REQUIRE(m_offsets_host[0] == 0 && R >= 0, "%s: offsets must start at 0", name);
@@ -917,7 +918,7 @@ static int grouped_rows_gemm(const uint8_t* a, const uint8_t* sa, const uint8_t*
   const int64_t need = (int64_t)sizeof(int64_t) * (G + 1) + 2 * (int64_t)sizeof(int32_t) * max_entries;
   MT_REQUIRE(scratch_bytes >= need, "%s: scratch too small (%lld < %lld bytes)", name, (long long)scratch_bytes,
              (long long)need);
-  std::vector<int32_t> table(2 * max_entries);
+  int32_t* table = host_table;
   int64_t n = 0, g = 0;
   for (int64_t rb = 0; rb < rbs; ++rb) {
     const int64_t lo = rb * 128, hi = std::min<int64_t>(lo + 128, R);
@@ -934,7 +935,7 @@ static int grouped_rows_gemm(const uint8_t* a, const uint8_t* sa, const uint8_t*
   int64_t* d_offsets = reinterpret_cast<int64_t*>(sc);
   int32_t* d_table = reinterpret_cast<int32_t*>(sc + sizeof(int64_t) * (G + 1));
   MT_CUDA(cudaMemcpyAsync(d_offsets, m_offsets_host, sizeof(int64_t) * (G + 1), cudaMemcpyHostToDevice, st));
-  MT_CUDA(cudaMemcpyAsync(d_table, table.data(), sizeof(int32_t) * 2 * max_entries, cudaMemcpyHostToDevice, st));
+  MT_CUDA(cudaMemcpyAsync(d_table, table, sizeof(int32_t) * 2 * max_entries, cudaMemcpyHostToDevice, st));
   if (n == 0) return MT_OK;
 
   GemmArgs args{};
@@ -982,8 +983,46 @@ int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t
                           int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G, int64_t N, int64_t K,
                           int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd, void* scratch,
                           int64_t scratch_bytes, mt_stream_t stream) {
-  return mt::grouped_rows_gemm(a, sa_swz, b, sb_swz, b_rows, ldb, m_offsets_host, G, N, K, b_group_rows, b_group_k, d,
-                               d_dtype, ldd, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+  MT_REQUIRE(m_offsets_host && G > 0 && G <= 65536, "mt_grouped_gemm_mxfp8: bad group description");
+  std::vector<int32_t> table(2 * mt::grouped_entries_upper_bound(std::max<int64_t>(m_offsets_host[G], 0), G));
+  return mt::grouped_rows_gemm("mt_grouped_gemm_mxfp8", a, sa_swz, b, sb_swz, b_rows, ldb, m_offsets_host, G, N, K,
+                               b_group_rows, b_group_k, d, d_dtype, ldd, scratch, scratch_bytes, table.data(),
+                               static_cast<cudaStream_t>(stream));
+}
+
+// ---- the same grouped GEMM for callers that cannot allocate device memory ----
+// Its tile tables live in this fixed array inside the library image (one copy per GPU that
+// loads the library, held until the process exits) instead of caller-provided scratch.
+#define MT_STATIC_ENTRIES (MT_STATIC_MAX_ROWS / 128 + MT_STATIC_MAX_GROUPS)
+#define MT_STATIC_SCRATCH_BYTES \
+  ((8 * (MT_STATIC_MAX_GROUPS + 1) + 8 * MT_STATIC_ENTRIES + 255) / 256 * 256)
+static __device__ __align__(256) unsigned char g_grouped_static_scratch[MT_STATIC_SCRATCH_BYTES];
+
+int mt_grouped_gemm_mxfp8_static(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
+                                 int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G, int64_t N,
+                                 int64_t K, int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
+                                 mt_stream_t stream) {
+  const char* name = "mt_grouped_gemm_mxfp8_static";
+  MT_REQUIRE(m_offsets_host && G > 0, "%s: bad group description", name);
+  MT_REQUIRE(G <= MT_STATIC_MAX_GROUPS, "%s: %lld groups exceed the built-in limit of %d; use mt_grouped_gemm_mxfp8 "
+             "with caller-provided scratch", name, (long long)G, MT_STATIC_MAX_GROUPS);
+  MT_REQUIRE(m_offsets_host[G] <= MT_STATIC_MAX_ROWS, "%s: %lld rows exceed the built-in limit of %d; use "
+             "mt_grouped_gemm_mxfp8 with caller-provided scratch", name, (long long)m_offsets_host[G], MT_STATIC_MAX_ROWS);
+  // The array's name is only a host-side handle; the kernel needs its device address, which is
+  // looked up once per device (with that device current) and remembered.
+  static void* dev_ptr[64] = {};
+  int dev = -1;
+  MT_CUDA(cudaGetDevice(&dev));
+  MT_REQUIRE(dev >= 0 && dev < 64, "%s: device ordinal %d not supported", name, dev);
+  if (dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    MT_CUDA(cudaGetSymbolAddress(&p, g_grouped_static_scratch));
+    dev_ptr[dev] = p;
+  }
+  static thread_local int32_t host_table[2 * MT_STATIC_ENTRIES];
+  return mt::grouped_rows_gemm(name, a, sa_swz, b, sb_swz, b_rows, ldb, m_offsets_host, G, N, K, b_group_rows, b_group_k,
+                               d, d_dtype, ldd, dev_ptr[dev], MT_STATIC_SCRATCH_BYTES, host_table,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const uint8_t* b_t, const uint8_t* sb_t_swz,
