@@ -80,7 +80,9 @@ def gather_packed_along_first_dim(parts: Sequence[torch.Tensor], process_group) 
     out = out.view(world, packed.numel())
     res, off = [], 0
     for p, n in zip(parts, sizes):
-        piece = out[:, off:off + n].reshape(world * p.shape[0], *p.shape[1:]) if p.dim() > 0 else out[:, off:off + n]
-        res.append(piece.contiguous().view(p.dtype) if p.dtype != torch.uint8 else piece.contiguous())
+        piece = out[:, off:off + n].contiguous().reshape(-1)          # bytes of all ranks, rank-major
+        if p.dtype != torch.uint8:
+            piece = piece.view(p.dtype)
+        res.append(piece.reshape(world * p.shape[0], *p.shape[1:]))
         off += n
     return tuple(res)

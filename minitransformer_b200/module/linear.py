@@ -246,11 +246,15 @@ class _QuantizedLinear(torch.autograd.Function):
         handle.wait()
         world = get_distributed_world_size(tp_group)
         out = out.view(world, -1)
-        nq = qx_t.numel()
-        q = out[:, :nq].reshape(world * qx_t.shape[0], qx_t.shape[1])
-        s = out[:, nq:].reshape(world * sx_t.shape[0], sx_t.shape[1])
-        return (_interleave_gathered_transpose(q, world).view(qx_t.dtype),
-                _interleave_gathered_transpose(s, world).view(sx_t.dtype))
+        nq = qx_t.numel() * qx_t.element_size()   # bytes of the codes inside each rank's packet
+
+        def unpack(piece, like):
+            flat = piece.contiguous().reshape(-1)
+            if like.dtype != torch.uint8:
+                flat = flat.view(like.dtype)
+            return _interleave_gathered_transpose(flat.reshape(world * like.shape[0], like.shape[1]), world)
+
+        return unpack(out[:, :nq], qx_t), unpack(out[:, nq:], sx_t)
 
     @staticmethod
     def reset_wgrad_if_needed(ctx, w, wgrad):

@@ -1,0 +1,108 @@
+"""Tensor-parallel NVFP4 MLP (column-parallel fc1 -> row-parallel fc2, sequence parallel,
+quantized all-gather) on two GPUs over NCCL against the same layers on one GPU. Skipped on
+boxes with a single GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _single_gpu_reference(x, w1, w2, dy, recipe):
+    from minitransformer_b200.module import config
+    from minitransformer_b200.module.linear import Linear
+    p = config.get_qlinear_params_from_predefined(recipe)
+    kw = dict(bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=p)
+    fc1, fc2 = Linear(x.shape[1], w1.shape[0], **kw), Linear(w1.shape[0], w2.shape[0], **kw)
+    with torch.no_grad():
+        fc1.weight.copy_(w1)
+        fc2.weight.copy_(w2)
+    xd = x.clone().requires_grad_(True)
+    h = fc1(xd)
+    y = fc2(h)
+    y.backward(dy)
+    return y.detach(), xd.grad, fc1.weight.grad, fc2.weight.grad, h.detach()
+
+
+def _worker(rank, world, port, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from minitransformer_b200 import kernels as K
+        from minitransformer_b200.module import config
+        from minitransformer_b200.module.linear import Linear
+        recipe = config.QuantizeRecipe.FP4_SUB_CHANNEL
+        g = torch.Generator().manual_seed(3)
+        T, H, Fd = 512, 256, 768
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+        w1 = (torch.randn(Fd, H, generator=g) * 0.02).to(torch.bfloat16).cuda()
+        w2 = (torch.randn(H, Fd, generator=g) * 0.02).to(torch.bfloat16).cuda()
+        dy = (torch.randn(T, H, generator=g) * 1e-3).to(torch.bfloat16).cuda()
+        y_ref, dx_ref, dw1_ref, dw2_ref, h_ref = _single_gpu_reference(x, w1, w2, dy, recipe)
+
+        p = config.get_qlinear_params_from_predefined(recipe)
+        assert p.allgather_quantize
+        kw = dict(bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=p, tp_group=dist.group.WORLD,
+                  sequence_parallel=True)
+        fc1 = Linear(H, Fd, parallel_mode="column", **kw)
+        fc2 = Linear(Fd, H, parallel_mode="row", **kw)
+        with torch.no_grad():
+            fc1.weight.copy_(w1.chunk(world, 0)[rank])
+            fc2.weight.copy_(w2.chunk(world, 1)[rank])
+        xd = x.chunk(world, 0)[rank].clone().requires_grad_(True)
+        h = fc1(xd)
+        y = fc2(h)
+        y.backward(dy.chunk(world, 0)[rank])
+        torch.cuda.synchronize()
+
+        def relf(a, b):
+            return float((a.float() - b.float()).norm() / b.float().norm())
+
+        errs = {
+            # the gathered quantized activation equals quantizing the gathered tensor, but each
+            # rank quantizes only its weight shard (own per-tensor scale), so fc1 is close, not equal
+            "h": relf(h, h_ref.chunk(world, 1)[rank]),
+            "y": relf(y, y_ref.chunk(world, 0)[rank]),
+            "dx": relf(xd.grad, dx_ref.chunk(world, 0)[rank]),
+            "dw1": relf(fc1.weight.grad, dw1_ref.chunk(world, 0)[rank]),
+            "dw2": relf(fc2.weight.grad, dw2_ref.chunk(world, 1)[rank]),
+        }
+        # quantized gather == quantize(gathered): check the activation codes directly
+        from minitransformer_b200.module.linear import _QuantizedLinear
+        qg = _QuantizedLinear.quantize_optionally_allgather(p.quantize_op, x.chunk(world, 0)[rank].contiguous(), p.x_params,
+                                                            True, True, True, dist.group.WORLD)
+        qf = p.quantize_op.quantize(x, p.x_params, return_transpose=True)
+        same = (torch.equal(qg.data, qf.data) and torch.equal(qg.scale.view(torch.uint8), qf.scale.view(torch.uint8))
+                and torch.equal(qg.data_t, qf.data_t)
+                and torch.equal(qg.scale_t.view(torch.uint8), qf.scale_t.view(torch.uint8)[: H])
+                and float(qg.global_amax_row) == float(qf.global_amax_row)
+                and float(qg.global_amax_col) == float(qf.global_amax_col))
+        result[rank] = (errs, bool(same), K.read_device_status())
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_nvfp4_mlp_matches_single_gpu():
+    world = 2
+    mgr = mp.Manager()
+    result = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), result), nprocs=world, join=True)
+    for rank in range(world):
+        errs, same, status = result[rank]
+        assert same, "gathered quantized shards differ from quantizing the gathered tensor"
+        assert status == 0
+        # FP4 quantization noise of a different weight scale dominates; 0.134 is the error of
+        # NVFP4 against an unquantized product, so 0.05 separates 'same recipe' from 'wrong result'
+        assert all(e < 0.05 for e in errs.values()), errs
