@@ -62,6 +62,8 @@ struct GemmArgs {
   int64_t d_group_stride;        // MODE_GROUPED_K: elements between consecutive group outputs
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
+  int sf_buffers;                // pair kernel: 1 or 2 alternating sets of scale-factor columns in tensor memory
+  int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
 };
 
 template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
@@ -443,7 +445,8 @@ struct PairCfg {
   static constexpr int TMEM_ACC = 0;
   static constexpr int TMEM_SFA = P_BLOCK_N;
   static constexpr int TMEM_SFB = TMEM_SFA + 4 * CH;
-  static_assert(TMEM_SFB + 8 * CH <= G_TMEM_COLS, "tensor memory over-subscribed");
+  static constexpr int TMEM_SF_SET = 12 * CH;   // columns of one set of scale factors (A: 4*CH, B: 8*CH)
+  static_assert(TMEM_SFA + 2 * TMEM_SF_SET <= G_TMEM_COLS, "tensor memory over-subscribed");
   static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory over-subscribed");
 };
 
@@ -478,6 +481,22 @@ __device__ __forceinline__ uint32_t make_idesc_pair(int format, int sf_id) {
   d |= static_cast<uint32_t>(P_BLOCK_N >> 3) << 17;
   d |= static_cast<uint32_t>(256 >> 4) << 24;  // M = 256 across the pair
   return d;
+}
+
+// Tile order of the pair kernel: bands of `band` tile rows; inside a band the row index runs
+// fastest, so CTAs that run together share the B tile and cycle through a few A tiles.
+__device__ __forceinline__ void pair_tile_coord(const GemmArgs& a, int tile, int& mb, int& nb) {
+  if (a.band <= 0) {
+    nb = tile / a.tiles_m;
+    mb = tile - nb * a.tiles_m;
+    return;
+  }
+  const int per_band = a.band * a.tiles_n;
+  const int b = tile / per_band;
+  const int r = tile - b * per_band;
+  const int rows = min(a.band, a.tiles_m - b * a.band);
+  nb = r / rows;
+  mb = b * a.band + (r - nb * rows);
 }
 
 template <int kFormat, int STAGES>
@@ -534,7 +553,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       uint32_t it = 0;
       bool alive = true;
       for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs) {
-        const int nb = tile / a.tiles_m, mb = tile - nb * a.tiles_m;
+        int mb, nb;
+        pair_tile_coord(a, tile, mb, nb);
         const int32_t a_row = mb * 256 + (int)rank * 128;
         const int32_t b_row = nb * 256 + (int)rank * 128;
         const int32_t sfa_chunk0 = (int32_t)((int64_t)(mb * 2 + (int)rank) * a.kc_a);
@@ -572,22 +592,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
           tc_fence_after();
+          // alternate between two sets of scale-factor columns so that the copy for this step
+          // does not have to wait for the previous step's MMAs to finish reading theirs
+          const uint32_t sf_set = (a.sf_buffers > 1 && (it & 1)) ? Cfg::TMEM_SF_SET : 0;
 #pragma unroll
           for (int c = 0; c < CH; ++c)
-            tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
+            tc_copy_sf_pair(tmem_base + sf_set + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int c = 0; c < CH; ++c)
-              tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFB + 4 * (c * 2 + h),
+              tc_copy_sf_pair(tmem_base + sf_set + Cfg::TMEM_SFB + 4 * (c * 2 + h),
                               umma_desc_sf(sfb_base + s * Cfg::SFB_BYTES + (h * CH + c) * 512));
           const uint64_t adesc = umma_desc_sw128(a_base + s * Cfg::A_BYTES);
           const uint64_t bdesc = umma_desc_sw128(b_base + s * Cfg::B_BYTES);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t idesc = make_idesc_pair(kFormat, j);
-            const uint32_t sfa_t = tmem_base + Cfg::TMEM_SFA + (kFormat == FMT_NVFP4 ? 4 * j : 0);
-            const uint32_t sfb_t = tmem_base + Cfg::TMEM_SFB + (kFormat == FMT_NVFP4 ? 8 * j : 0);
+            const uint32_t sfa_t = tmem_base + sf_set + Cfg::TMEM_SFA + (kFormat == FMT_NVFP4 ? 4 * j : 0);
+            const uint32_t sfb_t = tmem_base + sf_set + Cfg::TMEM_SFB + (kFormat == FMT_NVFP4 ? 8 * j : 0);
             issue_mma_pair<kFormat>(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, (k > 0 || j > 0) ? 1u : 0u);
           }
           tc_commit_pair(&empty_bar[s], 3);
@@ -608,7 +631,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     uint32_t tile_it = 0;
     bool alive = true;
     for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
-      const int nb = tile / a.tiles_m, mb = tile - nb * a.tiles_m;
+      int mb, nb;
+      pair_tile_coord(a, tile, mb, nb);
       if (!mbar_wait_bounded(acc_full, tile_it & 1, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
       tc_fence_after();
       const int64_t row0 = (int64_t)mb * 256 + rank * 128 + q * 32;
@@ -855,6 +879,11 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
     const size_t es = d_dtype == MT_F32 ? 4 : 2;
     static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
     if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
+    static int sf_buffers = -1, band = -1;  // MT_GEMM_SFBUF, MT_GEMM_BAND: tuning aids
+    if (sf_buffers < 0) { const char* e = getenv("MT_GEMM_SFBUF"); sf_buffers = e ? atoi(e) : 2; }
+    if (band < 0) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : 8; }
+    args.sf_buffers = sf_buffers;
+    args.band = band;
     CUtensorMap md = ma;
     args.tma_store = allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16);
     if (args.tma_store) {
