@@ -62,7 +62,7 @@ struct GemmArgs {
   int64_t d_group_stride;        // MODE_GROUPED_K: elements between consecutive group outputs
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
-  int sf_buffers;                // pair kernel: 1 or 2 alternating sets of scale-factor columns in tensor memory
+  int debug_skip_store;          // tuning aid: the epilogue drains tensor memory but writes nothing
   int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
 };
 
@@ -408,45 +408,52 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
 
 
 // ------------------------------------------------------------------------------------------
-// CTA-pair kernel (cta_group::2): a cluster of two CTAs computes a 256 x 256 output tile.
+// CTA-pair kernel (cta_group::2): a cluster of two CTAs computes a 256 x BN output tile,
+// BN = 256 (one accumulator) or 192 (two accumulators: the epilogue of a tile overlaps the
+// MMAs of the next one; 2 * 192 accumulator columns + 48 scale-factor columns fit the 512
+// columns of tensor memory).
 // CTA r of the pair owns rows [128 r, 128 r + 128) of the tile (its A rows, its half of the
-// accumulator in its own tensor memory) and loads rows [128 r, +128) of the B tile; the
+// accumulator in its own tensor memory) and loads rows [r * BN/2, +BN/2) of the B tile; the
 // tensor cores of both SMs read both halves of B, so each byte of B is fetched from L2 and
 // written to shared memory once per pair. Scale factors: each CTA loads the A scales of its
-// own rows and the B scales of all 256 columns. The leader (rank 0) waits on one "full"
-// barrier that both CTAs' TMA loads signal, copies scale factors and issues the MMAs for
-// both SMs; tcgen05.commit signals the "empty" and "accumulator full" barriers in both CTAs.
-// No load is multicast.
+// own rows and the B scales of the two 128-row chunks the tile's columns touch (a 192-wide
+// tile starts 0 or 64 rows into a chunk: the MMA is pointed 0 or 2 tensor-memory columns
+// into the copied chunks). The leader (rank 0) waits on one "full" barrier that both CTAs' TMA
+// loads signal, copies scale factors and issues the MMAs for both SMs; tcgen05.commit signals
+// the "empty" and "accumulator full" barriers in both CTAs. No load is multicast.
 // ------------------------------------------------------------------------------------------
 constexpr int P_EPI_WARPS = 8;                       // two warps per tensor-memory lane quarter
 constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;     // producer warp + MMA warp + epilogue warps
-constexpr int P_BLOCK_N = 256;
 
-template <int kFormat, int STAGES>
+template <int kFormat, int BN, int STAGES>
 struct PairCfg {
+  static_assert(BN == 256 || BN == 192, "pair tile width");
   static constexpr int CH = (kFormat == FMT_NVFP4) ? 4 : 1;
+  static constexpr int ACC = (BN == 256) ? 1 : 2;              // accumulator buffers
+  static constexpr int NSB = 2;                                // 128-row B scale chunks per tile
   static constexpr int A_BYTES = G_BLOCK_M * G_BLOCK_KB;       // 128 rows of A
-  static constexpr int B_BYTES = 128 * G_BLOCK_KB;             // this CTA's 128 rows of B
+  static constexpr int B_BYTES = (BN / 2) * G_BLOCK_KB;        // this CTA's rows of B
   static constexpr int SFA_BYTES = CH * 512;
-  static constexpr int SFB_BYTES = 2 * CH * 512;               // all 256 columns
+  static constexpr int SFB_BYTES = NSB * CH * 512;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
-  // 4 KiB output staging per epilogue warp; 1024-byte aligned so the 128-byte swizzle pattern
-  // of the TMA store lines up with the row index used when filling it
+  // one 4 KiB output staging buffer per epilogue warp (a second buffer per warp would cost a
+  // pipeline stage, which measured slower); 1024-byte aligned so the swizzle pattern of the
+  // TMA store lines up with the row index used when filling it
   static constexpr int OFF_EPI = (OFF_SFB + STAGES * SFB_BYTES + 1023) / 1024 * 1024;
   static constexpr int EPI_BYTES = P_EPI_WARPS * 4096;
   static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 2;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 * ACC;
   static constexpr int SMEM_BYTES = OFF_BAR + NUM_BARS * 8 + 16;
   static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
   static constexpr int TMEM_ACC = 0;
-  static constexpr int TMEM_SFA = P_BLOCK_N;
+  static constexpr int TMEM_SFA = ACC * BN;
   static constexpr int TMEM_SFB = TMEM_SFA + 4 * CH;
-  static constexpr int TMEM_SF_SET = 12 * CH;   // columns of one set of scale factors (A: 4*CH, B: 8*CH)
-  static_assert(TMEM_SFA + 2 * TMEM_SF_SET <= G_TMEM_COLS, "tensor memory over-subscribed");
+  static_assert(B_BYTES % 1024 == 0, "B stage must keep the 1024-byte swizzle alignment");
+  static_assert(TMEM_SFB + 4 * NSB * CH <= G_TMEM_COLS, "tensor memory over-subscribed");
   static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory over-subscribed");
 };
 
@@ -468,7 +475,7 @@ __device__ __forceinline__ void issue_mma_pair(uint32_t tmem_d, uint64_t adesc, 
   }
 }
 
-__device__ __forceinline__ uint32_t make_idesc_pair(int format, int sf_id) {
+__device__ __forceinline__ uint32_t make_idesc_pair(int format, int block_n, int sf_id) {
   uint32_t d = 0;
   if (format == FMT_NVFP4) {
     d |= 1u << 7;
@@ -478,17 +485,23 @@ __device__ __forceinline__ uint32_t make_idesc_pair(int format, int sf_id) {
     d |= static_cast<uint32_t>(sf_id) << 4;
     d |= static_cast<uint32_t>(sf_id) << 29;
   }
-  d |= static_cast<uint32_t>(P_BLOCK_N >> 3) << 17;
+  d |= static_cast<uint32_t>(block_n >> 3) << 17;
   d |= static_cast<uint32_t>(256 >> 4) << 24;  // M = 256 across the pair
   return d;
 }
 
-// Tile order of the pair kernel: bands of `band` tile rows; inside a band the row index runs
-// fastest, so CTAs that run together share the B tile and cycle through a few A tiles.
+// Tile order of the pair kernel. band < 0: column index fastest (CTAs that run together share
+// the A tile and sweep B); band == 0: row index fastest; band > 0: bands of `band` tile rows,
+// row index fastest inside a band.
 __device__ __forceinline__ void pair_tile_coord(const GemmArgs& a, int tile, int& mb, int& nb) {
-  if (a.band <= 0) {
+  if (a.band == 0) {
     nb = tile / a.tiles_m;
     mb = tile - nb * a.tiles_m;
+    return;
+  }
+  if (a.band < 0) {
+    mb = tile / a.tiles_n;
+    nb = tile - mb * a.tiles_n;
     return;
   }
   const int per_band = a.band * a.tiles_n;
@@ -499,21 +512,26 @@ __device__ __forceinline__ void pair_tile_coord(const GemmArgs& a, int tile, int
   mb = b * a.band + (r - nb * rows);
 }
 
-template <int kFormat, int STAGES>
+__device__ __forceinline__ float bias_at(const GemmArgs& a, int64_t col) {
+  return (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col]
+                                  : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col]);
+}
+
+template <int kFormat, int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                  const __grid_constant__ CUtensorMap map_sfa,
                                  const __grid_constant__ CUtensorMap map_sfb,
                                  const __grid_constant__ CUtensorMap map_d, const GemmArgs a) {
-  using Cfg = PairCfg<kFormat, STAGES>;
-  constexpr int CH = Cfg::CH;
+  using Cfg = PairCfg<kFormat, BN, STAGES>;
+  constexpr int CH = Cfg::CH, ACC = Cfg::ACC, NSB = Cfg::NSB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* full_bar = bars;                 // used in the leader only (both CTAs' loads signal it)
-  uint64_t* empty_bar = bars + STAGES;       // one set per CTA, signalled by the leader's commit
-  uint64_t* acc_full = bars + 2 * STAGES;    // one per CTA, signalled by the leader's commit
-  uint64_t* acc_empty = bars + 2 * STAGES + 1;  // leader only: 2 x P_EPI_WARPS arrivals
+  uint64_t* full_bar = bars;                        // used in the leader only (both CTAs' loads signal it)
+  uint64_t* empty_bar = bars + STAGES;              // one set per CTA, signalled by the leader's commit
+  uint64_t* acc_full = bars + 2 * STAGES;           // per CTA and accumulator, signalled by the leader's commit
+  uint64_t* acc_empty = bars + 2 * STAGES + ACC;    // leader only: 2 x P_EPI_WARPS arrivals each
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -525,8 +543,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 2 * P_EPI_WARPS);
+    for (int i = 0; i < ACC; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 2 * P_EPI_WARPS); }
     mbar_fence_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -556,9 +573,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         int mb, nb;
         pair_tile_coord(a, tile, mb, nb);
         const int32_t a_row = mb * 256 + (int)rank * 128;
-        const int32_t b_row = nb * 256 + (int)rank * 128;
+        const int32_t b_row = nb * BN + (int)rank * (BN / 2);
         const int32_t sfa_chunk0 = (int32_t)((int64_t)(mb * 2 + (int)rank) * a.kc_a);
-        const int32_t sfb_chunk0 = (int32_t)((int64_t)(nb * 2) * a.kc_b);
+        const int32_t sfb_rb0 = (nb * BN) >> 7;   // first 128-row chunk of B scales the tile touches
         for (int k = 0; k < num_k; ++k, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -569,9 +586,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, kx, a_row);
           tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, kx, b_row);
           tma_load_2d_pair(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, &map_sfa, bar, 0, sfa_chunk0 + k * CH);
-          tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES, &map_sfb, bar, 0, sfb_chunk0 + k * CH);
-          tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + CH * 512, &map_sfb, bar, 0,
-                           sfb_chunk0 + (int32_t)a.kc_b + k * CH);
+#pragma unroll
+          for (int h = 0; h < NSB; ++h)
+            tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + h * CH * 512, &map_sfb, bar, 0,
+                             (int32_t)((int64_t)(sfb_rb0 + h) * a.kc_b) + k * CH);
         }
       }
     }
@@ -584,67 +602,73 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
       const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
       for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
-        if (!mbar_wait_bounded(acc_empty, (tile_it & 1) ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
+        int mb, nb;
+        pair_tile_coord(a, tile, mb, nb);
+        const int as = tile_it % ACC;
+        const uint32_t aph = (tile_it / ACC) & 1;
+        if (!mbar_wait_bounded(&acc_empty[as], aph ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC;
+        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + as * BN;
+        const uint32_t sfb_col_off = ((nb * BN) & 127) >> 5;   // tile start inside its first scale chunk, in columns
         for (int k = 0; k < num_k; ++k, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
           tc_fence_after();
-          // alternate between two sets of scale-factor columns so that the copy for this step
-          // does not have to wait for the previous step's MMAs to finish reading theirs
-          const uint32_t sf_set = (a.sf_buffers > 1 && (it & 1)) ? Cfg::TMEM_SF_SET : 0;
 #pragma unroll
           for (int c = 0; c < CH; ++c)
-            tc_copy_sf_pair(tmem_base + sf_set + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
+            tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < NSB; ++h)
 #pragma unroll
             for (int c = 0; c < CH; ++c)
-              tc_copy_sf_pair(tmem_base + sf_set + Cfg::TMEM_SFB + 4 * (c * 2 + h),
+              tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFB + 4 * (c * NSB + h),
                               umma_desc_sf(sfb_base + s * Cfg::SFB_BYTES + (h * CH + c) * 512));
           const uint64_t adesc = umma_desc_sw128(a_base + s * Cfg::A_BYTES);
           const uint64_t bdesc = umma_desc_sw128(b_base + s * Cfg::B_BYTES);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t idesc = make_idesc_pair(kFormat, j);
-            const uint32_t sfa_t = tmem_base + sf_set + Cfg::TMEM_SFA + (kFormat == FMT_NVFP4 ? 4 * j : 0);
-            const uint32_t sfb_t = tmem_base + sf_set + Cfg::TMEM_SFB + (kFormat == FMT_NVFP4 ? 8 * j : 0);
+            const uint32_t idesc = make_idesc_pair(kFormat, BN, j);
+            const uint32_t sfa_t = tmem_base + Cfg::TMEM_SFA + (kFormat == FMT_NVFP4 ? 4 * j : 0);
+            const uint32_t sfb_t = tmem_base + Cfg::TMEM_SFB + (kFormat == FMT_NVFP4 ? 4 * NSB * j : 0) + sfb_col_off;
             issue_mma_pair<kFormat>(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, (k > 0 || j > 0) ? 1u : 0u);
           }
           tc_commit_pair(&empty_bar[s], 3);
         }
-        if (alive) tc_commit_pair(acc_full, 3);
+        if (alive) tc_commit_pair(&acc_full[as], 3);
       }
     }
     __syncwarp();
   } else {
-    // ================= epilogue (both CTAs): warp e handles lane quarter e % 4, column half e / 4 =================
+    // ======== epilogue (both CTAs): warp e reads lane quarter e % 4; columns [0,128) or [128,BN) ========
     const int e = warp - 2;
     const int q = warp & 3;          // hardware rule: a warp reads the lane quarter warp_id % 4
     const int half = (e >> 2) & 1;   // with 8 warps, quarters repeat after 4 warps
+    const int ncols = half ? BN - 128 : 128;   // 128, or 64 for the second half of a 192-wide tile
     float alpha = 1.0f;
     if (a.amax_a != nullptr && a.amax_b != nullptr)
       alpha = __fdiv_rn(__fmul_rn(*a.amax_a, *a.amax_b), 6.0f * 6.0f * 448.0f * 448.0f);
-    const uint32_t acc_empty_leader = map_to_cta(smem_u32(acc_empty), 0);
     uint32_t tile_it = 0;
     bool alive = true;
     for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
       int mb, nb;
       pair_tile_coord(a, tile, mb, nb);
-      if (!mbar_wait_bounded(acc_full, tile_it & 1, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
+      const int as = tile_it % ACC;
+      const uint32_t aph = (tile_it / ACC) & 1;
+      const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[as]), 0);
+      if (!mbar_wait_bounded(&acc_full[as], aph, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
       tc_fence_after();
       const int64_t row0 = (int64_t)mb * 256 + rank * 128 + q * 32;
       const int64_t row = row0 + lane;
       const bool row_ok = row < a.M;
-      const int64_t colw = (int64_t)nb * P_BLOCK_N + half * 128;  // first of this warp's 128 columns
+      const int64_t colw = (int64_t)nb * BN + half * 128;  // first of this warp's columns
+      const uint32_t tmem_w = tmem_base + Cfg::TMEM_ACC + as * BN + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
       if (!a.tma_store) {
         // direct path (unaligned outputs, bf16 accumulate): registers -> global, 32 columns at a time
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c * 32 < ncols; ++c) {
           uint32_t r[32];
-          tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + (static_cast<uint32_t>(q * 32) << 16) + half * 128 + c * 32, r);
+          tc_ld_32x32(tmem_w + c * 32, r);
           tc_wait_ld();
           const int64_t col0 = colw + c * 32;
           if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, num_k > 0, row * a.ldd + col0, col0);
@@ -654,16 +678,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         continue;
       }
-      // Pull this warp's 32 x 128 accumulator block into registers and hand tensor memory
-      // back to the MMA issuer at once; conversion and stores overlap the next tile's MMAs.
+      // Pull this warp's accumulator block into registers and hand tensor memory back to the
+      // MMA issuer at once; conversion and stores overlap the MMAs that follow.
       uint32_t acc[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c)
-        tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + (static_cast<uint32_t>(q * 32) << 16) + half * 128 + c * 32, acc[c]);
+        if (BN == 256 || c < 2 || half == 0) tc_ld_32x32(tmem_w + c * 32, acc[c]);
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      if (a.debug_skip_store) continue;
 
       uint8_t* stage = smem + Cfg::OFF_EPI + e * 4096;   // 32 rows x 128 bytes, 128-byte swizzle
       const uint32_t swz = lane & 7;
@@ -671,6 +696,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       if (a.d_dtype == MT_BF16) {
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {           // 64 columns = 128 bytes per row
+          if (ch * 64 >= ncols) break;
           if (lane == 0) bulk_wait_read_all();     // the previous store has drained the buffer
           __syncwarp();
 #pragma unroll
@@ -683,8 +709,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
               float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
               if (a.bias != nullptr) {
                 const int64_t gc = colw + col;
-                if (gc < a.N) v0 += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[gc] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[gc]);
-                if (gc + 1 < a.N) v1 += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[gc + 1] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[gc + 1]);
+                if (gc < a.N) v0 += bias_at(a, gc);
+                if (gc + 1 < a.N) v1 += bias_at(a, gc + 1);
               }
               __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
               w[t] = *reinterpret_cast<uint32_t*>(&h);
@@ -701,6 +727,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       } else {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {           // 32 fp32 columns = 128 bytes per row
+          if (ch * 32 >= ncols) break;
           if (lane == 0) bulk_wait_read_all();
           __syncwarp();
 #pragma unroll
@@ -711,7 +738,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
               v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[ch][j * 4 + t])) : 0.0f;
               if (a.bias != nullptr) {
                 const int64_t gc = colw + ch * 32 + j * 4 + t;
-                if (gc < a.N) v[t] += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[gc] : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[gc]);
+                if (gc < a.N) v[t] += bias_at(a, gc);
               }
             }
             *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
@@ -772,11 +799,11 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
 
 static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
 
-template <int kFormat, int STAGES>
+template <int kFormat, int BN, int STAGES>
 static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa,
                             const CUtensorMap& msb, const CUtensorMap& md, const GemmArgs& args, cudaStream_t st) {
-  using Cfg = PairCfg<kFormat, STAGES>;
-  auto kern = gemm_blockscaled_pair_kernel<kFormat, STAGES>;
+  using Cfg = PairCfg<kFormat, BN, STAGES>;
+  auto kern = gemm_blockscaled_pair_kernel<kFormat, BN, STAGES>;
   static int max_pairs = -1;
   if (max_pairs < 0) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
@@ -857,15 +884,26 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   }
   // K == 0 never reaches this point; tensor maps below need K_bytes >= 16
   if (use_pair && M > G_BLOCK_M && N > 128) {
-    args.tiles_m = (int)((M + 255) / 256);
-    args.tiles_n = (int)((N + 255) / 256);
+    // Tile width: 256 by default. The 192-wide variant (two accumulators, epilogue overlapped
+    // with the next tile's MMAs) measured no faster on the benchmark shapes because the main
+    // loop is bound by shared-memory bandwidth either way; MT_GEMM_PAIR_N=192 selects it.
+    static int forced_bn = -1, band = -2;
+    if (forced_bn < 0) { const char* e = getenv("MT_GEMM_PAIR_N"); forced_bn = e ? atoi(e) : 0; }
+    if (band == -2) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : -1; }
+    const int64_t tm = (M + 255) / 256;
+    int pbn = 256;
+    if (forced_bn == 192 || forced_bn == 256) pbn = forced_bn;
+    args.tiles_m = (int)tm;
+    args.tiles_n = (int)((N + pbn - 1) / pbn);
     args.num_tiles = args.tiles_m * args.tiles_n;
+    args.band = band;
+    { static int skip = -1; if (skip < 0) { const char* e = getenv("MT_GEMM_DEBUG_SKIP_STORE"); skip = e ? atoi(e) : 0; } args.debug_skip_store = skip; }
     CUtensorMap ma, mb, msa, msb;
     int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K_bytes, (uint64_t)M, (uint64_t)K_bytes,
                                 G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != MT_OK) return rc;
     rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)K_bytes, (uint64_t)N, (uint64_t)K_bytes,
-                            G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+                            G_BLOCK_KB, (uint32_t)(pbn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != MT_OK) return rc;
     const uint32_t ch = format == FMT_NVFP4 ? 4 : 1;
     rc = make_tensor_map_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sa, 128, (uint64_t)(args.rb_a * args.kc_a), 512, 128, ch,
@@ -879,21 +917,19 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
     const size_t es = d_dtype == MT_F32 ? 4 : 2;
     static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
     if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
-    static int sf_buffers = -1, band = -1;  // MT_GEMM_SFBUF, MT_GEMM_BAND: tuning aids
-    if (sf_buffers < 0) { const char* e = getenv("MT_GEMM_SFBUF"); sf_buffers = e ? atoi(e) : 2; }
-    if (band < 0) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : 8; }
-    args.sf_buffers = sf_buffers;
-    args.band = band;
     CUtensorMap md = ma;
     args.tma_store = allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16);
     if (args.tma_store) {
-      rc = make_tensor_map_2d(&md, d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                              (int)es, d, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * es, d_dtype == MT_F32 ? 32 : 64, 32,
+      const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+      rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * es, d_dtype == MT_F32 ? 32 : 64, 32,
                               CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc != MT_OK) return rc;
     }
-    return format == FMT_NVFP4 ? launch_gemm_pair<FMT_NVFP4, 5>(ma, mb, msa, msb, md, args, st)
-                               : launch_gemm_pair<FMT_MXFP8, 5>(ma, mb, msa, msb, md, args, st);
+    if (format == FMT_NVFP4)
+      return pbn == 192 ? launch_gemm_pair<FMT_NVFP4, 192, 5>(ma, mb, msa, msb, md, args, st)
+                        : launch_gemm_pair<FMT_NVFP4, 256, 5>(ma, mb, msa, msb, md, args, st);
+    return pbn == 192 ? launch_gemm_pair<FMT_MXFP8, 192, 5>(ma, mb, msa, msb, md, args, st)
+                      : launch_gemm_pair<FMT_MXFP8, 256, 5>(ma, mb, msa, msb, md, args, st);
   }
   const int bn = pick_block_n(N);
   args.tiles_m = (int)((M + G_BLOCK_M - 1) / G_BLOCK_M);

@@ -204,6 +204,8 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the bulk groups of this thread have finished READING shared memory.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Same, but lets the most recent group stay in flight.
+__device__ __forceinline__ void bulk_wait_read_all_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- thread-block clusters / CTA pairs (cta_group::2) ----
