@@ -183,6 +183,83 @@ __device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_
   }
 }
 
+__device__ __forceinline__ float bias_at(const GemmArgs& a, int64_t col) {
+  return (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col]
+                                  : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col]);
+}
+
+// One warp's 32 rows x `ncols` (<= 128) accumulator block, already in registers (acc[c][i] =
+// column 32c + i of this lane's row), -> alpha / bias -> bf16 or fp32 -> a 4 KiB shared-memory
+// buffer in the 128-byte-swizzled layout -> TMA store (or TMA add-reduction for fp32
+// accumulation) of 64 (bf16) or 32 (fp32) columns at a time. `row0` / `colw` are the block's
+// first row / column in the tensor map's coordinates; rows and columns beyond the map's
+// bounds are clipped by the hardware.
+__device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUtensorMap* map_d,
+                                                   const uint32_t (&acc)[4][32], int ncols, uint8_t* stage, int lane,
+                                                   int64_t row0, int64_t map_rows, int64_t colw, float alpha,
+                                                   bool has_k) {
+  const uint32_t swz = lane & 7;
+  if (a.d_dtype == MT_BF16) {
+#pragma unroll
+    for (int ch = 0; ch < 2; ++ch) {           // 64 columns = 128 bytes per row
+      if (ch * 64 >= ncols) break;
+      if (lane == 0) bulk_wait_read_all();     // the previous store has drained the buffer
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {            // 16-byte chunk j = columns 8j .. 8j+7
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int col = ch * 64 + j * 8 + t * 2;
+          float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
+          float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
+          if (a.bias != nullptr) {
+            const int64_t gc = colw + col;
+            if (gc < a.N) v0 += bias_at(a, gc);
+            if (gc + 1 < a.N) v1 += bias_at(a, gc + 1);
+          }
+          __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+          w[t] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 < map_rows && colw + ch * 64 < a.N) {
+        tma_store_2d(map_d, stage, (int32_t)(colw + ch * 64), (int32_t)row0);
+        bulk_commit_group();
+      }
+    }
+  } else {
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {           // 32 fp32 columns = 128 bytes per row
+      if (ch * 32 >= ncols) break;
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[ch][j * 4 + t])) : 0.0f;
+          if (a.bias != nullptr) {
+            const int64_t gc = colw + ch * 32 + j * 4 + t;
+            if (gc < a.N) v[t] += bias_at(a, gc);
+          }
+        }
+        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 < map_rows && colw + ch * 32 < a.N) {
+        if (a.accumulate) tma_reduce_add_2d(map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
+        else tma_store_2d(map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
+        bulk_commit_group();
+      }
+    }
+  }
+}
+
 struct TileCoord {
   int64_t a_row0;      // first row of the A tile (TMA y coordinate)
   int64_t b_row0;      // first row of the B tile
@@ -512,11 +589,6 @@ __device__ __forceinline__ void pair_tile_coord(const GemmArgs& a, int tile, int
   mb = b * a.band + (r - nb * rows);
 }
 
-__device__ __forceinline__ float bias_at(const GemmArgs& a, int64_t col) {
-  return (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col]
-                                  : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col]);
-}
-
 template <int kFormat, int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -690,68 +762,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       if (a.debug_skip_store) continue;
 
-      uint8_t* stage = smem + Cfg::OFF_EPI + e * 4096;   // 32 rows x 128 bytes, 128-byte swizzle
-      const uint32_t swz = lane & 7;
-      const bool has_k = num_k > 0;
-      if (a.d_dtype == MT_BF16) {
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {           // 64 columns = 128 bytes per row
-          if (ch * 64 >= ncols) break;
-          if (lane == 0) bulk_wait_read_all();     // the previous store has drained the buffer
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {            // 16-byte chunk j = columns 8j .. 8j+7
-            uint32_t w[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const int col = ch * 64 + j * 8 + t * 2;
-              float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
-              float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
-              if (a.bias != nullptr) {
-                const int64_t gc = colw + col;
-                if (gc < a.N) v0 += bias_at(a, gc);
-                if (gc + 1 < a.N) v1 += bias_at(a, gc + 1);
-              }
-              __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-              w[t] = *reinterpret_cast<uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && row0 < a.M && colw + ch * 64 < a.N) {
-            tma_store_2d(&map_d, stage, (int32_t)(colw + ch * 64), (int32_t)row0);
-            bulk_commit_group();
-          }
-        }
-      } else {
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {           // 32 fp32 columns = 128 bytes per row
-          if (ch * 32 >= ncols) break;
-          if (lane == 0) bulk_wait_read_all();
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float v[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[ch][j * 4 + t])) : 0.0f;
-              if (a.bias != nullptr) {
-                const int64_t gc = colw + ch * 32 + j * 4 + t;
-                if (gc < a.N) v[t] += bias_at(a, gc);
-              }
-            }
-            *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && row0 < a.M && colw + ch * 32 < a.N) {
-            if (a.accumulate) tma_reduce_add_2d(&map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
-            else tma_store_2d(&map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
-            bulk_commit_group();
-          }
-        }
-      }
+      store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, row0, a.M, colw, alpha,
+                         num_k > 0);
     }
   }
 
@@ -1041,7 +1053,9 @@ extern "C" {
 int64_t mt_grouped_scratch_bytes(int64_t rows, int64_t groups) {
   if (rows < 0 || groups < 0) return 0;
   const int64_t e = mt::grouped_entries_upper_bound(rows, groups);
-  return ((int64_t)sizeof(int64_t) * (groups + 1) + 2 * (int64_t)sizeof(int32_t) * e + 255) / 256 * 256;
+  // large enough for any grouped entry point: offsets + (row block, group) table for the GEMMs,
+  // 16-byte tile records for the transposed quantize
+  return ((int64_t)sizeof(int64_t) * (groups + 1) + 16 * e + 255) / 256 * 256;
 }
 
 int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
