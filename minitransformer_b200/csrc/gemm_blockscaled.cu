@@ -62,6 +62,7 @@ struct GemmArgs {
   int64_t d_group_stride;        // MODE_GROUPED_K: elements between consecutive group outputs
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
+  int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
   int debug_skip_store;          // tuning aid: the epilogue drains tensor memory but writes nothing
   int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
 };
@@ -589,6 +590,69 @@ __device__ __forceinline__ void pair_tile_coord(const GemmArgs& a, int tile, int
   mb = b * a.band + (r - nb * rows);
 }
 
+// Tile of the pair kernel in every mode: the TileCoord fields (a_row0 = first of the tile's 256
+// rows) plus the row of accumulator row 0 in the output tensor map (grouped-K outputs are one
+// map over all groups' matrices stacked along rows) and whether d_row_hi coincides with the
+// map's last row, so that the map's own clipping may stand in for the row-range test.
+struct PairTile : TileCoord {
+  int64_t d_map_row0;
+  bool hi_is_end;
+};
+
+template <int kFormat, int BN>
+__device__ __forceinline__ PairTile pair_tile(const GemmArgs& a, int tile) {
+  constexpr int CH = (kFormat == FMT_NVFP4) ? 4 : 1;
+  PairTile t;
+  t.a_k_byte0 = t.b_k_byte0 = 0;
+  t.num_k = (int)((a.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB);
+  t.sfa_kc0 = t.sfb_kc0 = 0;
+  t.d_base = 0;
+  if (a.mode == MODE_DENSE) {
+    int mb, nb;
+    pair_tile_coord(a, tile, mb, nb);
+    t.a_row0 = (int64_t)mb * 256;
+    t.b_row0 = (int64_t)nb * BN;
+    t.d_row_lo = 0;
+    t.d_row_hi = a.M;
+    t.d_map_row0 = t.a_row0;
+    t.hi_is_end = true;
+  } else if (a.mode == MODE_GROUPED_ROWS) {
+    // entries (256-row block, group), column block fastest: pairs that run together share A
+    const int e = tile / a.tiles_n, nb = tile - e * a.tiles_n;
+    const int g = a.tile_group[e];
+    t.a_row0 = (int64_t)a.tile_rb[e] * 256;
+    t.b_row0 = (int64_t)g * a.b_group_rows + (int64_t)nb * BN;
+    t.b_k_byte0 = (int64_t)g * a.b_group_k_bytes;
+    t.sfb_kc0 = t.b_k_byte0 / G_BLOCK_KB * CH;
+    t.d_row_lo = a.group_offsets[g];
+    t.d_row_hi = a.group_offsets[g + 1];
+    t.d_col0 = (int64_t)nb * BN;
+    t.d_map_row0 = t.a_row0;
+    t.hi_is_end = t.d_row_hi == a.M;
+  } else {
+    const int per_group = a.tiles_m * a.tiles_n;
+    const int g = tile / per_group;
+    const int r = tile - g * per_group;
+    const int mb = r / a.tiles_n, nb = r - mb * a.tiles_n;
+    const int64_t e0 = a.group_offsets[g], e1 = a.group_offsets[g + 1];
+    t.a_row0 = (int64_t)mb * 256;
+    t.b_row0 = (int64_t)nb * BN;
+    t.a_k_byte0 = t.b_k_byte0 = e0 * 2 / a.k_elems_per_byte_x2;
+    t.num_k = (int)(((e1 - e0) * 2 / a.k_elems_per_byte_x2 + G_BLOCK_KB - 1) / G_BLOCK_KB);
+    t.sfa_kc0 = t.sfb_kc0 = t.a_k_byte0 / G_BLOCK_KB * CH;
+    t.d_row_lo = 0;
+    t.d_row_hi = a.M;
+    t.d_base = (int64_t)g * a.d_group_stride;
+    t.d_map_row0 = (int64_t)g * a.M + t.a_row0;
+    t.hi_is_end = g == a.num_groups - 1;
+  }
+  if (a.mode != MODE_GROUPED_ROWS) t.d_col0 = t.b_row0;
+  t.d_row0 = t.a_row0;
+  t.sfa_rb = t.a_row0 / 128;
+  t.sfb_rb = t.b_row0 / 128;
+  return t;
+}
+
 template <int kFormat, int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -634,7 +698,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int num_k = (int)((a.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB);
 
   if (warp == 0) {
     // ================= TMA producer (one per CTA) =================
@@ -642,12 +705,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       uint32_t it = 0;
       bool alive = true;
       for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs) {
-        int mb, nb;
-        pair_tile_coord(a, tile, mb, nb);
-        const int32_t a_row = mb * 256 + (int)rank * 128;
-        const int32_t b_row = nb * BN + (int)rank * (BN / 2);
-        const int32_t sfa_chunk0 = (int32_t)((int64_t)(mb * 2 + (int)rank) * a.kc_a);
-        const int32_t sfb_rb0 = (nb * BN) >> 7;   // first 128-row chunk of B scales the tile touches
+        const PairTile t = pair_tile<kFormat, BN>(a, tile);
+        const int32_t a_row = (int32_t)t.a_row0 + (int)rank * 128;
+        const int32_t b_row = (int32_t)t.b_row0 + (int)rank * (BN / 2);
+        const int32_t sfa_chunk0 = (int32_t)((t.sfa_rb + (int)rank) * a.kc_a + t.sfa_kc0);
+        const int64_t sfb_rb0 = t.sfb_rb;   // first 128-row chunk of B scales the tile touches
+        const int32_t sfb_kc0 = (int32_t)t.sfb_kc0;
+        const int32_t a_kx0 = (int32_t)t.a_k_byte0, b_kx0 = (int32_t)t.b_k_byte0;
+        const int num_k = t.num_k;
         for (int k = 0; k < num_k; ++k, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -655,13 +720,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           if (leader) mbar_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
           const int32_t kx = k * G_BLOCK_KB;
-          tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, kx, a_row);
-          tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, kx, b_row);
+          tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, a_kx0 + kx, a_row);
+          tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, b_kx0 + kx, b_row);
           tma_load_2d_pair(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, &map_sfa, bar, 0, sfa_chunk0 + k * CH);
 #pragma unroll
           for (int h = 0; h < NSB; ++h)
             tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + h * CH * 512, &map_sfb, bar, 0,
-                             (int32_t)((int64_t)(sfb_rb0 + h) * a.kc_b) + k * CH);
+                             (int32_t)((sfb_rb0 + h) * a.kc_b) + sfb_kc0 + k * CH);
         }
       }
     }
@@ -674,14 +739,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
       const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
       for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
-        int mb, nb;
-        pair_tile_coord(a, tile, mb, nb);
+        const PairTile t = pair_tile<kFormat, BN>(a, tile);
+        const int num_k = t.num_k;
         const int as = tile_it % ACC;
         const uint32_t aph = (tile_it / ACC) & 1;
         if (!mbar_wait_bounded(&acc_empty[as], aph ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + as * BN;
-        const uint32_t sfb_col_off = ((nb * BN) & 127) >> 5;   // tile start inside its first scale chunk, in columns
+        const uint32_t sfb_col_off = ((uint32_t)t.b_row0 & 127u) >> 5;   // tile start inside its first scale chunk, in columns
         for (int k = 0; k < num_k; ++k, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -723,27 +788,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     uint32_t tile_it = 0;
     bool alive = true;
     for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
-      int mb, nb;
-      pair_tile_coord(a, tile, mb, nb);
+      const PairTile t = pair_tile<kFormat, BN>(a, tile);
+      const int num_k = t.num_k;
       const int as = tile_it % ACC;
       const uint32_t aph = (tile_it / ACC) & 1;
       const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[as]), 0);
       if (!mbar_wait_bounded(&acc_full[as], aph, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
       tc_fence_after();
-      const int64_t row0 = (int64_t)mb * 256 + rank * 128 + q * 32;
+      const int64_t row0 = t.d_row0 + rank * 128 + q * 32;   // first of this warp's 32 rows
       const int64_t row = row0 + lane;
-      const bool row_ok = row < a.M;
-      const int64_t colw = (int64_t)nb * BN + half * 128;  // first of this warp's columns
+      const bool row_ok = row >= t.d_row_lo && row < t.d_row_hi;
+      const int64_t colw = t.d_col0 + half * 128;            // first of this warp's columns
       const uint32_t tmem_w = tmem_base + Cfg::TMEM_ACC + as * BN + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
-      if (!a.tma_store) {
-        // direct path (unaligned outputs, bf16 accumulate): registers -> global, 32 columns at a time
+      // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
+      // so a block that straddles a group boundary takes the direct, row-masked path.
+      const bool staged = a.tma_store && row0 >= t.d_row_lo && (row0 + 32 <= t.d_row_hi || t.hi_is_end);
+      if (!staged) {
+        // direct path (unaligned outputs, bf16 accumulate, group edges): registers -> global
 #pragma unroll 1
         for (int c = 0; c * 32 < ncols; ++c) {
           uint32_t r[32];
           tc_ld_32x32(tmem_w + c * 32, r);
           tc_wait_ld();
           const int64_t col0 = colw + c * 32;
-          if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, num_k > 0, row * a.ldd + col0, col0);
+          if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, num_k > 0, t.d_base + row * a.ldd + col0, col0);
         }
         tc_fence_before();
         __syncwarp();
@@ -762,8 +830,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       if (a.debug_skip_store) continue;
 
-      store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, row0, a.M, colw, alpha,
-                         num_k > 0);
+      store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
+                         t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0);
     }
   }
 
@@ -838,6 +906,68 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
   return MT_OK;
 }
 
+// MT_GEMM_PAIR=0 forces the single-CTA kernel everywhere (tuning aid).
+static bool pair_enabled() {
+  static int use_pair = -1;
+  if (use_pair < 0) {
+    const char* e = getenv("MT_GEMM_PAIR");
+    use_pair = e ? atoi(e) : 1;
+  }
+  return use_pair != 0;
+}
+
+// MT_GEMM_PAIR_N = 192 or 256 overrides the pair kernel's tile width (tuning aid); 0 = heuristic.
+static int forced_pair_n() {
+  static int forced_bn = -1;
+  if (forced_bn < 0) { const char* e = getenv("MT_GEMM_PAIR_N"); forced_bn = e ? atoi(e) : 0; }
+  return (forced_bn == 192 || forced_bn == 256) ? forced_bn : 0;
+}
+
+// Builds the five tensor maps of the pair kernel and launches it. A is [a_rows, a_ld_bytes]
+// bytes, B is [b_rows, b_ld_bytes]; the output map covers [d_rows, d_cols] elements with row
+// pitch ldd. args carries everything else (mode, tile counts, scale-factor geometry).
+static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows, int64_t a_ld_bytes, const uint8_t* b,
+                           int64_t b_rows, int64_t b_ld_bytes, void* d, int d_dtype, int64_t d_rows, int64_t d_cols,
+                           int64_t ldd, int accumulate, GemmArgs& args, cudaStream_t st) {
+  static int band = -2;
+  if (band == -2) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : -1; }
+  args.band = band;
+  { static int skip = -1; if (skip < 0) { const char* e = getenv("MT_GEMM_DEBUG_SKIP_STORE"); skip = e ? atoi(e) : 0; } args.debug_skip_store = skip; }
+  CUtensorMap ma, mb, msa, msb;
+  int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)a_ld_bytes, (uint64_t)a_rows,
+                              (uint64_t)a_ld_bytes, G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)b_ld_bytes, (uint64_t)b_rows,
+                          (uint64_t)b_ld_bytes, G_BLOCK_KB, (uint32_t)(pbn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MT_OK) return rc;
+  const uint32_t ch = format == FMT_NVFP4 ? 4 : 1;
+  rc = make_tensor_map_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, args.sa, 128, (uint64_t)(args.rb_a * args.kc_a), 512, 128, ch,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != MT_OK) return rc;
+  rc = make_tensor_map_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, args.sb, 128, (uint64_t)(args.rb_b * args.kc_b), 512, 128, ch,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != MT_OK) return rc;
+  // Output through shared memory + TMA stores when the output rows are 16-byte aligned;
+  // fp32 accumulation uses the TMA add-reduction, bf16 accumulation the direct path.
+  const size_t es = d_dtype == MT_F32 ? 4 : 2;
+  static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
+  if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
+  CUtensorMap md = ma;
+  args.tma_store = allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16);
+  args.map_rows = d_rows;
+  if (args.tma_store) {
+    const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)d_cols, (uint64_t)d_rows, (uint64_t)ldd * es,
+                            d_dtype == MT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != MT_OK) return rc;
+  }
+  if (format == FMT_NVFP4)
+    return pbn == 192 ? launch_gemm_pair<FMT_NVFP4, 192, 5>(ma, mb, msa, msb, md, args, st)
+                      : launch_gemm_pair<FMT_NVFP4, 256, 5>(ma, mb, msa, msb, md, args, st);
+  return pbn == 192 ? launch_gemm_pair<FMT_MXFP8, 192, 5>(ma, mb, msa, msb, md, args, st)
+                    : launch_gemm_pair<FMT_MXFP8, 256, 5>(ma, mb, msa, msb, md, args, st);
+}
+
 // Environment override used while tuning: MT_GEMM_BLOCK_N = 128 or 256.
 static int pick_block_n(int64_t N) {
   static int forced = -1;
@@ -889,59 +1019,16 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
   args.mode = MODE_DENSE;
   args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
-  static int use_pair = -1;  // MT_GEMM_PAIR=0 forces the single-CTA kernel (tuning aid)
-  if (use_pair < 0) {
-    const char* e = getenv("MT_GEMM_PAIR");
-    use_pair = e ? atoi(e) : 1;
-  }
   // K == 0 never reaches this point; tensor maps below need K_bytes >= 16
-  if (use_pair && M > G_BLOCK_M && N > 128) {
+  if (pair_enabled() && M > G_BLOCK_M && N > 128) {
     // Tile width: 256 by default. The 192-wide variant (two accumulators, epilogue overlapped
     // with the next tile's MMAs) measured no faster on the benchmark shapes because the main
     // loop is bound by shared-memory bandwidth either way; MT_GEMM_PAIR_N=192 selects it.
-    static int forced_bn = -1, band = -2;
-    if (forced_bn < 0) { const char* e = getenv("MT_GEMM_PAIR_N"); forced_bn = e ? atoi(e) : 0; }
-    if (band == -2) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : -1; }
-    const int64_t tm = (M + 255) / 256;
-    int pbn = 256;
-    if (forced_bn == 192 || forced_bn == 256) pbn = forced_bn;
-    args.tiles_m = (int)tm;
+    const int pbn = forced_pair_n() ? forced_pair_n() : 256;
+    args.tiles_m = (int)((M + 255) / 256);
     args.tiles_n = (int)((N + pbn - 1) / pbn);
     args.num_tiles = args.tiles_m * args.tiles_n;
-    args.band = band;
-    { static int skip = -1; if (skip < 0) { const char* e = getenv("MT_GEMM_DEBUG_SKIP_STORE"); skip = e ? atoi(e) : 0; } args.debug_skip_store = skip; }
-    CUtensorMap ma, mb, msa, msb;
-    int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)K_bytes, (uint64_t)M, (uint64_t)K_bytes,
-                                G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != MT_OK) return rc;
-    rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)K_bytes, (uint64_t)N, (uint64_t)K_bytes,
-                            G_BLOCK_KB, (uint32_t)(pbn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc != MT_OK) return rc;
-    const uint32_t ch = format == FMT_NVFP4 ? 4 : 1;
-    rc = make_tensor_map_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sa, 128, (uint64_t)(args.rb_a * args.kc_a), 512, 128, ch,
-                            CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != MT_OK) return rc;
-    rc = make_tensor_map_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sb, 128, (uint64_t)(args.rb_b * args.kc_b), 512, 128, ch,
-                            CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != MT_OK) return rc;
-    // Output through shared memory + TMA stores when the output rows are 16-byte aligned;
-    // fp32 accumulation uses the TMA add-reduction, bf16 accumulation the direct path.
-    const size_t es = d_dtype == MT_F32 ? 4 : 2;
-    static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
-    if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
-    CUtensorMap md = ma;
-    args.tma_store = allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16);
-    if (args.tma_store) {
-      const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-      rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * es, d_dtype == MT_F32 ? 32 : 64, 32,
-                              CU_TENSOR_MAP_SWIZZLE_128B);
-      if (rc != MT_OK) return rc;
-    }
-    if (format == FMT_NVFP4)
-      return pbn == 192 ? launch_gemm_pair<FMT_NVFP4, 192, 5>(ma, mb, msa, msb, md, args, st)
-                        : launch_gemm_pair<FMT_NVFP4, 256, 5>(ma, mb, msa, msb, md, args, st);
-    return pbn == 192 ? launch_gemm_pair<FMT_MXFP8, 192, 5>(ma, mb, msa, msb, md, args, st)
-                      : launch_gemm_pair<FMT_MXFP8, 256, 5>(ma, mb, msa, msb, md, args, st);
+    return launch_pair_any(format, pbn, a, M, K_bytes, b, N, K_bytes, d, d_dtype, M, N, ldd, accumulate, args, st);
   }
   const int bn = pick_block_n(N);
   args.tiles_m = (int)((M + G_BLOCK_M - 1) / G_BLOCK_M);
@@ -989,8 +1076,12 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
   MT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sa) && aligned16(sb) && aligned16(scratch),
              "%s: operands must be 16-byte aligned", name);
 
-  // entries: for every 128-row block, every group owning at least one of its rows
-  const int64_t rbs = (R + 127) / 128;
+  // entries: for every row block (256 rows for the pair kernel, else 128), every group owning
+  // at least one of its rows
+  const bool pair = pair_enabled() && N_out >= 256 && R > 128;
+  const int pbn = forced_pair_n() ? forced_pair_n() : 256;
+  const int64_t blk = pair ? 256 : 128;
+  const int64_t rbs = (R + blk - 1) / blk;
   const int64_t max_entries = grouped_entries_upper_bound(R, G);
   const int64_t need = (int64_t)sizeof(int64_t) * (G + 1) + 2 * (int64_t)sizeof(int32_t) * max_entries;
   MT_REQUIRE(scratch_bytes >= need, "%s: scratch too small (%lld < %lld bytes)", name, (long long)scratch_bytes,
@@ -998,7 +1089,7 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
   int32_t* table = host_table;
   int64_t n = 0, g = 0;
   for (int64_t rb = 0; rb < rbs; ++rb) {
-    const int64_t lo = rb * 128, hi = std::min<int64_t>(lo + 128, R);
+    const int64_t lo = rb * blk, hi = std::min<int64_t>(lo + blk, R);
     while (g < G && m_offsets_host[g + 1] <= lo) ++g;  // skip groups that end before this block
     for (int64_t gg = g; gg < G && m_offsets_host[gg] < hi; ++gg) {
       if (m_offsets_host[gg + 1] <= m_offsets_host[gg]) continue;  // empty group
@@ -1019,7 +1110,7 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
   args.sa = sa; args.sb = sb;
   args.kc_a = padded_chunks(Kc / 32);
   args.kc_b = padded_chunks(ldb_bytes / 32);
-  args.rb_a = rbs; args.rb_b = (b_rows + 127) / 128;
+  args.rb_a = (R + 127) / 128; args.rb_b = (b_rows + 127) / 128;
   args.M = R; args.N = N_out; args.K_bytes = Kc;
   args.d = d; args.ldd = ldd; args.d_dtype = d_dtype;
   args.status = device_status_ptr();
@@ -1032,6 +1123,12 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
   args.b_group_rows = b_group_rows;
   args.b_group_k_bytes = b_group_k;
   args.k_elems_per_byte_x2 = 2;
+  if (pair) {
+    args.tiles_m = (int)n;
+    args.tiles_n = (int)((N_out + pbn - 1) / pbn);
+    args.num_tiles = args.tiles_m * args.tiles_n;
+    return launch_pair_any(FMT_MXFP8, pbn, a, R, Kc, b, b_rows, ldb_bytes, d, d_dtype, R, N_out, ldd, 0, args, st);
+  }
   const int bn = N_out % 256 == 0 ? 256 : 128;
   args.tiles_m = (int)n;
   args.tiles_n = (int)(N_out / bn);
@@ -1145,6 +1242,14 @@ int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const ui
   args.group_offsets = d_offsets;
   args.d_group_stride = N_out * K_out;
   args.k_elems_per_byte_x2 = 2;
+  if (pair_enabled() && N_out > 128 && K_out > 128) {
+    const int pbn = forced_pair_n() ? forced_pair_n() : 256;
+    args.tiles_m = (int)((N_out + 255) / 256);
+    args.tiles_n = (int)((K_out + pbn - 1) / pbn);
+    args.num_tiles = (int)(G * args.tiles_m * args.tiles_n);
+    return launch_pair_any(FMT_MXFP8, pbn, a_t, N_out, Rp, b_t, K_out, Rp, d, d_dtype, G * N_out, K_out, K_out, accumulate,
+                           args, st);
+  }
   const int bn = K_out > 128 ? 256 : 128;
   args.tiles_m = (int)((N_out + G_BLOCK_M - 1) / G_BLOCK_M);
   args.tiles_n = (int)((K_out + bn - 1) / bn);

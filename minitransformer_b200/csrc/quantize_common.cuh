@@ -81,20 +81,28 @@ __device__ __forceinline__ float round_to_bf16(float v) {
 // w[j] holds rows j = 0..15 of the two columns as packed bf16x2; on return w[j] holds
 // y_j = bf16( (1/4) * sum_i s_i * x_i * (-1)^popcount(i & j) ) for both columns.
 // Sign vector s = (+,+,+,-,+,-,-,-,-,-,-,+,-,+,-,-). The butterfly runs in packed fp32.
+// The signs cost no instruction: a butterfly on (s_a * A, s_b * B) equals s_a * (A +- B) with
+// add and subtract exchanged when s_a != s_b, so each block of 2h values carries the sign of
+// its first element as a common factor, and the whole vector ends with the factor s_0 = +1.
+// Negation commutes with rounding, so every value equals the one computed with the signs
+// applied up front, except that a zero may come out with the other sign; zeros of either
+// sign quantize to code 0 and do not move an abs-max.
 __device__ __forceinline__ void rht16_x2(uint32_t (&w)[16]) {
   constexpr uint32_t kNegRows = (1u << 3) | (1u << 5) | (1u << 6) | (1u << 7) | (1u << 8) | (1u << 9) | (1u << 10) |
                                 (1u << 12) | (1u << 14) | (1u << 15);
   f32x2_t v[16];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = bf16x2_to_f32x2(((kNegRows >> i) & 1u) ? (w[i] ^ 0x80008000u) : w[i]);
+  for (int i = 0; i < 16; ++i) v[i] = bf16x2_to_f32x2(w[i]);
 #pragma unroll
   for (int h = 1; h < 16; h <<= 1) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       if ((i & h) == 0) {
+        const int first = i & ~(h - 1);   // first element of this value's block of h
+        const bool exchange = ((kNegRows >> first) & 1u) != ((kNegRows >> (first + h)) & 1u);
         const f32x2_t a = v[i], b = v[i + h];
-        v[i] = add2(a, b);
-        v[i + h] = sub2(a, b);
+        v[i] = exchange ? sub2(a, b) : add2(a, b);
+        v[i + h] = exchange ? add2(a, b) : sub2(a, b);
       }
     }
   }

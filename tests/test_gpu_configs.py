@@ -108,7 +108,7 @@ def test_config5_small_llama_style_step_mxfp8_vs_bf16():
         logits = m(ids)
         loss = torch.nn.functional.cross_entropy(logits.float().view(-1, dims["vocab"]), tgt.view(-1))
         loss.backward()
-        losses.append(float(loss))
+        losses.append(loss.item())
         grads.append(torch.cat([p.grad.float().flatten() for n, p in sorted(m.named_parameters()) if p.grad is not None]))
     assert math.isfinite(losses[0]) and abs(losses[0] - losses[1]) / losses[1] < 0.02, losses
     cos = float(torch.nn.functional.cosine_similarity(grads[0], grads[1], dim=0))
