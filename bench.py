@@ -30,6 +30,11 @@ METRIC = "nvfp4_linear_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 
 C2 = dict(tokens=8192, in_features=4096, out_features=14336)
+# DRAM bytes (read + write) per GEMM launch of this workload, average of fprop / dgrad / wgrad,
+# from a one-pass ncu capture of this script (dram__bytes_read.sum + dram__bytes_write.sum:
+# 270.4, 155.5 and 279.0 MB). Slightly below the algorithmic bytes because part of each output
+# is still in L2 when the kernel ends.
+GEMM_DRAM_BYTES_PER_LAUNCH = 235.0e6
 C4 = dict(tokens=8192, hidden=8192, ffn=28672)
 CPU_SAMPLE = dict(tokens=512, in_features=4096, out_features=3584)
 
@@ -163,6 +168,41 @@ def _physical_gpu_index(local_rank):
         except Exception:
             return local_rank
     return local_rank
+
+
+def _tp_workload_single_gpu(torch, Linear, params, dev, kernels, steps=5, warmup=3):
+    """The workload the N > 1 runs shard (tensor-parallel MLP, fc1 then fc2, fwd+bwd), unsharded on
+    one GPU: the base of the strong-scaling series, reported beside the N = 1 headline."""
+    T, H, Fd = C4["tokens"], C4["hidden"], C4["ffn"]
+    gen = torch.Generator(device="cpu").manual_seed(4321)
+    x = torch.randn(T, H, generator=gen).to(torch.bfloat16).to(dev)
+    dy = (torch.randn(T, H, generator=gen) * 1e-3).to(torch.bfloat16).to(dev)
+    init = lambda t: torch.nn.init.normal_(t, std=0.02)
+    fc1 = Linear(H, Fd, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
+                 fuse_wgrad_accumulation=True, init_method=init)
+    fc2 = Linear(Fd, H, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
+                 fuse_wgrad_accumulation=True, init_method=init)
+    for m in (fc1, fc2):
+        m.weight.main_grad = torch.zeros_like(m.weight, dtype=torch.float32)
+
+    def step():
+        xd = x.detach().requires_grad_(True)
+        y = fc2(fc1(xd, is_first_microbatch=True), is_first_microbatch=True)
+        y.backward(dy)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    flops = 6 * 2.0 * T * H * Fd
+    return {"value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+            "workload": f"NVFP4 MLP fc1+fc2 fwd+bwd, tokens={T}, hidden={H}, ffn={Fd}, no sharding"}
 
 
 def run_gpu_arm(args):
@@ -335,23 +375,36 @@ def run_gpu_arm(args):
         }
         if n == 1:
             g_avg = sum(g_ms) / len(g_ms)
+            T_, H_, F_ = C2["tokens"], C2["in_features"], C2["out_features"]
+            # codes (0.5 B/elt) and scales (one byte per 16 elements) of both operands, plus the output
+            gemm_alg_bytes = ((T_ * H_ + F_ * H_) * 0.5625 + T_ * F_ * 2          # fprop, bf16 out
+                              + (T_ * F_ + H_ * F_) * 0.5625 + T_ * H_ * 2        # dgrad, bf16 out
+                              + (F_ * T_ + H_ * T_) * 0.5625 + F_ * H_ * 4) / 3   # wgrad, fp32 out
             achieved = gemm_flops_each / (g_avg * 1e-3) / 1e12
             peak = 4.0 * peaks["bf16_sustained"]
             line["roofline"] = {
                 "bound": "tensor", "kernel": "gemm_blockscaled_kernel<NVFP4> (fprop/dgrad/wgrad average)",
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_unit": "bytes per launch (DRAM read + write, ncu)",
+                "algorithmic_bytes": gemm_alg_bytes,
                 "peak_source": f"4 x {peaks['source']} sustained bf16 cuBLAS rate ({peaks['bf16_sustained']} TFLOP/s); "
                                "no FP4 figure is measured on this pool",
                 "frac_of_nominal_9000": achieved / 9000.0, "avg_launch_ms": g_avg,
             }
+            # dy: the abs-max pass reads 2 B/elt; the cast reads 2 B/elt and writes two 0.5 B/elt code
+            # copies plus two 1/16 B/elt scale copies. The per-tensor scale makes the first read
+            # unavoidable for a tensor larger than L2, so the sequence moves 5.125 B/elt.
             q_avg = sum(q_ms) / len(q_ms)
-            q_bytes = C2["tokens"] * C2["out_features"] * 3.125
+            elts = C2["tokens"] * C2["out_features"]
+            q_bytes = elts * 5.125
             q_gbs = q_bytes / (q_avg * 1e-3) / 1e9
             line["roofline_quantize"] = {
                 "bound": "hbm", "kernel": "amax_rht_kernel + quantize_nvfp4_kernel on dy (row + transposed, RHT)",
                 "achieved": q_gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": q_gbs / peaks["hbm"],
                 "algorithmic_bytes": q_bytes, "avg_sequence_ms": q_avg,
+                "achieved_counting_one_read": elts * 3.125 / (q_avg * 1e-3) / 1e9,
                 "peak_source": f"{peaks['source']} copy bandwidth"}
+            line["tp_workload_on_1_gpu"] = _tp_workload_single_gpu(torch, Linear, params, dev, kernels)
             tf, dt = cpu_run(4, 1)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": _cpu_sample_text(), "s_per_sample_step": dt}
