@@ -118,6 +118,26 @@ int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz,
                   void* d, int d_dtype, int64_t ldd,
                   const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
 
+/* The same GEMMs for operands whose contraction dimension is split into slabs stored one
+ * after another: a is a_slabs matrices [M, K / a_slabs] (bytes as above) back to back, and
+ * sa_swz is the a_slabs GEMM-layout scale buffers of those matrices back to back (each
+ * mt_swizzled_scale_bytes(M, K / a_slabs / block) bytes); likewise b with b_slabs. This is
+ * the layout an all-gather of per-rank transposed shards produces (rank r holds the tokens
+ * [r T/n, (r+1) T/n) of x^T), so the wgrad GEMM of a sequence-parallel layer reads the
+ * gathered buffer as it arrives, with no re-interleaving copy. Slab count 1 = plain layout.
+ * Needs M > 128, N > 128 and K / slabs a multiple of 256 (NVFP4) or 128 (MXFP8) elements.
+ * No counterpart in the reference, whose gather helpers move high-precision tensors
+ * (miniTransformer/distributed/distributed.py:68-121). */
+int mt_gemm_nvfp4_kslab(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, int64_t a_slabs,
+                        const uint8_t* b, const uint8_t* sb_swz, const float* amax_b, int64_t b_slabs,
+                        int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
+                        const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
+
+int mt_gemm_mxfp8_kslab(const uint8_t* a, const uint8_t* sa_swz, int64_t a_slabs,
+                        const uint8_t* b, const uint8_t* sb_swz, int64_t b_slabs,
+                        int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
+                        const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
+
 /* Same contracts, computed by a plain CUDA-core kernel that follows the emulation's
  * summation structure (per-block fp32 dot, scaled, fp32 accumulate). Scales are given in
  * the row-major layout. It exists so the tensor-core kernels can be checked on the device at

@@ -65,6 +65,13 @@ struct GemmArgs {
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
   int debug_skip_store;          // tuning aid: the epilogue drains tensor memory but writes nothing
   int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
+  // Pair kernel, operands split along K into slabs stored one after another (what an all-gather
+  // of per-rank transposed shards produces): K step k of A lies in slab k / a_slab_steps, whose
+  // rows start a_slab_rows further down the tensor map and whose scale chunks start
+  // a_slab_chunks further down the chunk list. One slab spanning all K steps = plain layout.
+  int a_slab_steps, b_slab_steps;
+  int64_t a_slab_rows, b_slab_rows;
+  int64_t a_slab_chunks, b_slab_chunks;
 };
 
 template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
@@ -719,14 +726,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.status, DS_EMPTY_WAIT)) { alive = false; break; }
           if (leader) mbar_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
-          const int32_t kx = k * G_BLOCK_KB;
-          tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, a_kx0 + kx, a_row);
-          tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, b_kx0 + kx, b_row);
-          tma_load_2d_pair(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, &map_sfa, bar, 0, sfa_chunk0 + k * CH);
+          // slab of each operand this K step falls in, and the step inside the slab
+          const int sl_a = k / a.a_slab_steps, ka = k - sl_a * a.a_slab_steps;
+          const int sl_b = k / a.b_slab_steps, kb = k - sl_b * a.b_slab_steps;
+          tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, a_kx0 + ka * G_BLOCK_KB,
+                           a_row + (int32_t)(sl_a * a.a_slab_rows));
+          tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, b_kx0 + kb * G_BLOCK_KB,
+                           b_row + (int32_t)(sl_b * a.b_slab_rows));
+          tma_load_2d_pair(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, &map_sfa, bar, 0,
+                           sfa_chunk0 + (int32_t)(sl_a * a.a_slab_chunks) + ka * CH);
 #pragma unroll
           for (int h = 0; h < NSB; ++h)
             tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + h * CH * 512, &map_sfb, bar, 0,
-                             (int32_t)((sfb_rb0 + h) * a.kc_b) + sfb_kc0 + k * CH);
+                             (int32_t)((sfb_rb0 + h) * a.kc_b + sl_b * a.b_slab_chunks) + sfb_kc0 + kb * CH);
         }
       }
     }
@@ -928,24 +940,34 @@ static int forced_pair_n() {
 // pitch ldd. args carries everything else (mode, tile counts, scale-factor geometry).
 static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows, int64_t a_ld_bytes, const uint8_t* b,
                            int64_t b_rows, int64_t b_ld_bytes, void* d, int d_dtype, int64_t d_rows, int64_t d_cols,
-                           int64_t ldd, int accumulate, GemmArgs& args, cudaStream_t st) {
+                           int64_t ldd, int accumulate, GemmArgs& args, cudaStream_t st, int64_t a_slabs = 1,
+                           int64_t b_slabs = 1) {
   static int band = -2;
   if (band == -2) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : -1; }
   args.band = band;
   { static int skip = -1; if (skip < 0) { const char* e = getenv("MT_GEMM_DEBUG_SKIP_STORE"); skip = e ? atoi(e) : 0; } args.debug_skip_store = skip; }
+  // a_slabs / b_slabs > 1: the operand is `slabs` matrices [rows, ld_bytes / slabs] stored one
+  // after another, each with its own scale-chunk list (args.kc_* counts chunks per slab)
+  const int64_t steps_total = (args.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB;
+  args.a_slab_steps = (int)std::max<int64_t>(1, steps_total / a_slabs);
+  args.b_slab_steps = (int)std::max<int64_t>(1, steps_total / b_slabs);
+  args.a_slab_rows = a_rows; args.b_slab_rows = b_rows;
+  args.a_slab_chunks = args.rb_a * args.kc_a; args.b_slab_chunks = args.rb_b * args.kc_b;
   CUtensorMap ma, mb, msa, msb;
-  int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)a_ld_bytes, (uint64_t)a_rows,
-                              (uint64_t)a_ld_bytes, G_BLOCK_KB, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)(a_ld_bytes / a_slabs),
+                              (uint64_t)(a_rows * a_slabs), (uint64_t)(a_ld_bytes / a_slabs), G_BLOCK_KB, 128,
+                              CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MT_OK) return rc;
-  rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)b_ld_bytes, (uint64_t)b_rows,
-                          (uint64_t)b_ld_bytes, G_BLOCK_KB, (uint32_t)(pbn / 2), CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_tensor_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b, (uint64_t)(b_ld_bytes / b_slabs),
+                          (uint64_t)(b_rows * b_slabs), (uint64_t)(b_ld_bytes / b_slabs), G_BLOCK_KB, (uint32_t)(pbn / 2),
+                          CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MT_OK) return rc;
   const uint32_t ch = format == FMT_NVFP4 ? 4 : 1;
-  rc = make_tensor_map_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, args.sa, 128, (uint64_t)(args.rb_a * args.kc_a), 512, 128, ch,
-                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tensor_map_2d(&msa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, args.sa, 128, (uint64_t)(args.a_slab_chunks * a_slabs), 512,
+                          128, ch, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != MT_OK) return rc;
-  rc = make_tensor_map_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, args.sb, 128, (uint64_t)(args.rb_b * args.kc_b), 512, 128, ch,
-                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_tensor_map_2d(&msb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, args.sb, 128, (uint64_t)(args.b_slab_chunks * b_slabs), 512,
+                          128, ch, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != MT_OK) return rc;
   // Output through shared memory + TMA stores when the output rows are 16-byte aligned;
   // fp32 accumulation uses the TMA add-reduction, bf16 accumulation the direct path.
@@ -981,8 +1003,10 @@ static int pick_block_n(int64_t N) {
 
 static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const float* amax_a, const uint8_t* b,
                        const uint8_t* sb, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,
-                       int64_t ldd, const void* bias, int bias_dtype, int accumulate, cudaStream_t st) {
+                       int64_t ldd, const void* bias, int bias_dtype, int accumulate, cudaStream_t st,
+                       int64_t a_slabs = 1, int64_t b_slabs = 1) {
   const char* name = format == FMT_NVFP4 ? "mt_gemm_nvfp4" : "mt_gemm_mxfp8";
+  MT_REQUIRE(a_slabs >= 1 && b_slabs >= 1, "%s: slab counts must be positive", name);
   MT_REQUIRE(d != nullptr, "%s: null output pointer", name);
   MT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative shape", name);
   if (K == 0) {
@@ -1008,7 +1032,17 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
 
   GemmArgs args{};
   args.sa = sa; args.sb = sb;
-  args.kc_a = args.kc_b = padded_chunks(K / block);
+  const bool slabbed = a_slabs > 1 || b_slabs > 1;
+  if (slabbed) {
+    // every slab must hold whole K steps, so that no load straddles two slabs
+    MT_REQUIRE(K_bytes % (a_slabs * G_BLOCK_KB) == 0 && K_bytes % (b_slabs * G_BLOCK_KB) == 0,
+               "%s: each K slab must be a multiple of %d bytes (K_bytes=%lld, slabs %lld / %lld)", name, G_BLOCK_KB,
+               (long long)K_bytes, (long long)a_slabs, (long long)b_slabs);
+    MT_REQUIRE(pair_enabled() && M > G_BLOCK_M && N > 128,
+               "%s: K-slab operands need M > 128 and N > 128 (M=%lld, N=%lld)", name, (long long)M, (long long)N);
+  }
+  args.kc_a = padded_chunks(K / a_slabs / block);
+  args.kc_b = padded_chunks(K / b_slabs / block);
   args.rb_a = (M + 127) / 128; args.rb_b = (N + 127) / 128;
   args.M = M; args.N = N; args.K_bytes = K_bytes;
   args.d = d; args.ldd = ldd; args.d_dtype = d_dtype;
@@ -1028,7 +1062,8 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
     args.tiles_m = (int)((M + 255) / 256);
     args.tiles_n = (int)((N + pbn - 1) / pbn);
     args.num_tiles = args.tiles_m * args.tiles_n;
-    return launch_pair_any(format, pbn, a, M, K_bytes, b, N, K_bytes, d, d_dtype, M, N, ldd, accumulate, args, st);
+    return launch_pair_any(format, pbn, a, M, K_bytes, b, N, K_bytes, d, d_dtype, M, N, ldd, accumulate, args, st, a_slabs,
+                           b_slabs);
   }
   const int bn = pick_block_n(N);
   args.tiles_m = (int)((M + G_BLOCK_M - 1) / G_BLOCK_M);
@@ -1269,6 +1304,21 @@ int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, 
                   int64_t ldd, const void* bias, int bias_dtype, int accumulate, mt_stream_t stream) {
   return mt::gemm_common(mt::FMT_NVFP4, a, sa_swz, amax_a, b, sb_swz, amax_b, M, N, K, d, d_dtype, ldd, bias,
                          bias_dtype, accumulate, static_cast<cudaStream_t>(stream));
+}
+
+int mt_gemm_nvfp4_kslab(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, int64_t a_slabs, const uint8_t* b,
+                        const uint8_t* sb_swz, const float* amax_b, int64_t b_slabs, int64_t M, int64_t N, int64_t K,
+                        void* d, int d_dtype, int64_t ldd, const void* bias, int bias_dtype, int accumulate,
+                        mt_stream_t stream) {
+  return mt::gemm_common(mt::FMT_NVFP4, a, sa_swz, amax_a, b, sb_swz, amax_b, M, N, K, d, d_dtype, ldd, bias,
+                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream), a_slabs, b_slabs);
+}
+
+int mt_gemm_mxfp8_kslab(const uint8_t* a, const uint8_t* sa_swz, int64_t a_slabs, const uint8_t* b, const uint8_t* sb_swz,
+                        int64_t b_slabs, int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
+                        const void* bias, int bias_dtype, int accumulate, mt_stream_t stream) {
+  return mt::gemm_common(mt::FMT_MXFP8, a, sa_swz, nullptr, b, sb_swz, nullptr, M, N, K, d, d_dtype, ldd, bias,
+                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream), a_slabs, b_slabs);
 }
 
 int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz, int64_t M,

@@ -86,3 +86,36 @@ def gather_packed_along_first_dim(parts: Sequence[torch.Tensor], process_group) 
         res.append(piece.reshape(world * p.shape[0], *p.shape[1:]))
         off += n
     return tuple(res)
+
+
+def _gather_bytes(t: torch.Tensor, out_shape, process_group, async_op: bool = False):
+    """All-gather of a contiguous tensor as bytes, rank-major, into a new tensor of out_shape."""
+    world = get_distributed_world_size(process_group)
+    src = t.contiguous().view(torch.uint8).reshape(-1)
+    out = torch.empty(world * src.numel(), dtype=torch.uint8, device=src.device)
+    handle = dist.all_gather_into_tensor(out, src, group=process_group, async_op=async_op)
+    return out.view(*out_shape), handle
+
+
+def gather_gemm_ready(data: torch.Tensor, scale_swz: torch.Tensor, process_group):
+    """Gathers a row-sharded quantized tensor in the form the GEMM reads: codes [rows, bytes]
+    concatenated along rows, and GEMM-layout scales, whose 128-row chunk lists simply follow
+    one another when every shard is a multiple of 128 rows. No copy after the collectives."""
+    world = get_distributed_world_size(process_group)
+    assert data.shape[0] % 128 == 0, "row shards must be multiples of 128 rows"
+    g_data, _ = _gather_bytes(data, (world * data.shape[0], data.shape[1] * data.element_size()), process_group)
+    g_scale, _ = _gather_bytes(scale_swz, (world * scale_swz.numel(),), process_group)
+    return g_data, g_scale
+
+
+def gather_transposed_as_k_slabs(data_t: torch.Tensor, scale_t_swz: torch.Tensor, process_group,
+                                 async_op: bool = False):
+    """Gathers the transposed copies of token shards. Rank r's copy [features, tokens / world]
+    is slab r of the contraction dimension of the gathered x^T; the result [world, features,
+    bytes] (and the per-rank GEMM-layout scale buffers back to back) is consumed as it is by
+    the K-slab GEMM entry points, so nothing is re-interleaved. Returns (codes, scales, handles)."""
+    world = get_distributed_world_size(process_group)
+    g_data, h0 = _gather_bytes(data_t, (world, data_t.shape[0], data_t.shape[1] * data_t.element_size()),
+                               process_group, async_op)
+    g_scale, h1 = _gather_bytes(scale_t_swz, (world * scale_t_swz.numel(),), process_group, async_op)
+    return g_data, g_scale, (h0, h1)

@@ -146,11 +146,32 @@ def _gemm_out(M, N, out_dtype, out, accumulate, device):
     return out
 
 
+def _slabs(q):
+    """(slab count, rows, bytes per row over all slabs) of a GEMM operand: a 3-D tensor
+    [slabs, rows, bytes per slab row] is the contraction dimension split into slabs stored one
+    after another (what an all-gather of per-rank transposed shards produces)."""
+    if q.dim() == 3:
+        assert q.is_contiguous()
+        return q.shape[0], q.shape[1], q.shape[0] * q.shape[2]
+    return 1, q.shape[0], q.shape[1]
+
+
 def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat16, out=None,
                accumulate=False, bias=None, check_kernel=False, sa_lin=None, sb_lin=None):
     """D[M,N] = alpha * qa[M,K/2] . qb[N,K/2]^T. With check_kernel=True the CUDA-core
-    checker runs instead (it takes the row-major scales sa_lin / sb_lin)."""
+    checker runs instead (it takes the row-major scales sa_lin / sb_lin). A 3-D operand
+    [slabs, rows, K/2/slabs] is read slab by slab along K (its scales likewise)."""
     _require_cuda(qa, "qa")
+    (a_slabs, M, ka), (b_slabs, N, kb) = _slabs(qa), _slabs(qb)
+    if a_slabs > 1 or b_slabs > 1:
+        assert ka == kb and not check_kernel
+        out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
+        _count(1)
+        _lib.call("mt_gemm_nvfp4_kslab", qa.data_ptr(), sa_swz.data_ptr(), amax_a.data_ptr(), a_slabs, qb.data_ptr(),
+                  sb_swz.data_ptr(), amax_b.data_ptr(), b_slabs, M, N, ka * 2, out.data_ptr(),
+                  _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
+                  0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+        return out
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1] * 2
     assert qb.shape[1] * 2 == K
     if K % 32 and not check_kernel:
@@ -176,6 +197,15 @@ def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat
 def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, accumulate=False, bias=None,
                check_kernel=False, sa_lin=None, sb_lin=None):
     _require_cuda(qa, "qa")
+    (a_slabs, M, ka), (b_slabs, N, kb) = _slabs(qa), _slabs(qb)
+    if a_slabs > 1 or b_slabs > 1:
+        assert ka == kb and not check_kernel
+        out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)
+        _count(1)
+        _lib.call("mt_gemm_mxfp8_kslab", qa.data_ptr(), sa_swz.data_ptr(), a_slabs, qb.data_ptr(), sb_swz.data_ptr(),
+                  b_slabs, M, N, ka, out.data_ptr(), _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
+                  0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+        return out
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1]
     assert qb.shape[1] == K
     out = _gemm_out(M, N, out_dtype, out, accumulate, qa.device)

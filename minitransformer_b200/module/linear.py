@@ -16,7 +16,8 @@ import torch
 from . import config
 from ._common import noop_cat
 from .base import LayerLinearBaseModule
-from ..distributed.distributed import (allreduce, gather_along_first_dim, gather_packed_along_first_dim,
+from ..distributed.distributed import (allreduce, gather_along_first_dim, gather_gemm_ready,
+                                       gather_packed_along_first_dim, gather_transposed_as_k_slabs,
                                        get_distributed_rank, get_distributed_world_size,
                                        reduce_scatter_along_first_dim, set_tensor_model_parallel_attributes)
 from ..ops import quantization
@@ -99,7 +100,8 @@ class _QuantizedLinear(torch.autograd.Function):
         qres_x = _QuantizedLinear.quantize_optionally_allgather(
             op, x, qlinear_params.x_params, transpose_required=is_grad_enabled,
             allgather_required=gather_required, allgather_quantize=qlinear_params.allgather_quantize,
-            tp_group=tp_group, keep_transpose_local=qlinear_params.memory_saving and gather_required)
+            tp_group=tp_group, keep_transpose_local=qlinear_params.memory_saving and gather_required,
+            weight_shape=tuple(w.shape))
 
         # weights are re-quantized on the first microbatch (or when the caller gives no hint)
         if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
@@ -150,7 +152,7 @@ class _QuantizedLinear(torch.autograd.Function):
         gather_required = ctx.parallel_mode == "row" and ctx.sequence_parallel
         qres_dy = _QuantizedLinear.quantize_optionally_allgather(
             op, dy, p.g_params, transpose_required=True, allgather_required=gather_required,
-            allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group)
+            allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group, weight_shape=tuple(w.shape))
 
         # memory-saving mode kept only this rank's token shard of x^T: gather it back while
         # the dgrad GEMM runs
@@ -193,7 +195,7 @@ class _QuantizedLinear(torch.autograd.Function):
     # -- helpers ------------------------------------------------------------------------------
     @staticmethod
     def quantize_optionally_allgather(quantize_op, x, qparams, transpose_required, allgather_required,
-                                      allgather_quantize, tp_group, keep_transpose_local=False):
+                                      allgather_quantize, tp_group, keep_transpose_local=False, weight_shape=None):
         """Quantizes x, gathering it across the tensor-parallel group first (bf16) or after
         (quantized) when the layer is sequence-parallel.
 
@@ -217,8 +219,11 @@ class _QuantizedLinear(torch.autograd.Function):
         r = quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=True,
                                  tp_group=tp_group)
         rows = x.shape[0]
-        parts = [r.data, r.scale[:rows]]
         gather_t = transpose_required and not keep_transpose_local
+        if (weight_shape is not None and min(weight_shape) > 128
+                and _QuantizedLinear._gemm_ready_gather_possible(r, rows, x.shape[1], world, transpose_required)):
+            return _QuantizedLinear._gather_gemm_ready(r, tp_group, gather_t, transpose_required)
+        parts = [r.data, r.scale[:rows]]
         if gather_t:
             parts += [r.data_t, r.scale_t[: x.shape[1]]]
         g = gather_packed_along_first_dim(parts, tp_group)
@@ -232,8 +237,50 @@ class _QuantizedLinear(torch.autograd.Function):
         return out
 
     @staticmethod
+    def _gemm_ready_gather_possible(r, rows, features, world, transpose_required):
+        """The copy-free gather needs GEMM-layout scales from the quantizer, shards of whole
+        128-row scale chunks, K slabs of whole 128-byte K steps for the transposed copy, and
+        GEMM shapes the CTA-pair kernel takes (more than 128 rows on both sides)."""
+        if r.scale_swz is None or (transpose_required and r.scale_t_swz is None):
+            return False
+        if rows % 128 or rows * world <= 128 or features <= 128:
+            return False
+        if transpose_required and (r.data_t.shape[1] * r.data_t.element_size()) % 128:
+            return False
+        return True
+
+    @staticmethod
+    def _gather_gemm_ready(r, tp_group, gather_t, transpose_required):
+        """Quantized gather without any copy after the collectives: row-wise codes and
+        GEMM-layout scales land where the fprop / dgrad GEMM reads them; the transposed copies
+        stay per-rank K slabs ([world, features, bytes]) that the wgrad GEMM walks slab by slab.
+        The scale fields of the result hold the GEMM layout (the row-major form is not
+        materialized on this path)."""
+        data, scale = gather_gemm_ready(r.data, r.scale_swz, tp_group)
+        if r.data.dtype != torch.uint8:
+            data = data.view(r.data.dtype)
+        scale._mt_swz = scale
+        out = quantization.QuantizeResult(data, scale, None, None, r.global_amax_row, r.global_amax_col, scale, None)
+        if gather_t:
+            data_t, scale_t, _ = gather_transposed_as_k_slabs(r.data_t, r.scale_t_swz, tp_group)
+            if r.data_t.dtype != torch.uint8:
+                data_t = data_t.view(r.data_t.dtype)
+            scale_t._mt_swz = scale_t
+            out.data_t, out.scale_t, out.scale_t_swz = data_t, scale_t, scale_t
+        elif transpose_required:
+            out.data_t, out.scale_t, out.scale_t_swz = r.data_t, r.scale_t, r.scale_t_swz
+            out._t_is_local_shard = True
+        return out
+
+    @staticmethod
     def _start_gather_transposed(qx_t, sx_t, tp_group):
         world = get_distributed_world_size(tp_group)
+        swz = getattr(sx_t, "_mt_swz", None)
+        if swz is not None and (qx_t.shape[1] * qx_t.element_size()) % 128 == 0 and qx_t.shape[0] > 128:
+            data_t, scale_t, handles = gather_transposed_as_k_slabs(qx_t, swz, tp_group, async_op=True)
+            if qx_t.dtype != torch.uint8:
+                data_t = data_t.view(qx_t.dtype)
+            return ("slabs", data_t, scale_t, handles)
         flat = torch.cat([qx_t.contiguous().view(torch.uint8).reshape(-1),
                           sx_t.contiguous().view(torch.uint8).reshape(-1)])
         out = torch.empty(world * flat.numel(), dtype=torch.uint8, device=flat.device)
@@ -242,6 +289,13 @@ class _QuantizedLinear(torch.autograd.Function):
 
     @staticmethod
     def _finish_gather_transposed(pending, tp_group):
+        if pending[0] == "slabs":
+            _, data_t, scale_t, handles = pending
+            for h in handles:
+                if h is not None:
+                    h.wait()
+            scale_t._mt_swz = scale_t
+            return data_t, scale_t
         out, handle, qx_t, sx_t = pending
         handle.wait()
         world = get_distributed_world_size(tp_group)

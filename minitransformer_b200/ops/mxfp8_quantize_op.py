@@ -37,7 +37,7 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
               global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):
         if out is not None:
             assert out.dtype == out_dtype, "output dtype mismatch"
-        M, N = qx.shape[0], qw.shape[0]
+        M, N = qx.shape[-2], qw.shape[-2]   # a 3-D operand is [K slabs, rows, bytes per slab row]
         return kernels.gemm_mxfp8(qx.view(torch.uint8), _swizzled(sx, M), qw.view(torch.uint8), _swizzled(sw, N),
                                   out_dtype=out_dtype, out=out, accumulate=accumulate,
                                   bias=bias if bias is not None and bias.numel() else None)

@@ -70,7 +70,7 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
         assert global_amax_qx is not None and global_amax_qw is not None, "NVFP4 needs the per-tensor abs-max"
         if out is not None:
             assert out.dtype == out_dtype, "output dtype mismatch"
-        M, N = qx.shape[0], qw.shape[0]
+        M, N = qx.shape[-2], qw.shape[-2]   # a 3-D operand is [K slabs, rows, bytes per slab row]
         return kernels.gemm_nvfp4(qx, _swizzled(sx, M), global_amax_qx, qw, _swizzled(sw, N), global_amax_qw,
                                   out_dtype=out_dtype, out=out, accumulate=accumulate,
                                   bias=bias if bias is not None and bias.numel() else None)

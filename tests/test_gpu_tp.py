@@ -85,6 +85,20 @@ def _worker(rank, world, port, result):
                 and torch.equal(qg.scale_t.view(torch.uint8), qf.scale_t.view(torch.uint8)[: H])
                 and float(qg.global_amax_row) == float(qf.global_amax_row)
                 and float(qg.global_amax_col) == float(qf.global_amax_col))
+        # the copy-free form of the same gather: codes concatenated in place, GEMM-layout scales,
+        # transposed copies left as per-rank K slabs that the GEMM walks directly
+        qs = _QuantizedLinear.quantize_optionally_allgather(p.quantize_op, x.chunk(world, 0)[rank].contiguous(), p.x_params,
+                                                            True, True, True, dist.group.WORLD, weight_shape=(Fd, H))
+        assert qs.data_t.dim() == 3 and qs.data_t.shape[0] == world
+        same = (same and torch.equal(qs.data, qf.data) and torch.equal(qs.scale_swz.view(-1), qf.scale_swz.view(-1))
+                and torch.equal(qs.data_t.permute(1, 0, 2).reshape(H, -1), qf.data_t))
+        d_plain = K.gemm_nvfp4(qf.data_t, qf.scale_t_swz, qf.global_amax_col, qf.data_t, qf.scale_t_swz,
+                               qf.global_amax_col, out_dtype=torch.float32)
+        d_slab = K.gemm_nvfp4(qf.data_t, qf.scale_t_swz, qf.global_amax_col, qs.data_t, qs.scale_t_swz,
+                              qs.global_amax_col, out_dtype=torch.float32)
+        d_slab2 = K.gemm_nvfp4(qs.data_t, qs.scale_t_swz, qs.global_amax_col, qs.data_t, qs.scale_t_swz,
+                               qs.global_amax_col, out_dtype=torch.float32)
+        same = same and torch.equal(d_plain, d_slab) and torch.equal(d_plain, d_slab2)
         result[rank] = (errs, bool(same), K.read_device_status())
     finally:
         dist.destroy_process_group()
