@@ -118,6 +118,13 @@ int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz,
                   void* d, int d_dtype, int64_t ldd,
                   const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
 
+/* Number of SMs every later GEMM launch of this process leaves idle (default 0). The GEMM
+ * kernels are persistent, one CTA per SM; a collective launched beside such a grid gets no SM
+ * until GEMM CTAs retire. A caller that overlaps a reduce-scatter with the wgrad GEMM sets a
+ * margin around that GEMM and resets it afterwards (the role of the sm_margin argument
+ * of the userbuffer overlap flags the reference's Linear carries, linear.py:649-671). */
+int mt_set_sm_margin(int sms);
+
 /* The same GEMMs for operands whose contraction dimension is split into slabs stored one
  * after another: a is a_slabs matrices [M, K / a_slabs] (bytes as above) back to back, and
  * sa_swz is the a_slabs GEMM-layout scale buffers of those matrices back to back (each

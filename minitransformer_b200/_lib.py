@@ -26,6 +26,7 @@ _SIGNATURES = {
     "mt_swizzle_scales": (_int, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "mt_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
     "mt_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
+    "mt_set_sm_margin": (_int, [_int]),
     "mt_gemm_nvfp4_kslab": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int,
                                    _int, _vp]),
     "mt_gemm_mxfp8_kslab": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),

@@ -874,6 +874,10 @@ static int sm_count() {
   return n;
 }
 
+// SMs the persistent GEMM grids leave idle (mt_set_sm_margin): room for a collective's kernel
+// that should run beside the GEMM instead of waiting for its CTAs to retire.
+static int g_sm_margin = 0;
+
 template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t st) {
   using Cfg = GemmCfg<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
@@ -883,7 +887,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
     attr_set = true;
   }
-  const int grid = std::min(args.num_tiles, sm_count());
+  const int grid = std::min(args.num_tiles, std::max(1, sm_count() - g_sm_margin));
   kern<<<grid, G_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, args);
   MT_CUDA(cudaGetLastError());
   return MT_OK;
@@ -912,7 +916,7 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
     max_pairs = n;
   }
-  const int pairs = std::min(args.num_tiles, max_pairs);
+  const int pairs = std::min(args.num_tiles, std::max(1, max_pairs - (g_sm_margin + 1) / 2));
   kern<<<2 * pairs, P_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, msa, msb, md, args);
   MT_CUDA(cudaGetLastError());
   return MT_OK;
@@ -1304,6 +1308,12 @@ int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, 
                   int64_t ldd, const void* bias, int bias_dtype, int accumulate, mt_stream_t stream) {
   return mt::gemm_common(mt::FMT_NVFP4, a, sa_swz, amax_a, b, sb_swz, amax_b, M, N, K, d, d_dtype, ldd, bias,
                          bias_dtype, accumulate, static_cast<cudaStream_t>(stream));
+}
+
+int mt_set_sm_margin(int sms) {
+  MT_REQUIRE(sms >= 0 && sms < 148, "mt_set_sm_margin: %d is not a valid SM count", sms);
+  mt::g_sm_margin = sms;
+  return MT_OK;
 }
 
 int mt_gemm_nvfp4_kslab(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, int64_t a_slabs, const uint8_t* b,

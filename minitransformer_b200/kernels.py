@@ -1,5 +1,6 @@
 """Thin torch-tensor front end over the C-ABI kernels: allocates outputs with torch, passes
 raw pointers and the current CUDA stream, raises on any error. No arithmetic happens here."""
+import contextlib
 from dataclasses import dataclass
 from typing import Optional
 
@@ -144,6 +145,17 @@ def _gemm_out(M, N, out_dtype, out, accumulate, device):
     else:
         assert out.shape == (M, N) and out.dtype == out_dtype and out.stride(1) == 1
     return out
+
+
+@contextlib.contextmanager
+def sm_margin(sms: int):
+    """GEMMs launched inside leave `sms` SMs idle, so that a collective in flight on another
+    stream runs beside them instead of behind them."""
+    _lib.call("mt_set_sm_margin", int(sms))
+    try:
+        yield
+    finally:
+        _lib.call("mt_set_sm_margin", 0)
 
 
 def _slabs(q):

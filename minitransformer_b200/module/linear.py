@@ -8,7 +8,9 @@ kernels, sequence-parallel inputs can be gathered in quantized form (codes + sca
 packed collective, after a MAX all-reduce of the per-tensor abs-max), and
 `fuse_wgrad_accumulation` really accumulates into `weight.main_grad` in place.
 """
+import contextlib
 import logging
+import os
 from typing import Any, Callable, Dict, List, Optional, Tuple, Union
 
 import torch
@@ -70,6 +72,21 @@ class _NonQuantizedLinear(torch.autograd.Function):
             handle.wait()
         dgrad = dgrad.view(-1, *ctx.x_shape[1:])
         return (dgrad, None, wgrad, None, b_grad) + (None,) * (_NUM_FN_ARGS - 5)
+
+
+def _overlap_sm_margin() -> int:
+    """SMs the wgrad GEMM leaves to a collective that runs beside it (MT_TP_SM_MARGIN, default 16)."""
+    try:
+        return max(0, int(os.environ.get("MT_TP_SM_MARGIN", "16")))
+    except ValueError:
+        return 16
+
+
+def _sm_margin(op, sms: int):
+    """Context in which the op's GEMMs leave `sms` SMs idle; ops without that control (the CPU
+    stand-in of the tests) get a null context."""
+    ctl = getattr(op, "sm_margin", None)
+    return ctl(sms) if (ctl is not None and sms > 0) else contextlib.nullcontext()
 
 
 def _interleave_gathered_transpose(stacked: torch.Tensor, world: int) -> torch.Tensor:
@@ -180,11 +197,14 @@ class _QuantizedLinear(torch.autograd.Function):
             else:
                 accumulate = ctx.fuse_wgrad_accumulation
             main_grad = w.main_grad if ctx.fuse_wgrad_accumulation else None
-            wgrad = op.qgemm(qres_dy.data_t, qx_t, p.mm_wgrad,
-                             main_grad.dtype if main_grad is not None else torch.float32,
-                             qres_dy.scale_t, sx_t, None, out=main_grad, accumulate=accumulate,
-                             global_amax_qx=qres_dy.global_amax_col, global_amax_qw=amax_x_col,
-                             qparams_x=p.g_params, qparams_w=p.x_params)
+            # a reduce-scatter / all-reduce of dgrad is in flight: leave it SMs to run on
+            margin = _overlap_sm_margin() if handle is not None else 0
+            with _sm_margin(op, margin):
+                wgrad = op.qgemm(qres_dy.data_t, qx_t, p.mm_wgrad,
+                                 main_grad.dtype if main_grad is not None else torch.float32,
+                                 qres_dy.scale_t, sx_t, None, out=main_grad, accumulate=accumulate,
+                                 global_amax_qx=qres_dy.global_amax_col, global_amax_qw=amax_x_col,
+                                 qparams_x=p.g_params, qparams_w=p.x_params)
             wgrad = _QuantizedLinear.reset_wgrad_if_needed(ctx, w, wgrad)
 
         if handle is not None:

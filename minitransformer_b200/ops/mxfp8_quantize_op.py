@@ -33,6 +33,10 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
         return Q.QuantizeResult(r.data.view(mxfp8_output_t), r.scale, data_t, r.scale_t, None, None,
                                 r.scale_swz, r.scale_t_swz)
 
+    def sm_margin(self, sms: int):
+        """Context in which this op's GEMMs leave `sms` SMs idle (for a collective in flight)."""
+        return kernels.sm_margin(sms)
+
     def qgemm(self, qx, qw, m_params, out_dtype, sx, sw, bias=None, out=None, accumulate=False,
               global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):
         if out is not None:

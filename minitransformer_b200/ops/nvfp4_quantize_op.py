@@ -65,6 +65,10 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
         return Q.QuantizeResult(r.data, scale, r.data_t, scale_t, r.amax_row, r.amax_col,
                                 r.scale_swz, r.scale_t_swz)
 
+    def sm_margin(self, sms: int):
+        """Context in which this op's GEMMs leave `sms` SMs idle (for a collective in flight)."""
+        return kernels.sm_margin(sms)
+
     def qgemm(self, qx, qw, m_params, out_dtype, sx, sw, bias=None, out=None, accumulate=False,
               global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):
         assert global_amax_qx is not None and global_amax_qw is not None, "NVFP4 needs the per-tensor abs-max"
