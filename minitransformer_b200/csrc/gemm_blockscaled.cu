@@ -812,24 +812,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       const bool row_ok = row >= t.d_row_lo && row < t.d_row_hi;
       const int64_t colw = t.d_col0 + half * 128;            // first of this warp's columns
       const uint32_t tmem_w = tmem_base + Cfg::TMEM_ACC + as * BN + (static_cast<uint32_t>(q * 32) << 16) + half * 128;
-      // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
-      // so a block that straddles a group boundary takes the direct, row-masked path.
-      const bool staged = a.tma_store && row0 >= t.d_row_lo && (row0 + 32 <= t.d_row_hi || t.hi_is_end);
-      if (!staged) {
-        // direct path (unaligned outputs, bf16 accumulate, group edges): registers -> global
-#pragma unroll 1
-        for (int c = 0; c * 32 < ncols; ++c) {
-          uint32_t r[32];
-          tc_ld_32x32(tmem_w + c * 32, r);
-          tc_wait_ld();
-          const int64_t col0 = colw + c * 32;
-          if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, num_k > 0, t.d_base + row * a.ldd + col0, col0);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-        continue;
-      }
       // Pull this warp's accumulator block into registers and hand tensor memory back to the
       // MMA issuer at once; conversion and stores overlap the MMAs that follow.
       uint32_t acc[4][32];
@@ -841,7 +823,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       if (a.debug_skip_store) continue;
-
+      // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
+      // so a block that straddles a group boundary takes the direct, row-masked path (as do
+      // unaligned outputs and bf16 accumulation).
+      const bool staged = a.tma_store == 1 && row0 >= t.d_row_lo && (row0 + 32 <= t.d_row_hi || t.hi_is_end);
+      if (!staged) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int64_t col0 = colw + c * 32;
+          if (c * 32 < ncols && row_ok && col0 < a.N)
+            store_row_chunk(a, acc[c], alpha, num_k > 0, t.d_base + row * a.ldd + col0, col0);
+        }
+        continue;
+      }
       store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
                          t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0);
     }
@@ -979,7 +973,7 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
   if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
   CUtensorMap md = ma;
-  args.tma_store = allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16);
+  args.tma_store = (allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16)) ? allow_tma_store : 0;
   args.map_rows = d_rows;
   if (args.tma_store) {
     const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;

@@ -2,6 +2,7 @@
 torch.distributed on the caller's process group (NCCL over NVLink on GPUs, gloo in the CPU
 tests). Same entry points as miniTransformer/distributed/distributed.py:13-121, plus the
 packed quantized all-gather this implementation adds."""
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -88,34 +89,73 @@ def gather_packed_along_first_dim(parts: Sequence[torch.Tensor], process_group) 
     return tuple(res)
 
 
-def _gather_bytes(t: torch.Tensor, out_shape, process_group, async_op: bool = False):
-    """All-gather of a contiguous tensor as bytes, rank-major, into a new tensor of out_shape."""
+def _coalesce_gathers(world: int) -> bool:
+    """One coalesced launch or one collective per tensor: MT_TP_COALESCE=0/1 decides, else the
+    measured preference (separate collectives on 2 ranks, where the coalesced form was slower)."""
+    v = os.environ.get("MT_TP_COALESCE")
+    if v is not None:
+        return v not in ("0", "")
+    return world >= 4
+
+
+def _gather_many_bytes(tensors, out_shapes, process_group, async_op: bool = False):
+    """All-gathers several contiguous tensors as bytes, each rank-major into a new tensor of the
+    given shape, as ONE coalesced NCCL launch where the backend offers it (the per-collective
+    latency is what counts for the small scale tensors, above all on 8 ranks); otherwise one
+    collective per tensor. Returns (outputs, handles)."""
     world = get_distributed_world_size(process_group)
-    src = t.contiguous().view(torch.uint8).reshape(-1)
-    out = torch.empty(world * src.numel(), dtype=torch.uint8, device=src.device)
-    handle = dist.all_gather_into_tensor(out, src, group=process_group, async_op=async_op)
-    return out.view(*out_shape), handle
+    srcs = [t.contiguous().view(torch.uint8).reshape(-1) for t in tensors]
+    outs = [torch.empty(world * s.numel(), dtype=torch.uint8, device=s.device) for s in srcs]
+    group = process_group if process_group is not None else dist.group.WORLD
+    handles = []
+    coalesced = getattr(group, "allgather_into_tensor_coalesced", None)
+    done = False
+    if coalesced is not None and len(srcs) > 1 and srcs[0].is_cuda and _coalesce_gathers(world):
+        try:
+            work = coalesced(outs, srcs)
+            if async_op:
+                handles.append(work)
+            else:
+                work.wait()
+            done = True
+        except (RuntimeError, NotImplementedError, TypeError):
+            done = False
+    if not done:
+        for o, s_ in zip(outs, srcs):
+            handles.append(dist.all_gather_into_tensor(o, s_, group=process_group, async_op=async_op))
+    return [o.view(*shape) for o, shape in zip(outs, out_shapes)], [h for h in handles if h is not None]
 
 
-def gather_gemm_ready(data: torch.Tensor, scale_swz: torch.Tensor, process_group):
-    """Gathers a row-sharded quantized tensor in the form the GEMM reads: codes [rows, bytes]
-    concatenated along rows, and GEMM-layout scales, whose 128-row chunk lists simply follow
-    one another when every shard is a multiple of 128 rows. No copy after the collectives."""
+def gather_gemm_ready(data: torch.Tensor, scale_swz: torch.Tensor, process_group, data_t=None, scale_t_swz=None,
+                      async_op: bool = False):
+    """Gathers a token-sharded quantized tensor in the form the GEMMs read, with no copy after
+    the collective.
+    * Row-wise codes [rows, bytes] are concatenated along rows; GEMM-layout scales are gathered
+      as they are: with shards of whole 128-row chunks the ranks' chunk lists follow one another.
+    * The transposed copy of rank r, [features, tokens / world], is slab r of the contraction
+      dimension of the gathered x^T; the result [world, features, bytes] (and the per-rank
+      GEMM-layout scale buffers back to back) is what the K-slab GEMM entry points take.
+    Returns (codes, scales, codes_t or None, scales_t or None, handles)."""
     world = get_distributed_world_size(process_group)
     assert data.shape[0] % 128 == 0, "row shards must be multiples of 128 rows"
-    g_data, _ = _gather_bytes(data, (world * data.shape[0], data.shape[1] * data.element_size()), process_group)
-    g_scale, _ = _gather_bytes(scale_swz, (world * scale_swz.numel(),), process_group)
-    return g_data, g_scale
+    tensors = [data, scale_swz]
+    shapes = [(world * data.shape[0], data.shape[1] * data.element_size()), (world * scale_swz.numel(),)]
+    if data_t is not None:
+        tensors += [data_t, scale_t_swz]
+        shapes += [(world, data_t.shape[0], data_t.shape[1] * data_t.element_size()), (world * scale_t_swz.numel(),)]
+    outs, handles = _gather_many_bytes(tensors, shapes, process_group, async_op)
+    if data_t is None:
+        outs += [None, None]
+    return outs[0], outs[1], outs[2], outs[3], handles
 
 
 def gather_transposed_as_k_slabs(data_t: torch.Tensor, scale_t_swz: torch.Tensor, process_group,
                                  async_op: bool = False):
-    """Gathers the transposed copies of token shards. Rank r's copy [features, tokens / world]
-    is slab r of the contraction dimension of the gathered x^T; the result [world, features,
-    bytes] (and the per-rank GEMM-layout scale buffers back to back) is consumed as it is by
-    the K-slab GEMM entry points, so nothing is re-interleaved. Returns (codes, scales, handles)."""
+    """The transposed half of gather_gemm_ready on its own (the memory-saving mode gathers x^T
+    again in backward). Returns (codes [world, features, bytes], scales, handles)."""
     world = get_distributed_world_size(process_group)
-    g_data, h0 = _gather_bytes(data_t, (world, data_t.shape[0], data_t.shape[1] * data_t.element_size()),
-                               process_group, async_op)
-    g_scale, h1 = _gather_bytes(scale_t_swz, (world * scale_t_swz.numel(),), process_group, async_op)
-    return g_data, g_scale, (h0, h1)
+    outs, handles = _gather_many_bytes(
+        [data_t, scale_t_swz],
+        [(world, data_t.shape[0], data_t.shape[1] * data_t.element_size()), (world * scale_t_swz.numel(),)],
+        process_group, async_op)
+    return outs[0], outs[1], handles

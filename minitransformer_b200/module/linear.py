@@ -276,13 +276,13 @@ class _QuantizedLinear(torch.autograd.Function):
         stay per-rank K slabs ([world, features, bytes]) that the wgrad GEMM walks slab by slab.
         The scale fields of the result hold the GEMM layout (the row-major form is not
         materialized on this path)."""
-        data, scale = gather_gemm_ready(r.data, r.scale_swz, tp_group)
+        data, scale, data_t, scale_t, _ = gather_gemm_ready(
+            r.data, r.scale_swz, tp_group, r.data_t if gather_t else None, r.scale_t_swz if gather_t else None)
         if r.data.dtype != torch.uint8:
             data = data.view(r.data.dtype)
         scale._mt_swz = scale
         out = quantization.QuantizeResult(data, scale, None, None, r.global_amax_row, r.global_amax_col, scale, None)
         if gather_t:
-            data_t, scale_t, _ = gather_transposed_as_k_slabs(r.data_t, r.scale_t_swz, tp_group)
             if r.data_t.dtype != torch.uint8:
                 data_t = data_t.view(r.data_t.dtype)
             scale_t._mt_swz = scale_t
