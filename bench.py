@@ -35,6 +35,7 @@ C2 = dict(tokens=8192, in_features=4096, out_features=14336)
 # 270.4, 155.5 and 279.0 MB). Slightly below the algorithmic bytes because part of each output
 # is still in L2 when the kernel ends.
 GEMM_DRAM_BYTES_PER_LAUNCH = 235.0e6
+C3 = dict(experts=128, rows=131072, hidden=2048, ffn=768)
 C4 = dict(tokens=8192, hidden=8192, ffn=28672)
 CPU_SAMPLE = dict(tokens=512, in_features=4096, out_features=3584)
 
@@ -203,6 +204,77 @@ def _tp_workload_single_gpu(torch, Linear, params, dev, kernels, steps=5, warmup
     flops = 6 * 2.0 * T * H * Fd
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
             "workload": f"NVFP4 MLP fc1+fc2 fwd+bwd, tokens={T}, hidden={H}, ffn={Fd}, no sharding"}
+
+
+def _timed_loop(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _other_configs_single_gpu(torch, dev, steps=5, warmup=3):
+    """The two MXFP8 configurations beside the headline one, on one GPU: the dense forward
+    (4096^3) and the grouped (MoE expert) fc1 + fc2 forward+backward through GroupedLinear."""
+    import numpy as np
+    from minitransformer_b200.module import config as mt_config
+    from minitransformer_b200.module.group_linear import GroupedLinear
+    out = {}
+    params = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    op = params.quantize_op
+    gen = torch.Generator(device="cpu").manual_seed(99)
+
+    # dense MXFP8 forward: quantize x and w (row-wise), one GEMM
+    M = N = Kd = 4096
+    x = torch.randn(M, Kd, generator=gen).to(torch.bfloat16).to(dev)
+    w = (torch.randn(N, Kd, generator=gen) * 0.02).to(torch.bfloat16).to(dev)
+
+    def fwd():
+        qx = op.quantize(x, params.x_params, return_transpose=False)
+        qw = op.quantize(w, params.w_params, return_transpose=False)
+        return op.qgemm(qx.data, qw.data, params.mm_fprop, torch.bfloat16, qx.scale, qw.scale)
+
+    ms = _timed_loop(torch, fwd, 20, warmup)
+    qx = op.quantize(x, params.x_params, return_transpose=False)
+    qw = op.quantize(w, params.w_params, return_transpose=False)
+    ms_g = _timed_loop(torch, lambda: op.qgemm(qx.data, qw.data, params.mm_fprop, torch.bfloat16, qx.scale, qw.scale),
+                       20, warmup)
+    out["mxfp8_linear_fwd_4096"] = {"value": 2.0 * M * N * Kd / (ms * 1e-3) / 1e12, "unit": UNIT, "ms": ms,
+                                    "gemm_only_tflops": 2.0 * M * N * Kd / (ms_g * 1e-3) / 1e12,
+                                    "workload": "MXFP8 quantize(x) + quantize(w) + GEMM, M=N=K=4096"}
+    del x, w, qx, qw
+
+    # grouped MXFP8: 128 experts, 131072 rows, Zipf(1.1) group sizes, hidden 2048, ffn 768
+    G, R, H, Fd = C3["experts"], C3["rows"], C3["hidden"], C3["ffn"]
+    rng = np.random.default_rng(1234)
+    p = 1.0 / np.arange(1, G + 1) ** 1.1
+    m_splits = np.bincount(rng.choice(G, size=R, p=p / p.sum()), minlength=G).tolist()
+    init = lambda t: torch.nn.init.normal_(t, std=0.02)
+    kw = dict(bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params, init_method=init)
+    fc1, fc2 = GroupedLinear(G, H, Fd, **kw), GroupedLinear(G, Fd, H, **kw)
+    xg = torch.randn(R, H, generator=gen).to(torch.bfloat16).to(dev)
+    dyg = (torch.randn(R, H, generator=gen) * 1e-3).to(torch.bfloat16).to(dev)
+
+    def moe_step():
+        for m in (fc1, fc2):
+            for prm in m.parameters():
+                prm.grad = None
+        xd = xg.detach().requires_grad_(True)
+        y = fc2(fc1(xd, m_splits, is_first_microbatch=True), m_splits, is_first_microbatch=True)
+        y.backward(dyg)
+
+    ms = _timed_loop(torch, moe_step, steps, warmup)
+    flops = 6 * 2.0 * R * H * Fd
+    out["mxfp8_grouped_linear_fwd_bwd"] = {
+        "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
+        "workload": f"GroupedLinear fc1+fc2 fwd+bwd, {G} experts, {R} rows (Zipf 1.1 sizes), hidden {H}, ffn {Fd}"}
+    return out
 
 
 def run_gpu_arm(args):
@@ -405,6 +477,7 @@ def run_gpu_arm(args):
                 "achieved_counting_one_read": elts * 3.125 / (q_avg * 1e-3) / 1e9,
                 "peak_source": f"{peaks['source']} copy bandwidth"}
             line["tp_workload_on_1_gpu"] = _tp_workload_single_gpu(torch, Linear, params, dev, kernels)
+            line["other_configs"] = _other_configs_single_gpu(torch, dev)
             tf, dt = cpu_run(4, 1)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": _cpu_sample_text(), "s_per_sample_step": dt}

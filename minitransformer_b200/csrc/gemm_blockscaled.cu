@@ -876,10 +876,11 @@ template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t st) {
   using Cfg = GemmCfg<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
   auto kern = gemm_blockscaled_kernel<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[MT_MAX_DEVICES] = {};
+  const int slot = current_device_slot();
+  if (!attr_set[slot]) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
-    attr_set = true;
+    attr_set[slot] = true;
   }
   const int grid = std::min(args.num_tiles, std::max(1, sm_count() - g_sm_margin));
   kern<<<grid, G_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, args);
@@ -894,8 +895,9 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
                             const CUtensorMap& msb, const CUtensorMap& md, const GemmArgs& args, cudaStream_t st) {
   using Cfg = PairCfg<kFormat, BN, STAGES>;
   auto kern = gemm_blockscaled_pair_kernel<kFormat, BN, STAGES>;
-  static int max_pairs = -1;
-  if (max_pairs < 0) {
+  static int max_pairs_dev[MT_MAX_DEVICES] = {};   // 0 = not yet queried on that device
+  int& max_pairs = max_pairs_dev[current_device_slot()];
+  if (max_pairs <= 0) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
     // how many 2-CTA clusters can be resident at once (SMs pair up inside a GPC)
     cudaLaunchConfig_t cfg = {};

@@ -281,4 +281,13 @@ __device__ __forceinline__ uint64_t umma_desc_sf(uint32_t addr) {
 
 #endif  // __CUDACC__
 
+// Per-device one-time setup (function attributes are per device): returns the ordinal of the
+// current device, clamped to the cache size used by the launchers.
+constexpr int MT_MAX_DEVICES = 64;
+inline int current_device_slot() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < MT_MAX_DEVICES) ? dev : 0;
+}
+
 }  // namespace mt

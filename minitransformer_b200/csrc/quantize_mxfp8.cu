@@ -230,12 +230,13 @@ static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3)
 
 template <bool T, bool GRP = false>
 static int launch_mxfp8(const CUtensorMap& map, const Mxfp8Args& args, dim3 grid, cudaStream_t st) {
-  static bool attr_set = false;
+  static bool attr_set[MT_MAX_DEVICES] = {};
+  const int slot = current_device_slot();
   auto kern = quantize_mxfp8_kernel<T, GRP>;
   const int smem = (int)sizeof(Mxfp8Smem) + 128;
-  if (!attr_set) {
+  if (!attr_set[slot]) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
+    attr_set[slot] = true;
   }
   kern<<<grid, Q_THREADS, smem, st>>>(map, args);
   MT_CUDA(cudaGetLastError());

@@ -312,12 +312,13 @@ static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3)
 
 template <bool T, bool D2, bool R>
 static int launch_nvfp4(const CUtensorMap& map, const Nvfp4Args& args, dim3 grid, cudaStream_t st) {
-  static bool attr_set = false;
+  static bool attr_set[MT_MAX_DEVICES] = {};
+  const int slot = current_device_slot();
   auto kern = quantize_nvfp4_kernel<T, D2, R>;
   const int smem = (int)sizeof(Nvfp4Smem) + 128;
-  if (!attr_set) {
+  if (!attr_set[slot]) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
+    attr_set[slot] = true;
   }
   kern<<<grid, Q_THREADS, smem, st>>>(map, args);
   MT_CUDA(cudaGetLastError());

@@ -45,3 +45,15 @@ def noop_cat(tensors: Sequence[torch.Tensor], dim: int = 0) -> torch.Tensor:
     if len(tensors) == 1:
         return tensors[0]
     return _NoopCat.apply(dim, *tensors)
+
+
+def stacked_view(tensors: Sequence[torch.Tensor]):
+    """[len(tensors), *shape] view over tensors that sit back to back in one buffer (expert
+    weights allocated from one block, or their main_grad buffers), or None when they do not."""
+    if not tensors or not _adjacent(tensors):
+        return None
+    first = tensors[0]
+    out = first.detach().new_empty(0)
+    out.set_(first.untyped_storage(), first.storage_offset(), [len(tensors), *first.shape],
+             [first.numel(), *first.stride()])
+    return out

@@ -17,6 +17,7 @@ from typing import Callable, List, Optional, Tuple, Union
 import torch
 
 from . import config
+from ._common import stacked_view
 from .base import LayerLinearBaseModule
 from ..distributed.distributed import allreduce, get_distributed_rank, set_tensor_model_parallel_attributes
 from ..ops import quantization
@@ -40,8 +41,11 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
 
         qres_x = op.quantize(x, qlinear_params.x_params, return_transpose=False)
         if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
-            qres_w = op.grouped_quantize(torch.stack(weights, dim=0), qlinear_params.w_params,
-                                         return_transpose=is_grad_enabled)
+            # expert weights allocated by this module sit back to back: no stacking copy
+            w_all = stacked_view(weights)
+            if w_all is None:
+                w_all = torch.stack(weights, dim=0)
+            qres_w = op.grouped_quantize(w_all, qlinear_params.w_params, return_transpose=is_grad_enabled)
             weight_qresult_cache.store(qres_w)
         else:
             qres_w = weight_qresult_cache.to_qresult()
@@ -85,15 +89,31 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
         if any(w.requires_grad for w in ctx.weights):
             dy_t = op.grouped_transpose_quantize(dy, ctx.m_splits)
             x_t = op.grouped_transpose_quantize(x, ctx.m_splits)
-            out_dtype_wgrad = p.mm_wgrad.out_dtype or torch.float32
-            wg = op.grouped_gemm_1d1d(dy_t, x_t, out_dtype_wgrad, single_output=True)
             accumulate = ctx.fuse_wgrad_accumulation and (ctx.is_first_microbatch is None or not ctx.is_first_microbatch)
+            # Output type: the main_grad type when accumulating there; otherwise the parameter
+            # type, which is what autograd would cast an fp32 gradient to (one rounding of the
+            # fp32 accumulator either way), unless the recipe names a type.
+            main_all = None
+            if ctx.fuse_wgrad_accumulation:
+                out_dtype_wgrad = ctx.weights[0].main_grad.dtype
+                if all(w.requires_grad for w in ctx.weights):
+                    main_all = stacked_view([w.main_grad for w in ctx.weights])
+            else:
+                out_dtype_wgrad = p.mm_wgrad.out_dtype or ctx.weights[0].dtype
+            if main_all is not None:
+                # main_grad buffers sit back to back: the GEMM writes (or accumulates) in place
+                wg = op.grouped_gemm_1d1d(dy_t, x_t, out_dtype_wgrad, single_output=True, out=main_all,
+                                          accumulate=accumulate)
+            else:
+                wg = op.grouped_gemm_1d1d(dy_t, x_t, out_dtype_wgrad, single_output=True)
             for i, w in enumerate(ctx.weights):
                 if not w.requires_grad:
                     continue
                 if ctx.fuse_wgrad_accumulation:
                     # Megatron main_grad protocol, per expert
-                    if accumulate:
+                    if main_all is not None:
+                        pass
+                    elif accumulate:
                         w.main_grad.add_(wg[i])
                     else:
                         w.main_grad.copy_(wg[i])
@@ -174,10 +194,12 @@ class GroupedLinear(LayerLinearBaseModule):
         if is_rank_0():
             logger.info("layer %s grouped linear %s (%d experts) uses %s", layer_number, self.layer_name, num_gemms,
                         self.qlinear_params)
+        # All expert weights live in one block, each `weight{i}` a view of it, so that the
+        # grouped quantize reads them as one [num_gemms, out, in] tensor without a stacking copy.
+        block = torch.empty(num_gemms, self.out_features, self.in_features, device=device, dtype=params_dtype)
         for i in range(num_gemms):
-            self.register_parameter(f"weight{i}", torch.nn.Parameter(
-                torch.empty(self.out_features, self.in_features, device=device, dtype=params_dtype)),
-                init_fn=init_method, get_rng_state_tracker=get_rng_state_tracker)
+            self.register_parameter(f"weight{i}", torch.nn.Parameter(block[i]),
+                                    init_fn=init_method, get_rng_state_tracker=get_rng_state_tracker)
             if bias:
                 self.register_parameter(f"bias{i}", torch.nn.Parameter(
                     torch.empty(self.out_features, device=device, dtype=params_dtype)), init_fn=init_method_constant(0.0))

@@ -201,7 +201,9 @@ class _QuantizedLinear(torch.autograd.Function):
             margin = _overlap_sm_margin() if handle is not None else 0
             with _sm_margin(op, margin):
                 wgrad = op.qgemm(qres_dy.data_t, qx_t, p.mm_wgrad,
-                                 main_grad.dtype if main_grad is not None else torch.float32,
+                                 # without main_grad: the parameter's type, what autograd would cast an
+                                 # fp32 gradient to (one rounding of the fp32 accumulator either way)
+                                 main_grad.dtype if main_grad is not None else (p.mm_wgrad.out_dtype or w.dtype),
                                  qres_dy.scale_t, sx_t, None, out=main_grad, accumulate=accumulate,
                                  global_amax_qx=qres_dy.global_amax_col, global_amax_qw=amax_x_col,
                                  qparams_x=p.g_params, qparams_w=p.x_params)

@@ -48,3 +48,18 @@ def test_front_end_refuses_cpu_tensors():
     from minitransformer_b200 import kernels
     with pytest.raises(_lib.MtError):
         kernels.quantize_nvfp4(torch.zeros(16, 16, dtype=torch.bfloat16))
+
+
+def test_stacked_view_of_adjacent_parameters_is_copy_free():
+    """Expert weights allocated as views of one block are read as one stacked tensor; separate
+    allocations are reported as not stackable (the caller then copies)."""
+    import torch
+    from minitransformer_b200.module._common import stacked_view
+    from minitransformer_b200.module import group_linear  # noqa: F401  (the module imports cleanly)
+    block = torch.randn(4, 3, 5)
+    params = [torch.nn.Parameter(block[i]) for i in range(4)]
+    view = stacked_view(params)
+    assert view is not None and view.shape == (4, 3, 5)
+    assert view.data_ptr() == block.data_ptr() and torch.equal(view, block)
+    assert stacked_view([torch.randn(3, 5) for _ in range(3)]) is None
+    assert stacked_view([block[0], block[2]]) is None
