@@ -257,7 +257,15 @@ def _other_configs_single_gpu(torch, dev, steps=5, warmup=3):
     m_splits = np.bincount(rng.choice(G, size=R, p=p / p.sum()), minlength=G).tolist()
     init = lambda t: torch.nn.init.normal_(t, std=0.02)
     kw = dict(bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params, init_method=init)
+    fused = os.environ.get("MT_BENCH_MOE_FUSED", "1") != "0"
+    kw["fuse_wgrad_accumulation"] = fused
     fc1, fc2 = GroupedLinear(G, H, Fd, **kw), GroupedLinear(G, Fd, H, **kw)
+    if fused:
+        # Megatron-style fp32 main_grad buffers, one block per layer
+        for m in (fc1, fc2):
+            block = torch.zeros(G, m.out_features, m.in_features, dtype=torch.float32, device=dev)
+            for i in range(G):
+                getattr(m, f"weight{i}").main_grad = block[i]
     xg = torch.randn(R, H, generator=gen).to(torch.bfloat16).to(dev)
     dyg = (torch.randn(R, H, generator=gen) * 1e-3).to(torch.bfloat16).to(dev)
 

@@ -234,20 +234,32 @@ def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, ac
 
 
 # ---- grouped (per-expert) MXFP8 path ----
+# The same m_splits list is used by every grouped call of a training step (fc1 / fc2, forward and
+# backward): its prefix sums and their ctypes form are kept for the last few distinct lists.
+_OFFSETS_CACHE: dict = {}
+
+
 def _offsets_array(m_splits):
     import ctypes
-    off = [0]
-    for m in m_splits:
-        off.append(off[-1] + int(m))
-    return (ctypes.c_int64 * len(off))(*off), off
+    key = tuple(m_splits)
+    hit = _OFFSETS_CACHE.get(key)
+    if hit is None:
+        off = [0]
+        for m in key:
+            off.append(off[-1] + int(m))
+        pad = [0]
+        for m in key:
+            pad.append(pad[-1] + (int(m) + 127) // 128 * 128)
+        if len(_OFFSETS_CACHE) >= 8:
+            _OFFSETS_CACHE.pop(next(iter(_OFFSETS_CACHE)))
+        hit = _OFFSETS_CACHE[key] = ((ctypes.c_int64 * len(off))(*off), off, pad)
+    return hit[0], hit[1]
 
 
 def grouped_padded_offsets(m_splits):
     """Token offsets after padding every group to a multiple of 128 tokens."""
-    off = [0]
-    for m in m_splits:
-        off.append(off[-1] + (int(m) + 127) // 128 * 128)
-    return off
+    _offsets_array(m_splits)
+    return _OFFSETS_CACHE[tuple(m_splits)][2]
 
 
 def _grouped_scratch(rows: int, groups: int, device) -> torch.Tensor:

@@ -47,12 +47,26 @@ def noop_cat(tensors: Sequence[torch.Tensor], dim: int = 0) -> torch.Tensor:
     return _NoopCat.apply(dim, *tensors)
 
 
+_STACKED_OK: dict = {}
+
+
 def stacked_view(tensors: Sequence[torch.Tensor]):
     """[len(tensors), *shape] view over tensors that sit back to back in one buffer (expert
     weights allocated from one block, or their main_grad buffers), or None when they do not."""
-    if not tensors or not _adjacent(tensors):
+    if not tensors:
         return None
-    first = tensors[0]
+    # the full adjacency walk costs one Python call per tensor: remember its verdict for this
+    # exact set of tensor objects at these addresses
+    first, last = tensors[0], tensors[-1]
+    key = (tuple(map(id, tensors)), first.data_ptr(), last.data_ptr(), first.dtype)
+    ok = _STACKED_OK.get(key)
+    if ok is None:
+        ok = _adjacent(tensors)
+        if len(_STACKED_OK) >= 64:
+            _STACKED_OK.clear()
+        _STACKED_OK[key] = ok
+    if not ok:
+        return None
     out = first.detach().new_empty(0)
     out.set_(first.untyped_storage(), first.storage_offset(), [len(tensors), *first.shape],
              [first.numel(), *first.stride()])
