@@ -197,28 +197,33 @@ __device__ __forceinline__ float bias_at(const GemmArgs& a, int64_t col) {
 }
 
 // One warp's 32 rows x `ncols` (<= 128) accumulator block, already in registers (acc[c][i] =
-// column 32c + i of this lane's row), -> alpha / bias -> bf16 or fp32 -> a 4 KiB shared-memory
-// buffer in the 128-byte-swizzled layout -> TMA store (or TMA add-reduction for fp32
-// accumulation) of 64 (bf16) or 32 (fp32) columns at a time. `row0` / `colw` are the block's
-// first row / column in the tensor map's coordinates; rows and columns beyond the map's
-// bounds are clipped by the hardware.
+// column 32c + i of this lane's row), -> alpha / bias -> bf16 or fp32 -> shared memory -> TMA
+// store (or TMA add-reduction for fp32 accumulation). The warp's 4 KiB buffer is used as two
+// 2 KiB halves of 32 rows x 64 bytes (64-byte swizzle) in alternation: filling one half overlaps
+// the TMA engine reading the other. 32 (bf16) or 16 (fp32) columns per store. `row0` / `colw`
+// are the block's first row / column in the tensor map's coordinates; rows and columns beyond
+// the map's bounds are clipped by the hardware.
 __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUtensorMap* map_d,
-                                                   const uint32_t (&acc)[4][32], int ncols, uint8_t* stage, int lane,
-                                                   int64_t row0, int64_t map_rows, int64_t colw, float alpha,
-                                                   bool has_k) {
-  const uint32_t swz = lane & 7;
-  if (a.d_dtype == MT_BF16) {
+                                                        const uint32_t (&acc)[4][32], int ncols, uint8_t* stage,
+                                                        int lane, int64_t row0, int64_t map_rows, int64_t colw,
+                                                        float alpha, bool has_k) {
+  const uint32_t swz = (lane >> 1) & 3;
+  const bool f32 = a.d_dtype == MT_F32;
+  const int cols_per = f32 ? 16 : 32;
+  const int nchunks = ncols / cols_per;
 #pragma unroll
-    for (int ch = 0; ch < 2; ++ch) {           // 64 columns = 128 bytes per row
-      if (ch * 64 >= ncols) break;
-      if (lane == 0) bulk_wait_read_all();     // the previous store has drained the buffer
-      __syncwarp();
+  for (int ch = 0; ch < 8; ++ch) {
+    if (ch >= nchunks) break;
+    uint8_t* buf = stage + (ch & 1) * 2048;
+    if (lane == 0) bulk_wait_read_all_but_one();   // the store issued two chunks ago has drained this half
+    __syncwarp();
+    if (!f32) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {            // 16-byte chunk j = columns 8j .. 8j+7
+      for (int j = 0; j < 4; ++j) {               // 16-byte piece j = columns 8j .. 8j+7 of the chunk
         uint32_t w[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          const int col = ch * 64 + j * 8 + t * 2;
+          const int col = (ch & 3) * 32 + j * 8 + t * 2;
           float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
           float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
           if (a.bias != nullptr) {
@@ -229,41 +234,31 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
           __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
           w[t] = *reinterpret_cast<uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && row0 < map_rows && colw + ch * 64 < a.N) {
-        tma_store_2d(map_d, stage, (int32_t)(colw + ch * 64), (int32_t)row0);
-        bulk_commit_group();
-      }
-    }
-  } else {
+    } else {
 #pragma unroll
-    for (int ch = 0; ch < 4; ++ch) {           // 32 fp32 columns = 128 bytes per row
-      if (ch * 32 >= ncols) break;
-      if (lane == 0) bulk_wait_read_all();
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {               // 16-byte piece j = columns 4j .. 4j+3 of the chunk
         float v[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-          v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[ch][j * 4 + t])) : 0.0f;
+          const int col = ch * 16 + j * 4 + t;
+          v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
           if (a.bias != nullptr) {
-            const int64_t gc = colw + ch * 32 + j * 4 + t;
+            const int64_t gc = colw + col;
             if (gc < a.N) v[t] += bias_at(a, gc);
           }
         }
-        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(buf + lane * 64 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
       }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && row0 < map_rows && colw + ch * 32 < a.N) {
-        if (a.accumulate) tma_reduce_add_2d(map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
-        else tma_store_2d(map_d, stage, (int32_t)(colw + ch * 32), (int32_t)row0);
-        bulk_commit_group();
-      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    const int64_t c0 = colw + (int64_t)ch * cols_per;
+    if (lane == 0 && row0 < map_rows && c0 < a.N) {
+      if (f32 && a.accumulate) tma_reduce_add_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
+      else tma_store_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
+      bulk_commit_group();
     }
   }
 }
@@ -525,9 +520,10 @@ struct PairCfg {
   static constexpr int OFF_B = STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
-  // one 4 KiB output staging buffer per epilogue warp (a second buffer per warp would cost a
-  // pipeline stage, which measured slower); 1024-byte aligned so the swizzle pattern of the
-  // TMA store lines up with the row index used when filling it
+  // one 4 KiB output staging buffer per epilogue warp, used as two alternating 2 KiB halves (a
+  // second 4 KiB buffer per warp would cost a pipeline stage, which measured slower);
+  // 1024-byte aligned so the swizzle pattern of the TMA store lines up with the row index
+  // used when filling it
   static constexpr int OFF_EPI = (OFF_SFB + STAGES * SFB_BYTES + 1023) / 1024 * 1024;
   static constexpr int EPI_BYTES = P_EPI_WARPS * 4096;
   static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;
@@ -661,6 +657,8 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& a, int tile) {
 }
 
 template <int kFormat, int BN, int STAGES>
+// Register budget: 10 warps land 3 + 3 + 2 + 2 on the four SM sub-partitions of 16384 registers
+// each, so 168 per thread is the most that launches (more fails with "too many resources").
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                  const __grid_constant__ CUtensorMap map_sfa,
@@ -979,8 +977,9 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   args.map_rows = d_rows;
   if (args.tma_store) {
     const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    // box: 32 rows x 64 bytes (half of a warp's staging buffer), 64-byte swizzle
     rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)d_cols, (uint64_t)d_rows, (uint64_t)ldd * es,
-                            d_dtype == MT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+                            d_dtype == MT_F32 ? 16 : 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != MT_OK) return rc;
   }
   if (format == FMT_NVFP4)
