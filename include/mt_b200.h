@@ -183,6 +183,19 @@ int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t col
                                         uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
                                         void* scratch, int64_t scratch_bytes, mt_stream_t stream);
 
+/* The same transposed copy plus, from the same read of x, the plain row-wise copy that
+ * mt_quantize_mxfp8 would produce: q [rows, cols], s (optional, row-major [rows, cols/32], stride
+ * s_stride) and s_swz (GEMM layout, mt_swizzled_scale_bytes(rows, cols/32) bytes; bytes of rows
+ * beyond `rows` in the last 128-row chunk are not written: zero the buffer once if a defined
+ * value is wanted there). One pass over x serves the dgrad operand (row-wise dy) and the wgrad
+ * operand (dy^T per group); the reference's GroupedLinear quantizes and transposes in separate
+ * steps (miniTransformer/module/group_linear.py:87-108, 231-238). */
+int mt_grouped_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
+                              const int64_t* m_offsets_host, int64_t G,
+                              uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                              uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                              void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+
 /* D[rows of g, 0:N] = A[rows of g, 0:K] . B_g^T for every group g. A, D and sa_swz use the
  * plain (unpadded) row numbering. B is one matrix of b_rows rows of ldb bytes; group g uses
  * its rows [g*b_group_rows, +N) and contraction bytes [g*b_group_k, +K):

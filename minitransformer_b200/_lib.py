@@ -34,6 +34,8 @@ _SIGNATURES = {
     "mt_gemm_mxfp8_check": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
     "mt_grouped_scratch_bytes": (_i64, [_i64, _i64]),
     "mt_grouped_padded_rows": (_i64, [_c.POINTER(_i64), _i64, _c.POINTER(_i64)]),
+    "mt_grouped_quantize_mxfp8": (_int, [_vp, _i64, _i64, _c.POINTER(_i64), _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp,
+                                         _vp, _i64, _vp]),
     "mt_grouped_transpose_quantize_mxfp8": (_int, [_vp, _i64, _i64, _c.POINTER(_i64), _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
     "mt_grouped_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _c.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
                                      _vp, _int, _i64, _vp, _i64, _vp]),

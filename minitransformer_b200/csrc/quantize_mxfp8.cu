@@ -36,7 +36,10 @@ struct Mxfp8Args {
   int64_t out_cols;    // padded token count (row length of q_t)
 };
 
-template <bool kTranspose, bool kGrouped = false>
+// kGroupedRow (grouped mode only): also emit the plain row-wise copy of the tile's rows (codes,
+// row-major scales, GEMM-layout scales by global row index), so that one read of the tensor
+// serves both the dgrad operand and the wgrad operand.
+template <bool kTranspose, bool kGrouped = false, bool kGroupedRow = false>
 __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_constant__ CUtensorMap in_map,
                                                                    const Mxfp8Args a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -75,7 +78,7 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
 
   // ---- row pass: thread <-> (row, 1x32 block); 4 blocks per tile row ----
 #pragma unroll
-  for (int it = 0; it < (kGrouped ? 0 : 2); ++it) {
+  for (int it = 0; it < ((kGrouped && !kGroupedRow) ? 0 : 2); ++it) {
     const int r = it * 64 + (tid >> 2);
     const int b = tid & 3;
     uint4 w[4];
@@ -95,7 +98,7 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
       o[2 * i + 1] = e4m3x4_from_words(w[i].z, w[i].w, enc2);
     }
     const int64_t gr = m0 + r, gc = k0 + b * 32;
-    if (gr < a.rows && gc < a.cols) {
+    if (gr < a.rows && gc < a.cols && (!kGrouped || r < gt.y)) {
       uint4* dst = reinterpret_cast<uint4*>(a.q + gr * a.cols + gc);
       dst[0] = out[0];
       dst[1] = out[1];
@@ -157,6 +160,26 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
       const int64_t extra = a.kc_col - ((gt.z >> 7) + 1);
       for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
         *reinterpret_cast<uint4*>(base + 512 + i * 16) = make_uint4(0, 0, 0, 0);
+    }
+    if (kGroupedRow && tid < gt.y) {
+      // row-wise scales of this tile's rows: the tile starts anywhere inside a 128-row chunk of
+      // the GEMM layout, so every row stores its own 4 bytes (one 16-byte cell quarter)
+      const int64_t gr = m0 + tid;
+      const int64_t kb0 = k0 >> 5;
+      const int nvalid = (int)min((int64_t)4, (a.cols >> 5) - kb0);
+      uint32_t word = *reinterpret_cast<const uint32_t*>(sm.s_lin[tid]);
+      if (nvalid < 4) word &= (1u << (8 * nvalid)) - 1u;   // blocks beyond the tensor read as scale byte 0
+      if (a.s != nullptr) {
+        uint8_t* dst = a.s + gr * a.s_stride + kb0;
+        if (nvalid == 4 && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
+        else for (int i = 0; i < nvalid; ++i) dst[i] = sm.s_lin[tid][i];
+      }
+      uint8_t* cell = a.s_swz + ((gr >> 7) * a.kc_row + (k0 >> 7)) * 512 + (gr & 31) * 16 + ((gr >> 5) & 3) * 4;
+      *reinterpret_cast<uint32_t*>(cell) = word;
+      if (k0 + QT_COLS >= a.cols) {  // chunks up to the padded count along K
+        const int64_t extra = a.kc_row - ((k0 >> 7) + 1);
+        for (int64_t i = 1; i <= extra; ++i) *reinterpret_cast<uint32_t*>(cell + i * 512) = 0u;
+      }
     }
     return;
   }
@@ -228,11 +251,11 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
 
 static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
 
-template <bool T, bool GRP = false>
+template <bool T, bool GRP = false, bool GRPROW = false>
 static int launch_mxfp8(const CUtensorMap& map, const Mxfp8Args& args, dim3 grid, cudaStream_t st) {
   static bool attr_set[MT_MAX_DEVICES] = {};
   const int slot = current_device_slot();
-  auto kern = quantize_mxfp8_kernel<T, GRP>;
+  auto kern = quantize_mxfp8_kernel<T, GRP, GRPROW>;
   const int smem = (int)sizeof(Mxfp8Smem) + 128;
   if (!attr_set[slot]) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -290,13 +313,11 @@ extern "C" int64_t mt_grouped_padded_rows(const int64_t* m_offsets_host, int64_t
   return off;
 }
 
-extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
-                                                   const int64_t* m_offsets_host, int64_t G, uint8_t* q_t,
-                                                   uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, void* scratch,
-                                                   int64_t scratch_bytes, mt_stream_t stream) {
-  using namespace mt;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const char* name = "mt_grouped_transpose_quantize_mxfp8";
+namespace mt {
+static int grouped_quantize_mxfp8(const char* name, const void* x, int64_t rows, int64_t cols,
+                                  const int64_t* m_offsets_host, int64_t G, uint8_t* q, uint8_t* s, int64_t s_stride,
+                                  uint8_t* s_swz, uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                                  void* scratch, int64_t scratch_bytes, cudaStream_t st) {
   MT_REQUIRE(m_offsets_host && G > 0, "%s: bad group description", name);
   MT_REQUIRE(m_offsets_host[0] == 0 && m_offsets_host[G] == rows, "%s: offsets must run from 0 to rows", name);
   MT_REQUIRE(cols > 0 && cols % 32 == 0, "%s: cols (%lld) must be a positive multiple of 32", name, (long long)cols);
@@ -323,6 +344,13 @@ extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, 
   args.s_t_stride = s_t_stride;
   args.kc_col = padded_chunks(out_col / 32);
   args.q_t = q_t; args.s_t = s_t; args.s_t_swz = s_t_swz;
+  const bool row_too = q != nullptr;
+  if (row_too) {
+    MT_REQUIRE(s_swz && aligned16(q) && aligned16(s_swz), "%s: row-wise outputs need q and s_swz, 16-byte aligned", name);
+    MT_REQUIRE(!s || s_stride >= cols / 32, "%s: bad s stride", name);
+    args.q = q; args.s = s; args.s_swz = s_swz; args.s_stride = s_stride;
+    args.kc_row = padded_chunks(cols / 32);
+  }
   args.status = device_status_ptr();
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
   args.tiles = static_cast<const int4*>(scratch);
@@ -332,5 +360,25 @@ extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, 
                               (uint64_t)cols * 2, QT_COLS, QT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != MT_OK) return rc;
   dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)tiles.size());
-  return launch_mxfp8<true, true>(map, args, grid, st);
+  return row_too ? launch_mxfp8<true, true, true>(map, args, grid, st) : launch_mxfp8<true, true>(map, args, grid, st);
+}
+}  // namespace mt
+
+extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
+                                                   const int64_t* m_offsets_host, int64_t G, uint8_t* q_t,
+                                                   uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, void* scratch,
+                                                   int64_t scratch_bytes, mt_stream_t stream) {
+  return mt::grouped_quantize_mxfp8("mt_grouped_transpose_quantize_mxfp8", x, rows, cols, m_offsets_host, G, nullptr,
+                                    nullptr, 0, nullptr, q_t, s_t, s_t_stride, s_t_swz, scratch, scratch_bytes,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mt_grouped_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, const int64_t* m_offsets_host,
+                                         int64_t G, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                                         uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, void* scratch,
+                                         int64_t scratch_bytes, mt_stream_t stream) {
+  MT_REQUIRE(q != nullptr, "mt_grouped_quantize_mxfp8: null q");
+  return mt::grouped_quantize_mxfp8("mt_grouped_quantize_mxfp8", x, rows, cols, m_offsets_host, G, q, s, s_stride, s_swz,
+                                    q_t, s_t, s_t_stride, s_t_swz, scratch, scratch_bytes,
+                                    static_cast<cudaStream_t>(stream));
 }

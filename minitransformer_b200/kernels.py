@@ -287,6 +287,33 @@ def grouped_transpose_quantize_mxfp8(x: torch.Tensor, m_splits, want_linear_scal
     return q_t, s_t_swz, s_t, pad
 
 
+def grouped_quantize_mxfp8(x: torch.Tensor, m_splits):
+    """One pass over x [R, K] bf16 -> (Quantized row-wise copy, (q_t [K, Rp], s_t_swz, padded
+    offsets)): what quantize_mxfp8(x, return_transpose=False) and
+    grouped_transpose_quantize_mxfp8(x, m_splits) return, from a single read of x."""
+    _require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    R, K = x.shape
+    arr, off = _offsets_array(m_splits)
+    assert off[-1] == R, "m_splits must sum to the number of rows"
+    pad = grouped_padded_offsets(m_splits)
+    Rp = pad[-1]
+    dev = x.device
+    q = torch.empty((R, K), dtype=torch.uint8, device=dev)
+    s = torch.empty((R, K // 32), dtype=torch.uint8, device=dev)
+    # rows of the last 128-row chunk beyond R are not written by the kernel: start from zeros
+    s_swz = torch.zeros(swizzled_scale_bytes(R, K // 32), dtype=torch.uint8, device=dev)
+    q_t = torch.empty((K, Rp), dtype=torch.uint8, device=dev)
+    s_t_swz = torch.empty(swizzled_scale_bytes(K, Rp // 32), dtype=torch.uint8, device=dev)
+    if R:
+        scratch = _grouped_scratch(R, len(m_splits), dev)
+        _lib.call("mt_grouped_quantize_mxfp8", x.data_ptr(), R, K, arr, len(m_splits), q.data_ptr(), s.data_ptr(),
+                  K // 32, s_swz.data_ptr(), q_t.data_ptr(), None, Rp // 32, s_t_swz.data_ptr(), scratch.data_ptr(),
+                  scratch.numel(), _stream())
+        _count(1)
+    return Quantized(q, s, s_swz), (q_t, s_t_swz, pad)
+
+
 def grouped_gemm_mxfp8(qa, sa_swz, qb, sb_swz, m_splits, *, n_out: int, transposed_weights: bool,
                        out_dtype=torch.bfloat16):
     """Rows of qa [R, K] are split by m_splits; group g uses its own weight.

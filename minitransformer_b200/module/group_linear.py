@@ -39,7 +39,16 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
         x = cast_if_needed(x.reshape(-1, x_shape[-1]), activation_dtype)
         G, (N, K) = len(weights), weights[0].shape
 
-        qres_x = op.quantize(x, qlinear_params.x_params, return_transpose=False)
+        # With a backend that can do it, the per-group transposed copy that wgrad contracts over
+        # is produced by the same pass over x (and saved instead of x itself: 1 byte per element
+        # instead of 2); otherwise x is saved and transposed in backward.
+        fused_t = is_grad_enabled and hasattr(op, "grouped_quantize_with_transpose") and \
+            any(w.requires_grad for w in weights)
+        x_t = None
+        if fused_t:
+            qres_x, x_t = op.grouped_quantize_with_transpose(x, qlinear_params.x_params, m_splits)
+        else:
+            qres_x = op.quantize(x, qlinear_params.x_params, return_transpose=False)
         if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
             # expert weights allocated by this module sit back to back: no stacking copy
             w_all = stacked_view(weights)
@@ -62,7 +71,11 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
             ctx.num_gemms, ctx.in_features = G, K
             ctx.sw_t_swz = qres_w.scale_t_swz
             ctx.weights = weights
-            ctx.save_for_backward(x, qres_w.data_t, qres_w.scale_t)
+            ctx.x_t_pad = x_t[2] if x_t is not None else None
+            if x_t is not None:
+                ctx.save_for_backward(None, qres_w.data_t, qres_w.scale_t, x_t[0], x_t[1])
+            else:
+                ctx.save_for_backward(x, qres_w.data_t, qres_w.scale_t, None, None)
 
         if parallel_mode == "row" and tp_size > 1:
             y, _ = allreduce(y, tp_group)
@@ -70,14 +83,19 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, qw_t, sw_t = ctx.saved_tensors
+        x, qw_t, sw_t, x_t_q, x_t_s = ctx.saved_tensors
         p, op = ctx.qlinear_params, ctx.quantize_op
         if ctx.sw_t_swz is not None:
             sw_t._mt_swz = ctx.sw_t_swz
         out_dtype_dgrad = p.mm_dgrad.out_dtype or dy.dtype
         dy = dy.contiguous().view(-1, dy.shape[-1])
 
-        qres_dy = op.quantize(dy, p.g_params, return_transpose=False)
+        need_wgrad = any(w.requires_grad for w in ctx.weights)
+        dy_t = None
+        if need_wgrad and hasattr(op, "grouped_quantize_with_transpose"):
+            qres_dy, dy_t = op.grouped_quantize_with_transpose(dy, p.g_params, ctx.m_splits)
+        else:
+            qres_dy = op.quantize(dy, p.g_params, return_transpose=False)
         dgrad = op.grouped_qgemm(qres_dy.data, qw_t, p.mm_dgrad, out_dtype_dgrad, qres_dy.scale, sw_t,
                                  m_splits=ctx.m_splits, biases=None, qparams_x=p.g_params, qparams_w=p.w_params,
                                  weights_transposed=True, n_out=ctx.in_features)
@@ -86,9 +104,10 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
             dgrad, handle = allreduce(dgrad, ctx.tp_group, True)
 
         wgrads: List[Optional[torch.Tensor]] = [None] * ctx.num_gemms
-        if any(w.requires_grad for w in ctx.weights):
-            dy_t = op.grouped_transpose_quantize(dy, ctx.m_splits)
-            x_t = op.grouped_transpose_quantize(x, ctx.m_splits)
+        if need_wgrad:
+            if dy_t is None:
+                dy_t = op.grouped_transpose_quantize(dy, ctx.m_splits)
+            x_t = (x_t_q, x_t_s, ctx.x_t_pad) if x_t_q is not None else op.grouped_transpose_quantize(x, ctx.m_splits)
             accumulate = ctx.fuse_wgrad_accumulation and (ctx.is_first_microbatch is None or not ctx.is_first_microbatch)
             # Output type: the main_grad type when accumulating there; otherwise the parameter
             # type, which is what autograd would cast an fp32 gradient to (one rounding of the

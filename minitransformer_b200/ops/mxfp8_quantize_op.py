@@ -74,6 +74,14 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
         q_t, s_t_swz, _, pad = kernels.grouped_transpose_quantize_mxfp8(_as_2d_bf16(t), m_splits)
         return q_t, s_t_swz, pad
 
+    def grouped_quantize_with_transpose(self, t: torch.Tensor, qparams, m_splits):
+        """quantize(t) and grouped_transpose_quantize(t, m_splits) from one read of t:
+        returns (QuantizeResult of the row-wise copy, (q_t, s_t_swz, padded offsets))."""
+        assert qparams.quant_tile_shape in (None, (1, 32)), "MXFP8 uses 1x32 tiles"
+        r, t_copy = kernels.grouped_quantize_mxfp8(_as_2d_bf16(t), m_splits)
+        r.scale._mt_swz = r.scale_swz
+        return Q.QuantizeResult(r.data.view(mxfp8_output_t), r.scale, None, None, None, None, r.scale_swz, None), t_copy
+
     def grouped_gemm_1d1d(self, a, b, out_dtype=torch.float32, single_output: bool = True, out=None,
                           accumulate: bool = False):
         """a = grouped_transpose_quantize(dy), b = grouped_transpose_quantize(x) ->

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from conftest import bf16_bits_to_f32
-from helpers import from_bits, mismatch, np_u8, seeded_bf16, unswizzle_scales_ref
+from helpers import from_bits, mismatch, np_u8, padded_chunks, seeded_bf16, unswizzle_scales_ref
 from minitransformer_b200 import kernels as K
 from minitransformer_b200.module import config
 from minitransformer_b200.module.group_linear import GroupedLinear
@@ -122,6 +122,25 @@ def test_grouped_transpose_quantize_matches_oracle():
         assert not q_t[:, p0 + m:p1].any()   # zero padding
         off += m
     assert mismatch(unswizzle_scales_ref(np_u8(s_swz), Kd, pad[-1] // 32), s_lin) == 0
+
+
+@pytest.mark.parametrize("m_splits,cols", [([130, 0, 64, 1, 257, 60], 256), ([5, 7, 9, 11], 160), ([0, 384, 0], 96),
+                                          ([128, 128, 128], 128)])
+def test_grouped_quantize_with_transpose_equals_the_two_separate_passes(m_splits, cols):
+    """The single-read kernel must write exactly the bytes of the row-wise quantize plus those of
+    the grouped transposed quantize (checked against the oracle by the test above)."""
+    R = sum(m_splits)
+    t, _ = seeded_bf16((R, cols), 11)
+    xt = t.cuda()
+    row, (q_t, s_t_swz, pad) = K.grouped_quantize_mxfp8(xt, m_splits)
+    ref = K.quantize_mxfp8(xt, return_transpose=False)
+    ref_t, ref_s_t_swz, _, ref_pad = K.grouped_transpose_quantize_mxfp8(xt, m_splits)
+    assert list(pad) == list(ref_pad)
+    assert torch.equal(row.data, ref.data) and torch.equal(row.scale, ref.scale)
+    kb = padded_chunks(cols // 32) * 4   # including the zero-filled padding blocks of the valid rows
+    assert mismatch(unswizzle_scales_ref(np_u8(row.scale_swz), R, kb), unswizzle_scales_ref(np_u8(ref.scale_swz), R, kb)) == 0
+    assert torch.equal(q_t, ref_t) and torch.equal(s_t_swz, ref_s_t_swz)
+    assert K.read_device_status() == 0
 
 
 @pytest.mark.parametrize("m_splits", [[128, 128, 128], [130, 0, 64, 1, 257, 60], [0, 0, 300], [5, 7, 9, 11]])
