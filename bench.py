@@ -354,12 +354,20 @@ def run_gpu_arm(args):
             lin.weight.copy_(w)
         lin.weight.main_grad = torch.zeros((N_out, K_in), dtype=torch.float32, device=dev)
 
+        copy_stream = torch.cuda.Stream(device=dev)
+
         def e2e_step():
+            # the gradient's host->device copy runs on its own stream under the forward pass
+            main = torch.cuda.current_stream(dev)
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                dyd = dy_h.to(dev, non_blocking=True)
             xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
-            dyd = dy_h.to(dev, non_blocking=True)
             y = lin(xd, is_first_microbatch=True)
+            main.wait_stream(copy_stream)
+            dyd.record_stream(main)
             y.backward(dyd)
-            chk = torch.stack([y.float().sum(), xd.grad.float().sum(), lin.weight.main_grad.sum()])
+            chk = torch.stack([y.sum(dtype=torch.float32), xd.grad.sum(dtype=torch.float32), lin.weight.main_grad.sum()])
             return chk.cpu()
 
         h2d = x_h.numel() * 2 + dy_h.numel() * 2
@@ -396,7 +404,7 @@ def run_gpu_arm(args):
             xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
             dyd = dy_h.to(dev, non_blocking=True)
             y = mlp(xd, dyd)
-            chk = torch.stack([y.float().sum(), xd.grad.float().sum()])
+            chk = torch.stack([y.sum(dtype=torch.float32), xd.grad.sum(dtype=torch.float32)])
             return chk.cpu()
 
         h2d = x_h.numel() * 2 + dy_h.numel() * 2

@@ -114,11 +114,13 @@ class _QuantizedLinear(torch.autograd.Function):
         bias = cast_if_needed(bias, activation_dtype)
 
         gather_required = parallel_mode == "column" and sequence_parallel
+        # the gather (when there is one, in its copy-free form) is left in flight while the weight
+        # is quantized below, and awaited just before the GEMM
         qres_x = _QuantizedLinear.quantize_optionally_allgather(
             op, x, qlinear_params.x_params, transpose_required=is_grad_enabled,
             allgather_required=gather_required, allgather_quantize=qlinear_params.allgather_quantize,
             tp_group=tp_group, keep_transpose_local=qlinear_params.memory_saving and gather_required,
-            weight_shape=tuple(w.shape))
+            weight_shape=tuple(w.shape), async_gather=True)
 
         # weights are re-quantized on the first microbatch (or when the caller gives no hint)
         if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
@@ -127,6 +129,8 @@ class _QuantizedLinear(torch.autograd.Function):
         else:
             qres_w = weight_qresult_cache.to_qresult()
 
+        for h in getattr(qres_x, "_pending_handles", ()):
+            h.wait()
         y = op.qgemm(qres_x.data, qres_w.data, qlinear_params.mm_fprop, out_dtype, qres_x.scale, qres_w.scale,
                      bias, accumulate=False, global_amax_qx=qres_x.global_amax_row,
                      global_amax_qw=qres_w.global_amax_row, qparams_x=qlinear_params.x_params,
@@ -217,7 +221,8 @@ class _QuantizedLinear(torch.autograd.Function):
     # -- helpers ------------------------------------------------------------------------------
     @staticmethod
     def quantize_optionally_allgather(quantize_op, x, qparams, transpose_required, allgather_required,
-                                      allgather_quantize, tp_group, keep_transpose_local=False, weight_shape=None):
+                                      allgather_quantize, tp_group, keep_transpose_local=False, weight_shape=None,
+                                      async_gather=False):
         """Quantizes x, gathering it across the tensor-parallel group first (bf16) or after
         (quantized) when the layer is sequence-parallel.
 
@@ -244,7 +249,7 @@ class _QuantizedLinear(torch.autograd.Function):
         gather_t = transpose_required and not keep_transpose_local
         if (weight_shape is not None and min(weight_shape) > 128
                 and _QuantizedLinear._gemm_ready_gather_possible(r, rows, x.shape[1], world, transpose_required)):
-            return _QuantizedLinear._gather_gemm_ready(r, tp_group, gather_t, transpose_required)
+            return _QuantizedLinear._gather_gemm_ready(r, tp_group, gather_t, transpose_required, async_gather)
         parts = [r.data, r.scale[:rows]]
         if gather_t:
             parts += [r.data_t, r.scale_t[: x.shape[1]]]
@@ -272,18 +277,24 @@ class _QuantizedLinear(torch.autograd.Function):
         return True
 
     @staticmethod
-    def _gather_gemm_ready(r, tp_group, gather_t, transpose_required):
+    def _gather_gemm_ready(r, tp_group, gather_t, transpose_required, async_gather=False):
         """Quantized gather without any copy after the collectives: row-wise codes and
         GEMM-layout scales land where the fprop / dgrad GEMM reads them; the transposed copies
         stay per-rank K slabs ([world, features, bytes]) that the wgrad GEMM walks slab by slab.
         The scale fields of the result hold the GEMM layout (the row-major form is not
         materialized on this path)."""
-        data, scale, data_t, scale_t, _ = gather_gemm_ready(
-            r.data, r.scale_swz, tp_group, r.data_t if gather_t else None, r.scale_t_swz if gather_t else None)
+        data, scale, data_t, scale_t, handles = gather_gemm_ready(
+            r.data, r.scale_swz, tp_group, r.data_t if gather_t else None, r.scale_t_swz if gather_t else None,
+            async_op=async_gather)
         if r.data.dtype != torch.uint8:
             data = data.view(r.data.dtype)
         scale._mt_swz = scale
         out = quantization.QuantizeResult(data, scale, None, None, r.global_amax_row, r.global_amax_col, scale, None)
+        if async_gather:
+            # the caller waits on these before the first use of any gathered tensor; the sources
+            # stay referenced until then
+            out._pending_handles = tuple(handles)
+            out._pending_sources = (r.data, r.scale_swz, r.data_t, r.scale_t_swz)
         if gather_t:
             if r.data_t.dtype != torch.uint8:
                 data_t = data_t.view(r.data_t.dtype)
