@@ -63,7 +63,9 @@ struct GemmArgs {
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
-  int debug_skip_store;          // tuning aid: the epilogue drains tensor memory but writes nothing
+  int debug_skip_store;          // timing experiments (MT_GEMM_DEBUG_SKIP_STORE, results are wrong when set):
+                                 // bit 0 the epilogue drains tensor memory but writes nothing, bit 1 scale
+                                 // factors are copied for the first K step only, bit 2 B tiles are not loaded
   int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
   // Pair kernel, operands split along K into slabs stored one after another (what an all-gather
   // of per-rank transposed shards produces): K step k of A lies in slab k / a_slab_steps, whose
@@ -722,15 +724,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.status, DS_EMPTY_WAIT)) { alive = false; break; }
-          if (leader) mbar_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
+          const bool skip_b = (a.debug_skip_store & 4) != 0;   // bit 2: timing experiment without B loads
+          if (leader) mbar_expect_tx(&full_bar[s], 2 * (Cfg::STAGE_BYTES - (skip_b ? Cfg::B_BYTES : 0)));
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
           // slab of each operand this K step falls in, and the step inside the slab
           const int sl_a = k / a.a_slab_steps, ka = k - sl_a * a.a_slab_steps;
           const int sl_b = k / a.b_slab_steps, kb = k - sl_b * a.b_slab_steps;
           tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, a_kx0 + ka * G_BLOCK_KB,
                            a_row + (int32_t)(sl_a * a.a_slab_rows));
-          tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, b_kx0 + kb * G_BLOCK_KB,
-                           b_row + (int32_t)(sl_b * a.b_slab_rows));
+          if (!skip_b)
+            tma_load_2d_pair(smem + Cfg::OFF_B + s * Cfg::B_BYTES, &map_b, bar, b_kx0 + kb * G_BLOCK_KB,
+                             b_row + (int32_t)(sl_b * a.b_slab_rows));
           tma_load_2d_pair(smem + Cfg::OFF_SFA + s * Cfg::SFA_BYTES, &map_sfa, bar, 0,
                            sfa_chunk0 + (int32_t)(sl_a * a.a_slab_chunks) + ka * CH);
 #pragma unroll
@@ -762,6 +766,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
           tc_fence_after();
+          if (!(a.debug_skip_store & 2) || k == 0) {   // bit 1: timing experiment without scale copies
 #pragma unroll
           for (int c = 0; c < CH; ++c)
             tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
@@ -771,6 +776,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
             for (int c = 0; c < CH; ++c)
               tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFB + 4 * (c * NSB + h),
                               umma_desc_sf(sfb_base + s * Cfg::SFB_BYTES + (h * CH + c) * 512));
+          }
           const uint64_t adesc = umma_desc_sw128(a_base + s * Cfg::A_BYTES);
           const uint64_t bdesc = umma_desc_sw128(b_base + s * Cfg::B_BYTES);
 #pragma unroll
@@ -820,7 +826,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-      if (a.debug_skip_store) continue;
+      if (a.debug_skip_store & 1) continue;
       // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
       // so a block that straddles a group boundary takes the direct, row-masked path (as do
       // unaligned outputs and bf16 accumulation).

@@ -1,7 +1,7 @@
 """Small, self-contained kernel workloads for `ncu` captures (one kernel family each, a few
 launches, a few hundred MB on the device):
 
-    python -m minitransformer_b200.profile_cases gemm        # NVFP4 pair GEMM 4096x7168x4096, 3 launches
+    python -m minitransformer_b200.profile_cases gemm        # NVFP4 pair GEMM 4096x9472x4096 (8 full waves), 3 launches
     python -m minitransformer_b200.profile_cases gemm_mxfp8  # MXFP8 pair GEMM, same shape
     python -m minitransformer_b200.profile_cases quant       # abs-max + NVFP4 cast/transpose (RHT) of 8192x14336
     python -m minitransformer_b200.profile_cases quant_mxfp8 # MXFP8 cast/transpose of 8192x14336
@@ -19,7 +19,7 @@ def main(what: str) -> None:
     dev = "cuda"
     torch.manual_seed(0)
     if what in ("gemm", "gemm_mxfp8"):
-        M, N, Kd = 4096, 7168, 4096
+        M, N, Kd = 4096, 9472, 4096   # 16 x 37 pair tiles = 8 x 74: no partial last wave
         x = torch.randn(M, Kd, device=dev).to(torch.bfloat16)
         w = (torch.randn(N, Kd, device=dev) * 0.02).to(torch.bfloat16)
         if what == "gemm":
