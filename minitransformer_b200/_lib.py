@@ -7,7 +7,8 @@ import os
 import re
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmt_b200.so")
+# MT_B200_LIB points at another build of the same library (A/B timing of kernel variants)
+LIB_PATH = os.environ.get("MT_B200_LIB") or os.path.join(_HERE, "libmt_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "mt_b200.h")
 
 MT_BF16, MT_F32 = 0, 1

@@ -18,8 +18,7 @@ struct __align__(128) Nvfp4Smem {
   uint8_t out_t[QT_COLS][QT_ROWS / 2];   // 8 KiB, transposed codes (8-byte slots XOR-swizzled)
   uint8_t s_lin[QT_ROWS][8];             // row-wise scales, row-major
   uint8_t s_swz[2][512];                 // row-wise scales, chunk layout
-  uint8_t st_lin[QT_COLS][8];            // column-wise scales, row-major ([feature][token block])
-  uint8_t st_swz[2][512];
+  uint8_t st_blk[8][QT_COLS];            // column-wise scales as produced: [token block][feature]
   float blk_amax[8][8];                  // 16x16 block abs-max (2-D mode)
   float lut_row[128];                    // element factor per scale byte, row-wise copy
   float lut_col[128];                    // same for the transposed copy (its own per-tensor scale)
@@ -189,6 +188,7 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
 
   // ---- column pass: lane <-> 4 adjacent columns, warp <-> 16 rows ----
   if (kTranspose) {
+    uint32_t sb_word = 0;  // scale bytes of this lane's 4 columns (block = this warp's 16 rows)
     uint32_t wp[2][16];   // wp[p][j]: row j of column pair p (columns 4*lane + 2p, + 2p + 1)
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -221,11 +221,11 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
       const int slot = warp ^ (lane & 7);
       *reinterpret_cast<uint2*>(&sm.out_t[col][slot * 8]) = c_lo;
       *reinterpret_cast<uint2*>(&sm.out_t[col + 1][slot * 8]) = c_hi;
-      sm.st_lin[col][warp] = static_cast<uint8_t>(sb_lo);
-      sm.st_lin[col + 1][warp] = static_cast<uint8_t>(sb_hi);
-      sm.st_swz[warp >> 2][sf_chunk_offset(col, warp)] = static_cast<uint8_t>(sb_lo);
-      sm.st_swz[warp >> 2][sf_chunk_offset(col + 1, warp)] = static_cast<uint8_t>(sb_hi);
+      sb_word |= ((sb_lo & 0xFFu) | ((sb_hi & 0xFFu) << 8)) << (16 * p);
     }
+    // one conflict-free 4-byte store per lane; the row-major and GEMM layouts are assembled
+    // from this array when the tile is written out
+    *reinterpret_cast<uint32_t*>(&sm.st_blk[warp][lane * 4]) = sb_word;
   }
   __syncthreads();
 
@@ -274,14 +274,40 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
       }
     }
     if (tid < QT_COLS) {
+      // feature tid: its 8 token-block scales, gathered from the 8 rows of the staging array
       const int64_t gk = k0 + tid;
       const int64_t mb0 = m0 >> 4;
       const int nvalid = (int)min((int64_t)8, ((a.rows + 15) >> 4) - mb0);
-      if (gk < a.cols_s) store_bytes(a.s_t + gk * a.s_t_stride + mb0, sm.st_lin[tid], nvalid);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        lo |= static_cast<uint32_t>(sm.st_blk[w][tid]) << (8 * w);
+        hi |= static_cast<uint32_t>(sm.st_blk[w + 4][tid]) << (8 * w);
+      }
+      if (gk < a.cols_s && nvalid > 0) {
+        uint8_t* dst = a.s_t + gk * a.s_t_stride + mb0;
+        if (nvalid == 8 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+        } else {
+          for (int i = 0; i < nvalid; ++i) dst[i] = static_cast<uint8_t>((i < 4 ? lo >> (8 * i) : hi >> (8 * (i - 4))) & 0xFFu);
+        }
+      }
     }
     if (a.s_t_swz != nullptr) {
       uint8_t* base = a.s_t_swz + ((k0 >> 7) * a.kc_col + (m0 >> 6)) * 512;
-      if (tid < 64) *reinterpret_cast<uint4*>(base + tid * 16) = *reinterpret_cast<const uint4*>(&sm.st_swz[0][0] + tid * 16);
+      if (tid >= 128 && tid < 192) {
+        // 16-byte cell (chunk c, lane row r5): byte q * 4 + kb = scale of feature q * 32 + r5, block 4c + kb
+        const int c = (tid - 128) >> 5, r5 = tid & 31;
+        uint32_t cell[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t v = 0;
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) v |= static_cast<uint32_t>(sm.st_blk[c * 4 + kb][q * 32 + r5]) << (8 * kb);
+          cell[q] = v;
+        }
+        *reinterpret_cast<uint4*>(base + c * 512 + r5 * 16) = make_uint4(cell[0], cell[1], cell[2], cell[3]);
+      }
       if (m0 + QT_ROWS >= a.rows) {
         const int64_t extra = a.kc_col - ((m0 >> 6) + 2);
         for (int64_t i = tid; i < extra * 32; i += Q_THREADS)
