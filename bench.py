@@ -348,6 +348,33 @@ def run_gpu_arm(args):
                                 out=dw, global_amax_qx=qg.global_amax_col, global_amax_qw=qx.global_amax_col))
             return y, dx
 
+        def variant_step(p_, qw_cached=None):
+            """The same three GEMMs with another recipe, or with the weight's quantized copies kept
+            from an earlier microbatch (the module's weight_qresult_cache)."""
+            o_ = p_.quantize_op
+            qx = o_.quantize(x, p_.x_params, return_transpose=True)
+            qw = qw_cached if qw_cached is not None else o_.quantize(w, p_.w_params, return_transpose=True)
+            o_.qgemm(qx.data, qw.data, p_.mm_fprop, torch.bfloat16, qx.scale, qw.scale,
+                     global_amax_qx=qx.global_amax_row, global_amax_qw=qw.global_amax_row)
+            qg = o_.quantize(dy, p_.g_params, return_transpose=True)
+            o_.qgemm(qg.data, qw.data_t, p_.mm_dgrad, torch.bfloat16, qg.scale, qw.scale_t,
+                     global_amax_qx=qg.global_amax_row, global_amax_qw=qw.global_amax_col)
+            o_.qgemm(qg.data_t, qx.data_t, p_.mm_wgrad, torch.float32, qg.scale_t, qx.scale_t, out=dw,
+                     global_amax_qx=qg.global_amax_col, global_amax_qw=qx.global_amax_col)
+
+        def measure_variants():
+            out = {}
+            qw_keep = op.quantize(w, params.w_params, return_transpose=True)
+            ms = _timed_loop(torch, lambda: variant_step(params, qw_keep), 20, 3)
+            out["steady_microbatch_weights_cached"] = {"value": flops_step / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms}
+            p_norht = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT)
+            ms = _timed_loop(torch, lambda: variant_step(p_norht), 20, 3)
+            out["without_rht"] = {"value": flops_step / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms}
+            p_mx = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+            ms = _timed_loop(torch, lambda: variant_step(p_mx), 20, 3)
+            out["mxfp8_same_shape"] = {"value": flops_step / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms}
+            return out
+
         lin = Linear(K_in, N_out, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
                      fuse_wgrad_accumulation=True)
         with torch.no_grad():
@@ -493,6 +520,7 @@ def run_gpu_arm(args):
                 "achieved_counting_one_read": elts * 3.125 / (q_avg * 1e-3) / 1e9,
                 "peak_source": f"{peaks['source']} copy bandwidth"}
             line["tp_workload_on_1_gpu"] = _tp_workload_single_gpu(torch, Linear, params, dev, kernels)
+            line["variants"] = measure_variants()
             line["other_configs"] = _other_configs_single_gpu(torch, dev)
             tf, dt = cpu_run(4, 1)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",

@@ -41,6 +41,19 @@ def test_invalid_arguments_are_rejected_with_a_message():
     assert rc == -1 and b"dtype" in lib.mt_last_error_string()
     with pytest.raises(_lib.MtError):
         _lib.call("mt_swizzle_scales", None, 1, 1, 1, None, None)
+    # K-slab operands: every slab must hold whole 128-byte K steps, and the shapes must be ones
+    # the CTA-pair kernel takes
+    rc = lib.mt_gemm_nvfp4_kslab(p, p, p, 3, p, p, p, 1, 512, 512, 1024, p, 0, 512, None, 0, 0, None)
+    assert rc == -1 and b"slab" in lib.mt_last_error_string()
+    rc = lib.mt_gemm_mxfp8_kslab(p, p, 2, p, p, 1, 128, 512, 1024, p, 0, 512, None, 0, 0, None)
+    assert rc == -1 and b"M > 128" in lib.mt_last_error_string()
+    rc = lib.mt_gemm_mxfp8_kslab(p, p, 0, p, p, 1, 512, 512, 1024, p, 0, 512, None, 0, 0, None)
+    assert rc == -1 and b"positive" in lib.mt_last_error_string()
+    assert lib.mt_set_sm_margin(-1) == -1 and b"SM count" in lib.mt_last_error_string()
+    assert lib.mt_set_sm_margin(16) == 0 and lib.mt_set_sm_margin(0) == 0
+    off = (ctypes.c_int64 * 3)(0, 5, 9)
+    rc = lib.mt_grouped_quantize_mxfp8(p, 9, 64, off, 2, None, None, 2, None, p, None, 4, p, p, 4096, None)
+    assert rc == -1 and b"null q" in lib.mt_last_error_string()
 
 
 def test_front_end_refuses_cpu_tensors():
