@@ -171,6 +171,45 @@ def test_grouped_linear_mxfp8_matches_oracle(m_splits):
     assert K.read_device_status() == 0
 
 
+def test_grouped_linear_main_grad_accumulation_in_place():
+    """Megatron main_grad protocol for experts: with the main_grad buffers in one block the wgrad
+    GEMM writes (first microbatch) or accumulates (later ones) in place; with separate buffers it
+    goes through per-expert copies. Both must hold the same fp32 values."""
+    m_splits = [130, 0, 64, 1, 257, 60]
+    G, Kd, N = len(m_splits), 256, 384
+    R = sum(m_splits)
+    tx, _ = seeded_bf16((R, Kd), 41)
+    tdy, _ = seeded_bf16((R, N), 42, 1e-3)
+    params = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    kw = dict(bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params)
+    plain = GroupedLinear(G, Kd, N, **kw)
+    layers = {"block": GroupedLinear(G, Kd, N, fuse_wgrad_accumulation=True, **kw),
+              "separate": GroupedLinear(G, Kd, N, fuse_wgrad_accumulation=True, **kw)}
+    block = torch.full((G, N, Kd), 7.0, dtype=torch.float32, device="cuda")   # stale contents must be overwritten
+    for name, gl in layers.items():
+        with torch.no_grad():
+            for g in range(G):
+                getattr(gl, f"weight{g}").copy_(getattr(plain, f"weight{g}"))
+        for g in range(G):
+            getattr(gl, f"weight{g}").main_grad = block[g] if name == "block" else \
+                torch.full((N, Kd), 7.0, dtype=torch.float32, device="cuda")
+    xd = tx.cuda().requires_grad_(True)
+    plain(xd, m_splits).backward(tdy.cuda())
+    for first in (True, False):
+        for gl in layers.values():
+            gl(tx.cuda().requires_grad_(True), m_splits, is_first_microbatch=first).backward(tdy.cuda())
+    for g in range(G):
+        a = getattr(layers["block"], f"weight{g}").main_grad
+        b = getattr(layers["separate"], f"weight{g}").main_grad
+        assert torch.equal(a, b), g
+        want = 2.0 * getattr(plain, f"weight{g}").grad.float().cpu().numpy()
+        if m_splits[g] == 0:
+            assert float(a.abs().max()) == 0.0
+        else:
+            assert _relf(a, want) <= 5e-3, g     # the plain layer's gradient is rounded to bf16
+    assert K.read_device_status() == 0
+
+
 def test_grouped_linear_full_size_spot_checks():
     """Configuration-3 scale (128 experts, 131072 rows, seeded Zipf(1.1) group sizes with empty
     groups, hidden 2048 -> 768): expert slices of the grouped output against the dense kernel
