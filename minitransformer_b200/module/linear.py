@@ -131,10 +131,16 @@ class _QuantizedLinear(torch.autograd.Function):
 
         for h in getattr(qres_x, "_pending_handles", ()):
             h.wait()
-        y = op.qgemm(qres_x.data, qres_w.data, qlinear_params.mm_fprop, out_dtype, qres_x.scale, qres_w.scale,
-                     bias, accumulate=False, global_amax_qx=qres_x.global_amax_row,
-                     global_amax_qw=qres_w.global_amax_row, qparams_x=qlinear_params.x_params,
-                     qparams_w=qlinear_params.w_params)
+        x_t_handles = getattr(qres_x, "_pending_handles_t", ())
+        # the gather of x^T (needed by wgrad only) may still be running: leave it SMs
+        with _sm_margin(op, _overlap_sm_margin() if x_t_handles else 0):
+            y = op.qgemm(qres_x.data, qres_w.data, qlinear_params.mm_fprop, out_dtype, qres_x.scale, qres_w.scale,
+                         bias, accumulate=False, global_amax_qx=qres_x.global_amax_row,
+                         global_amax_qw=qres_w.global_amax_row, qparams_x=qlinear_params.x_params,
+                         qparams_w=qlinear_params.w_params)
+        if not is_grad_enabled:
+            for h in x_t_handles:
+                h.wait()
 
         if is_grad_enabled:
             ctx.use_bias = bias is not None
@@ -147,6 +153,8 @@ class _QuantizedLinear(torch.autograd.Function):
             ctx.fuse_wgrad_accumulation = fuse_wgrad_accumulation
             ctx.activation_dtype = activation_dtype
             ctx.x_t_is_local_shard = bool(getattr(qres_x, "_t_is_local_shard", False))
+            ctx.x_t_handles = x_t_handles          # awaited in backward, before wgrad reads x^T
+            ctx.x_t_sources = getattr(qres_x, "_pending_sources", None)
             # transposed copies only; their GEMM-layout scales travel as plain attributes
             ctx.sx_t_swz, ctx.sw_t_swz = qres_x.scale_t_swz, qres_w.scale_t_swz
             ctx.save_for_backward(qres_x.data_t, qres_x.scale_t, qres_x.global_amax_col,
@@ -173,7 +181,11 @@ class _QuantizedLinear(torch.autograd.Function):
         gather_required = ctx.parallel_mode == "row" and ctx.sequence_parallel
         qres_dy = _QuantizedLinear.quantize_optionally_allgather(
             op, dy, p.g_params, transpose_required=True, allgather_required=gather_required,
-            allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group, weight_shape=tuple(w.shape))
+            allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group, weight_shape=tuple(w.shape),
+            async_gather=True)
+        for h in getattr(qres_dy, "_pending_handles", ()):
+            h.wait()
+        dy_t_handles = getattr(qres_dy, "_pending_handles_t", ())
 
         # memory-saving mode kept only this rank's token shard of x^T: gather it back while
         # the dgrad GEMM runs
@@ -181,9 +193,13 @@ class _QuantizedLinear(torch.autograd.Function):
         if ctx.x_t_is_local_shard:
             pending_x_t = _QuantizedLinear._start_gather_transposed(qx_t, sx_t, ctx.tp_group)
 
-        dgrad = op.qgemm(qres_dy.data, qw_t, p.mm_dgrad, out_dtype_dgrad, qres_dy.scale, sw_t, None, None,
-                         accumulate=False, global_amax_qx=qres_dy.global_amax_row, global_amax_qw=amax_w_col,
-                         qparams_x=p.g_params, qparams_w=p.w_params)
+        # a gather of dy^T or of x^T (memory-saving mode) may be in flight: leave it SMs
+        with _sm_margin(op, _overlap_sm_margin() if (dy_t_handles or pending_x_t is not None) else 0):
+            dgrad = op.qgemm(qres_dy.data, qw_t, p.mm_dgrad, out_dtype_dgrad, qres_dy.scale, sw_t, None, None,
+                             accumulate=False, global_amax_qx=qres_dy.global_amax_row, global_amax_qw=amax_w_col,
+                             qparams_x=p.g_params, qparams_w=p.w_params)
+        for h in tuple(dy_t_handles) + tuple(getattr(ctx, "x_t_handles", ())):
+            h.wait()
 
         if pending_x_t is not None:
             qx_t, sx_t = _QuantizedLinear._finish_gather_transposed(pending_x_t, ctx.tp_group)
@@ -283,17 +299,25 @@ class _QuantizedLinear(torch.autograd.Function):
         stay per-rank K slabs ([world, features, bytes]) that the wgrad GEMM walks slab by slab.
         The scale fields of the result hold the GEMM layout (the row-major form is not
         materialized on this path)."""
-        data, scale, data_t, scale_t, handles = gather_gemm_ready(
-            r.data, r.scale_swz, tp_group, r.data_t if gather_t else None, r.scale_t_swz if gather_t else None,
-            async_op=async_gather)
+        handles_t = ()
+        if async_gather and gather_t:
+            # two collectives: the row-wise copy is needed by the next GEMM (fprop / dgrad), the
+            # transposed one only by wgrad, so it may stay in flight under that GEMM
+            data, scale, _, _, handles = gather_gemm_ready(r.data, r.scale_swz, tp_group, async_op=True)
+            data_t, scale_t, handles_t = gather_transposed_as_k_slabs(r.data_t, r.scale_t_swz, tp_group, async_op=True)
+        else:
+            data, scale, data_t, scale_t, handles = gather_gemm_ready(
+                r.data, r.scale_swz, tp_group, r.data_t if gather_t else None, r.scale_t_swz if gather_t else None,
+                async_op=async_gather)
         if r.data.dtype != torch.uint8:
             data = data.view(r.data.dtype)
         scale._mt_swz = scale
         out = quantization.QuantizeResult(data, scale, None, None, r.global_amax_row, r.global_amax_col, scale, None)
         if async_gather:
-            # the caller waits on these before the first use of any gathered tensor; the sources
+            # the caller waits on these before the first use of the gathered tensors; the sources
             # stay referenced until then
             out._pending_handles = tuple(handles)
+            out._pending_handles_t = tuple(handles_t)
             out._pending_sources = (r.data, r.scale_swz, r.data_t, r.scale_t_swz)
         if gather_t:
             if r.data_t.dtype != torch.uint8:
