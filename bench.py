@@ -38,6 +38,7 @@ GEMM_DRAM_BYTES_PER_LAUNCH = 235.0e6
 C3 = dict(experts=128, rows=131072, hidden=2048, ffn=768)
 C4 = dict(tokens=8192, hidden=8192, ffn=28672)
 CPU_SAMPLE = dict(tokens=512, in_features=4096, out_features=3584)
+CPU_SAMPLE_MLP = dict(tokens=512, hidden=2048, ffn=3584)
 
 
 def _peaks():
@@ -52,40 +53,61 @@ def _peaks():
 # ---------------------------------------------------------------------------------------------
 # CPU arm: numpy restatement of the reference emulation on a bounded sample
 # ---------------------------------------------------------------------------------------------
-def _cpu_step_inputs(seed=0):
+def _cpu_layers(n_gpus):
+    """(tokens, in, out) of the layers one CPU sample step runs: a slice of the headline Linear
+    at N = 1, a slice of the fc1 + fc2 pair of the tensor-parallel MLP otherwise."""
+    if n_gpus == 1:
+        s = CPU_SAMPLE
+        return [(s["tokens"], s["in_features"], s["out_features"])]
+    s = CPU_SAMPLE_MLP
+    return [(s["tokens"], s["hidden"], s["ffn"]), (s["tokens"], s["ffn"], s["hidden"])]
+
+
+def _cpu_step_inputs(n_gpus=1, seed=0):
     import numpy as np
     from oracle import formats as F
     rng = np.random.default_rng(seed)
-    s = CPU_SAMPLE
-    x = F.bf16_round(rng.standard_normal((s["tokens"], s["in_features"])).astype(np.float32))
-    w = F.bf16_round((rng.standard_normal((s["out_features"], s["in_features"])) * 0.02).astype(np.float32))
-    dy = F.bf16_round((rng.standard_normal((s["tokens"], s["out_features"])) * 1e-3).astype(np.float32))
-    return x, w, dy
+    layers = []
+    for t, k, n in _cpu_layers(n_gpus):
+        x = F.bf16_round(rng.standard_normal((t, k)).astype(np.float32))
+        w = F.bf16_round((rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        dy = F.bf16_round((rng.standard_normal((t, n)) * 1e-3).astype(np.float32))
+        layers.append((x, w, dy))
+    return layers
 
 
-def _cpu_sample_flops():
-    s = CPU_SAMPLE
-    return 3 * 2.0 * s["tokens"] * s["in_features"] * s["out_features"]
+def _cpu_sample_flops(n_gpus=1):
+    return sum(3 * 2.0 * t * k * n for t, k, n in _cpu_layers(n_gpus))
 
 
-def cpu_run(steps, warmup):
+def cpu_run(steps, warmup, n_gpus=1):
     """Times `steps` passes of the oracle's NVFP4 linear fwd+bwd on the sample; returns TFLOP/s."""
     from oracle import linear
-    x, w, dy = _cpu_step_inputs()
+    layers = _cpu_step_inputs(n_gpus)
+
+    def one():
+        for x, w, dy in layers:
+            linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
+
     for _ in range(warmup):
-        linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
+        one()
     t0 = time.perf_counter()
     for _ in range(steps):
-        linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
+        one()
     dt = (time.perf_counter() - t0) / max(1, steps)
-    return _cpu_sample_flops() / dt / 1e12, dt
+    return _cpu_sample_flops(n_gpus) / dt / 1e12, dt
 
 
-def _cpu_sample_text():
-    s = CPU_SAMPLE
-    return (f"NVFP4 linear fwd+bwd on tokens={s['tokens']} in={s['in_features']} out={s['out_features']} "
-            f"(1/64 of the GEMM flops of the 8192x4096x14336 workload), numpy restatement of the reference emulation, "
-            f"single-sgemm GEMM variant")
+def _cpu_sample_text(n_gpus=1):
+    if n_gpus == 1:
+        s = CPU_SAMPLE
+        return (f"NVFP4 linear fwd+bwd on tokens={s['tokens']} in={s['in_features']} out={s['out_features']} "
+                f"(1/64 of the GEMM flops of the 8192x4096x14336 workload), numpy restatement of the reference "
+                f"emulation, single-sgemm GEMM variant")
+    s = CPU_SAMPLE_MLP
+    return (f"NVFP4 fc1 + fc2 fwd+bwd on tokens={s['tokens']} hidden={s['hidden']} ffn={s['ffn']} (1/512 of the GEMM "
+            f"flops of the 8192x8192x28672 MLP; the two layers timed with independent seeded inputs), numpy "
+            f"restatement of the reference emulation, single-sgemm GEMM variant, no sharding (one host)")
 
 
 def run_reference_arm(args):
@@ -93,13 +115,13 @@ def run_reference_arm(args):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    tf, dt = cpu_run(args.steps, args.warmup)
+    tf, dt = cpu_run(args.steps, args.warmup, args.gpus)
     line = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
         "config": _workload_config(args.gpus),
-        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": _cpu_sample_text()},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": _cpu_sample_text(args.gpus)},
         "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
