@@ -257,9 +257,13 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
     fence_proxy_async_smem();
     __syncwarp();
     const int64_t c0 = colw + (int64_t)ch * cols_per;
-    if (lane == 0 && row0 < map_rows && c0 < a.N) {
-      if (f32 && a.accumulate) tma_reduce_add_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
-      else tma_store_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
+    if (lane == 0) {
+      if (row0 < map_rows && c0 < a.N) {
+        if (f32 && a.accumulate) tma_reduce_add_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
+        else tma_store_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
+      }
+      // one group per chunk, empty when the chunk lies outside the output: the "all but one"
+      // wait above counts groups, so the two halves must keep alternating group by group
       bulk_commit_group();
     }
   }

@@ -82,6 +82,11 @@ def _overlap_sm_margin() -> int:
         return 16
 
 
+def _env_flag(name: str, default: bool) -> bool:
+    v = os.environ.get(name)
+    return default if v is None else v not in ("0", "")
+
+
 def _sm_margin(op, sms: int):
     """Context in which the op's GEMMs leave `sms` SMs idle; ops without that control (the CPU
     stand-in of the tests) get a null context."""
@@ -300,7 +305,11 @@ class _QuantizedLinear(torch.autograd.Function):
         The scale fields of the result hold the GEMM layout (the row-major form is not
         materialized on this path)."""
         handles_t = ()
-        if async_gather and gather_t:
+        async_gather = async_gather and _env_flag("MT_TP_ASYNC_GATHER", True)
+        # Splitting pays on 2 ranks (3.69 against 3.78 ms per step of the benchmark MLP); on 8 ranks
+        # one collective awaited before the GEMM measured faster (1.85 against 2.16 ms), the extra
+        # launches costing more there than the overlap returns.
+        if async_gather and gather_t and _env_flag("MT_TP_SPLIT_GATHER", get_distributed_world_size(tp_group) <= 2):
             # two collectives: the row-wise copy is needed by the next GEMM (fprop / dgrad), the
             # transposed one only by wgrad, so it may stay in flight under that GEMM
             data, scale, _, _, handles = gather_gemm_ready(r.data, r.scale_swz, tp_group, async_op=True)
