@@ -76,3 +76,16 @@ def test_stacked_view_of_adjacent_parameters_is_copy_free():
     assert view.data_ptr() == block.data_ptr() and torch.equal(view, block)
     assert stacked_view([torch.randn(3, 5) for _ in range(3)]) is None
     assert stacked_view([block[0], block[2]]) is None
+    # the verdict is remembered per set of tensor objects: replacing one of them must be noticed
+    params[2] = torch.nn.Parameter(torch.randn(3, 5))
+    assert stacked_view(params) is None
+
+
+def test_group_offset_arrays_are_cached_per_split_list():
+    from minitransformer_b200 import kernels
+    a1, off1 = kernels._offsets_array([3, 0, 5])
+    a2, off2 = kernels._offsets_array((3, 0, 5))
+    assert a1 is a2 and off1 == [0, 3, 3, 8]
+    assert kernels.grouped_padded_offsets([3, 0, 5]) == [0, 128, 128, 256]
+    a3, off3 = kernels._offsets_array([3, 1, 5])
+    assert a3 is not a1 and off3 == [0, 3, 4, 9] and list(a3) == off3
