@@ -2,7 +2,15 @@
 // 16) or FP8 (E4M3, E8M0 scale per 32) operands, both K-major, fp32 accumulation in tensor
 // memory.
 //
-// Persistent, warp-specialised CTA (one per SM, 192 threads):
+// Two persistent, warp-specialised kernels share the tile descriptions and the epilogue helpers:
+//
+// gemm_blockscaled_pair_kernel (the one that runs whenever M > 128 and N > 128): a cluster of
+// two CTAs (cta_group::2, 320 threads each) per 256 x 256 output tile, described in the comment
+// above it. It serves the dense GEMM, the grouped GEMMs (rows grouped by expert; per-expert
+// contraction ranges for wgrad) and operands whose contraction dimension is split into slabs
+// (the raw result of an all-gather of per-rank transposed shards).
+//
+// gemm_blockscaled_kernel (small shapes): one CTA per SM, 192 threads:
 //   warp 0     TMA producer: per K step one 2-D tiled load each for the A and B tiles
 //              (128-byte rows, 128-byte swizzle) and 1-D bulk copies of the scale-factor
 //              chunks, all completing on the stage's "full" mbarrier;
@@ -14,8 +22,8 @@
 // Every wait on an mbarrier is bounded; on expiry the CTA raises a bit in the device status
 // word, abandons its remaining tiles, frees its tensor memory and exits.
 //
-// The grouped variants reuse the same kernel: a tile is described by (group, m block,
-// n block) and the operand / output bases are looked up per group.
+// Grouped modes: a tile is described by (group, row block, column block) and the operand /
+// output bases are looked up per group (TileCoord / PairTile).
 #include <algorithm>
 #include <vector>
 
