@@ -1,0 +1,31 @@
+"""The CPU arm of bench.py (`--impl reference`) runs without a GPU: one JSON line with the keys
+the benchmark contract names, timed on the numpy restatement of the reference emulation."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(*extra):
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0", *extra], capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    return out.stdout.strip().splitlines()
+
+
+def test_reference_arm_prints_one_contract_line():
+    lines = _run()
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 1 and d["steps"] == 1
+    assert d["metric"] == "nvfp4_linear_fwd_bwd_tflops" and d["unit"] == "TFLOP/s" and d["higher_is_better"] is True
+    assert d["value"] > 0 and d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["kind"] == "port"
+    assert d["e2e"] == {"value": d["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert d["config"]["tokens"] == 8192 and d["config"]["out_features"] == 14336
+
+
+def test_reference_arm_other_ranks_stay_silent(monkeypatch):
+    monkeypatch.setenv("RANK", "1")
+    assert _run("--gpus", "2") == []
