@@ -118,3 +118,55 @@ def test_column_then_row_parallel_linear_on_two_gloo_ranks(allgather_quantize, m
     result = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), allgather_quantize, memory_saving, result), nprocs=world, join=True)
     assert dict(result) == {0: True, 1: True}
+
+
+def _grouped_worker(rank, world, port, result):
+    """Tensor-parallel GroupedLinear on the non-quantized path: column-parallel experts followed
+    by row-parallel experts; the output of the row-parallel layer and the input gradient of the
+    column-parallel layer are all-reduced (there is no sequence parallelism for experts)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from minitransformer_b200.module.group_linear import GroupedLinear
+        torch.manual_seed(1)
+        G, H, Fd = 3, 128, 256
+        m_splits = [5, 0, 9]
+        R = sum(m_splits)
+        x_full = torch.randn(R, H)
+        w1 = [torch.randn(Fd, H) * 0.1 for _ in range(G)]
+        w2 = [torch.randn(H, Fd) * 0.1 for _ in range(G)]
+        dy = torch.randn(R, H)
+        p = config.QLinearParams(quantize=False)
+        kw = dict(bias=False, params_dtype=torch.float32, device="cpu", qlinear_params=p, tp_group=dist.group.WORLD,
+                  tp_size=world)
+        fc1 = GroupedLinear(G, H, Fd, parallel_mode="column", **kw)
+        fc2 = GroupedLinear(G, Fd, H, parallel_mode="row", **kw)
+        assert fc1.out_features == Fd // world and fc2.in_features == Fd // world
+        with torch.no_grad():
+            for g in range(G):
+                getattr(fc1, f"weight{g}").copy_(w1[g].chunk(world, 0)[rank])
+                getattr(fc2, f"weight{g}").copy_(w2[g].chunk(world, 1)[rank])
+        x = x_full.clone().requires_grad_(True)
+        y = fc2(fc1(x, m_splits), m_splits)
+        y.backward(dy)
+
+        xs, dys = torch.split(x_full, m_splits), torch.split(dy, m_splits)
+        hs = [a @ w.t() for a, w in zip(xs, w1)]
+        y_ref = torch.cat([h @ w.t() for h, w in zip(hs, w2)])
+        dhs = [d @ w for d, w in zip(dys, w2)]
+        dx_ref = torch.cat([d @ w for d, w in zip(dhs, w1)])
+        ok = torch.allclose(y, y_ref, atol=1e-4) and torch.allclose(x.grad, dx_ref, atol=1e-4)
+        for g in range(G):
+            ok &= torch.allclose(getattr(fc1, f"weight{g}").grad, (dhs[g].t() @ xs[g]).chunk(world, 0)[rank], atol=1e-4)
+            ok &= torch.allclose(getattr(fc2, f"weight{g}").grad, (dys[g].t() @ hs[g]).chunk(world, 1)[rank], atol=1e-4)
+        result[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_grouped_linear_on_two_gloo_ranks():
+    world = 2
+    mgr = mp.Manager()
+    result = mgr.dict()
+    mp.spawn(_grouped_worker, args=(world, _free_port(), result), nprocs=world, join=True)
+    assert dict(result) == {0: True, 1: True}
