@@ -384,6 +384,31 @@ def run_gpu_arm(args):
             o_.qgemm(qg.data_t, qx.data_t, p_.mm_wgrad, torch.float32, qg.scale_t, qx.scale_t, out=dw,
                      global_amax_qx=qg.global_amax_col, global_amax_qw=qx.global_amax_col)
 
+        def library_comparator():
+            """cuBLASLt's block-scaled NVFP4 GEMM (through torch._scaled_mm) on the same quantized
+            operands and shapes: a measured ceiling for the GEMM kernels, not a product path.
+            Its result lacks the per-tensor factor, which does not change the timing."""
+            try:
+                f4, f8 = torch.float4_e2m1fn_x2, torch.float8_e4m3fn
+                qx = op.quantize(x, params.x_params, return_transpose=True)
+                qw = op.quantize(w, params.w_params, return_transpose=True)
+                qg = op.quantize(dy, params.g_params, return_transpose=True)
+                cases = {"fprop": (qx.data, qx.scale_swz, qw.data, qw.scale_swz, torch.bfloat16),
+                         "dgrad": (qg.data, qg.scale_swz, qw.data_t, qw.scale_t_swz, torch.bfloat16),
+                         "wgrad": (qg.data_t, qg.scale_t_swz, qx.data_t, qx.scale_t_swz, torch.float32)}
+                out = {}
+                for name, (a_, sa_, b_, sb_, dt) in cases.items():
+                    fn = lambda: torch._scaled_mm(a_.view(f4), b_.view(f4).t(), scale_a=sa_.view(f8),
+                                                  scale_b=sb_.view(f8), out_dtype=dt)
+                    try:
+                        ms = _timed_loop(torch, fn, 10, 3)
+                        out[name] = {"tflops": gemm_flops_each / (ms * 1e-3) / 1e12, "ms": ms}
+                    except Exception as e:   # a shape / dtype combination the library does not take
+                        out[name] = {"unavailable": repr(e)[:120]}
+                return out
+            except Exception as e:
+                return {"unavailable": repr(e)[:200]}
+
         def measure_variants():
             """Variants and the headline recipe timed in alternating bursts of 5 steps, so that all
             of them see the same clocks (a long run settles at lower SM clocks under the power cap
@@ -552,6 +577,8 @@ def run_gpu_arm(args):
                 "achieved_counting_one_read": elts * 3.125 / (q_avg * 1e-3) / 1e9,
                 "peak_source": f"{peaks['source']} copy bandwidth"}
             line["tp_workload_on_1_gpu"] = _tp_workload_single_gpu(torch, Linear, params, dev, kernels)
+            line["roofline"]["library_comparator"] = {"what": "torch._scaled_mm (cuBLASLt NVFP4 block-scaled GEMM), same "
+                                                      "operands, per GEMM", **library_comparator()}
             line["variants"] = measure_variants()
             line["other_configs"] = _other_configs_single_gpu(torch, dev)
             tf, dt = cpu_run(4, 1)
