@@ -73,7 +73,8 @@ struct GemmArgs {
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
   int debug_skip_store;          // timing experiments (MT_GEMM_DEBUG_SKIP_STORE, results are wrong when set):
                                  // bit 0 the epilogue drains tensor memory but writes nothing, bit 1 scale
-                                 // factors are copied for the first K step only, bit 2 B tiles are not loaded
+                                 // factors are copied for the first K step only, bit 2 B tiles are not loaded, bit 3 the
+                                 // epilogue stages the output in shared memory but issues no TMA store
   int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
   // Pair kernel, operands split along K into slabs stored one after another (what an all-gather
   // of per-rank transposed shards produces): K step k of A lies in slab k / a_slab_steps, whose
@@ -266,7 +267,7 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
     __syncwarp();
     const int64_t c0 = colw + (int64_t)ch * cols_per;
     if (lane == 0) {
-      if (row0 < map_rows && c0 < a.N) {
+      if (row0 < map_rows && c0 < a.N && !(a.debug_skip_store & 8)) {   // bit 3: stage but do not store
         if (f32 && a.accumulate) tma_reduce_add_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
         else tma_store_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
       }
