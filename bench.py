@@ -80,14 +80,44 @@ def _cpu_sample_flops(n_gpus=1):
     return sum(3 * 2.0 * t * k * n for t, k, n in _cpu_layers(n_gpus))
 
 
-def cpu_run(steps, warmup, n_gpus=1):
-    """Times `steps` passes of the oracle's NVFP4 linear fwd+bwd on the sample; returns TFLOP/s."""
-    from oracle import linear
-    layers = _cpu_step_inputs(n_gpus)
+def _reference_emulation():
+    """The reference's own PyTorch emulation from oracle/_ref/ (placed there by oracle/make_ref.py),
+    or None when that folder has not been made."""
+    try:
+        from oracle import make_ref
+        return make_ref.load()
+    except Exception:
+        return None
 
-    def one():
-        for x, w, dy in layers:
-            linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
+
+def cpu_kind():
+    return "reference" if _reference_emulation() is not None else "port"
+
+
+def cpu_run(steps, warmup, n_gpus=1):
+    """Times `steps` passes of the NVFP4 linear fwd+bwd on the sample with all host cores:
+    the reference's _QuantizedLinear (forward + backward on CPU tensors) when oracle/_ref/
+    exists, otherwise the numpy restatement. Returns (TFLOP/s, seconds per sample step)."""
+    layers = _cpu_step_inputs(n_gpus)
+    ref = _reference_emulation()
+    if ref is not None:
+        import torch
+        torch.set_num_threads(os.cpu_count() or 1)
+        params = ref.get_params(ref.QuantizeRecipe.FP4_SUB_CHANNEL_REF)
+        tl = [tuple(torch.from_numpy(a).to(torch.bfloat16) for a in layer) for layer in layers]
+
+        def one():
+            for x, w, dy in tl:
+                xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+                y = ref.QuantizedLinear.apply(xr, None, wr, ref.QuantizeResultCache(), None, False, None, 1, None,
+                                              params, torch.bfloat16, True, None, False)
+                y.backward(dy)
+    else:
+        from oracle import linear
+
+        def one():
+            for x, w, dy in layers:
+                linear.nvfp4_linear_fwd_bwd(x, w, dy, with_rht=True, fused=True)
 
     for _ in range(warmup):
         one()
@@ -99,15 +129,17 @@ def cpu_run(steps, warmup, n_gpus=1):
 
 
 def _cpu_sample_text(n_gpus=1):
+    what = ("the reference's own _QuantizedLinear forward + backward (PyTorch emulation, recipe FP4_SUB_CHANNEL_REF) "
+            "on CPU tensors" if cpu_kind() == "reference" else
+            "numpy restatement of the reference emulation, single-sgemm GEMM variant")
     if n_gpus == 1:
         s = CPU_SAMPLE
         return (f"NVFP4 linear fwd+bwd on tokens={s['tokens']} in={s['in_features']} out={s['out_features']} "
-                f"(1/64 of the GEMM flops of the 8192x4096x14336 workload), numpy restatement of the reference "
-                f"emulation, single-sgemm GEMM variant")
+                f"(1/64 of the GEMM flops of the 8192x4096x14336 workload, scaled linearly), {what}")
     s = CPU_SAMPLE_MLP
     return (f"NVFP4 fc1 + fc2 fwd+bwd on tokens={s['tokens']} hidden={s['hidden']} ffn={s['ffn']} (1/512 of the GEMM "
-            f"flops of the 8192x8192x28672 MLP; the two layers timed with independent seeded inputs), numpy "
-            f"restatement of the reference emulation, single-sgemm GEMM variant, no sharding (one host)")
+            f"flops of the 8192x8192x28672 MLP; the two layers timed with independent seeded inputs), {what}, "
+            f"no sharding (one host)")
 
 
 def run_reference_arm(args):
@@ -121,7 +153,7 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
         "config": _workload_config(args.gpus),
-        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": "port", "sample": _cpu_sample_text(args.gpus)},
+        "cpu_baseline": {"value": tf, "unit": UNIT, "cores": cores, "kind": cpu_kind(), "sample": _cpu_sample_text(args.gpus)},
         "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -582,7 +614,7 @@ def run_gpu_arm(args):
             line["variants"] = measure_variants()
             line["other_configs"] = _other_configs_single_gpu(torch, dev)
             tf, dt = cpu_run(4, 1)
-            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+            line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": cpu_kind(),
                                     "sample": _cpu_sample_text(), "s_per_sample_step": dt}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -2,8 +2,8 @@
  * C ABI of the B200 (sm_100a) quantized-linear kernels.
  *
  * Every entry point takes raw device pointers, 64-bit sizes and a CUDA stream, launches
- * asynchronously on that stream, allocates nothing, never synchronises the device and
- * returns 0 on success or a negative mt_status on failure (mt_last_error_string() then
+ * asynchronously on that stream, allocates nothing, never synchronises the device
+ * (mt_read_device_status excepted) and returns 0 on success or a negative mt_status on failure (mt_last_error_string() then
  * describes it for the calling thread). Pointers must be 16-byte aligned unless stated.
  *
  * Reference interfaces these replace are cited per function as file:line inside
@@ -96,6 +96,22 @@ int mt_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
 int mt_swizzle_scales(const uint8_t* s, int64_t rows, int64_t k_blocks, int64_t s_stride,
                       uint8_t* s_swz, mt_stream_t stream);
 
+/* Optional per-call settings of the GEMM entry points (a null pointer = all defaults).
+ *   sm_margin  SMs this launch leaves idle. The GEMM kernels are persistent, one CTA per SM; a
+ *              collective launched beside such a grid gets no SM until GEMM CTAs retire. A
+ *              caller that overlaps a reduce-scatter with the wgrad GEMM gives that GEMM a
+ *              margin (the role of the sm_margin of the userbuffer overlap flags the
+ *              reference's Linear carries, miniTransformer/module/linear.py:649-671).
+ *   d_amax     optional device fp32 scalar: the kernel raises it (atomic max) to the largest
+ *              |value| it stores in d, after rounding to d's type. Zero it before the launch.
+ *              The next layer's NVFP4 quantize can take it as its per-tensor abs-max instead
+ *              of re-reading d (the QuantizeInputMetaBase.amax hook,
+ *              miniTransformer/ops/quantization.py:90-94). Not available with accumulate. */
+typedef struct mt_gemm_opts {
+  int sm_margin;
+  float* d_amax;
+} mt_gemm_opts;
+
 /* Block-scaled GEMM  D[M,N] = alpha * (A . B^T) (+ bias[N]) (+ D when accumulate), both
  * operands K-major, fp32 accumulation in tensor memory (tcgen05.mma, block_scale).
  *   NVFP4: a u8 [M, K/2], b u8 [N, K/2], K % 32 == 0, scales E4M3 per 16, swizzled layout;
@@ -110,20 +126,15 @@ int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a,
                   const uint8_t* b, const uint8_t* sb_swz, const float* amax_b,
                   int64_t M, int64_t N, int64_t K,
                   void* d, int d_dtype, int64_t ldd,
-                  const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
+                  const void* bias, int bias_dtype, int accumulate,
+                  const mt_gemm_opts* opts, mt_stream_t stream);
 
 int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz,
                   const uint8_t* b, const uint8_t* sb_swz,
                   int64_t M, int64_t N, int64_t K,
                   void* d, int d_dtype, int64_t ldd,
-                  const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
-
-/* Number of SMs every later GEMM launch of this process leaves idle (default 0). The GEMM
- * kernels are persistent, one CTA per SM; a collective launched beside such a grid gets no SM
- * until GEMM CTAs retire. A caller that overlaps a reduce-scatter with the wgrad GEMM sets a
- * margin around that GEMM and resets it afterwards (the role of the sm_margin argument
- * of the userbuffer overlap flags the reference's Linear carries, linear.py:649-671). */
-int mt_set_sm_margin(int sms);
+                  const void* bias, int bias_dtype, int accumulate,
+                  const mt_gemm_opts* opts, mt_stream_t stream);
 
 /* The same GEMMs for operands whose contraction dimension is split into slabs stored one
  * after another: a is a_slabs matrices [M, K / a_slabs] (bytes as above) back to back, and
@@ -138,50 +149,45 @@ int mt_set_sm_margin(int sms);
 int mt_gemm_nvfp4_kslab(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, int64_t a_slabs,
                         const uint8_t* b, const uint8_t* sb_swz, const float* amax_b, int64_t b_slabs,
                         int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
-                        const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
+                        const void* bias, int bias_dtype, int accumulate,
+                        const mt_gemm_opts* opts, mt_stream_t stream);
 
 int mt_gemm_mxfp8_kslab(const uint8_t* a, const uint8_t* sa_swz, int64_t a_slabs,
                         const uint8_t* b, const uint8_t* sb_swz, int64_t b_slabs,
                         int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
-                        const void* bias, int bias_dtype, int accumulate, mt_stream_t stream);
-
-/* Same contracts, computed by a plain CUDA-core kernel that follows the emulation's
- * summation structure (per-block fp32 dot, scaled, fp32 accumulate). Scales are given in
- * the row-major layout. It exists so the tensor-core kernels can be checked on the device at
- * sizes where a CPU check would take minutes; it is not a product path. */
-int mt_gemm_nvfp4_check(const uint8_t* a, const uint8_t* sa, int64_t sa_stride, const float* amax_a,
-                        const uint8_t* b, const uint8_t* sb, int64_t sb_stride, const float* amax_b,
-                        int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
-                        int accumulate, mt_stream_t stream);
-int mt_gemm_mxfp8_check(const uint8_t* a, const uint8_t* sa, int64_t sa_stride,
-                        const uint8_t* b, const uint8_t* sb, int64_t sb_stride,
-                        int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
-                        int accumulate, mt_stream_t stream);
+                        const void* bias, int bias_dtype, int accumulate,
+                        const mt_gemm_opts* opts, mt_stream_t stream);
 
 /* ---- Grouped (per-expert) MXFP8 path behind GroupedLinear ----
- * Rows of the activation matrix are split into G consecutive groups by the host array
- * m_offsets_host[G+1] (m_offsets_host[0] = 0, m_offsets_host[G] = rows; empty groups allowed);
- * group g multiplies with its own weight. Replaces the calls the reference's GroupedLinear
- * makes into modules that do not exist in its tree: grouped_qgemm
+ * Rows of the activation matrix are split into G consecutive groups by m_offsets[G+1], an array
+ * in DEVICE memory (m_offsets[0] = 0, m_offsets[G] = rows, non-decreasing; empty groups
+ * allowed); group g multiplies with its own weight. Replaces the calls the reference's
+ * GroupedLinear makes into modules that do not exist in its tree: grouped_qgemm
  * (miniTransformer/module/group_linear.py:108-119, 198-209), grouped_transpose_quantize
  * (:231-236) and cutlass_grouped_gemm_1d1d (:238-243).
- * `scratch` is caller-owned device memory of at least mt_grouped_scratch_bytes(rows, G)
- * bytes; the entry points copy small tile tables into it (the copy from pageable host
- * memory makes these calls synchronise with the stream). */
-int64_t mt_grouped_scratch_bytes(int64_t rows, int64_t groups);
+ *
+ * A plan is built once per distinct m_offsets by mt_grouped_plan_build (one small kernel, no
+ * host copy) into caller-owned device memory of mt_grouped_plan_bytes(rows, G) bytes and is
+ * then shared by every grouped call of the step (fc1 / fc2, forward and backward): it holds the
+ * offsets, the offsets after padding every group to 128 tokens and the tile tables. The
+ * grouped entry points read it on the device; none of them touches host memory or
+ * synchronises. Offsets that are not a valid partition of [0, rows) leave an empty plan (the
+ * grouped calls then compute nothing) and raise bit 32 of the device status word
+ * (mt_read_device_status). `padded_rows` below is the padded token total, which the caller
+ * knows from its split sizes: sum over groups of ceil(m_g / 128) * 128. */
+int64_t mt_grouped_plan_bytes(int64_t rows, int64_t groups);
+int mt_grouped_plan_build(const int64_t* m_offsets, int64_t groups, int64_t rows,
+                          void* plan, int64_t plan_bytes, mt_stream_t stream);
 
-/* Token offsets of the groups after padding every group to a multiple of 128 tokens.
- * Writes G+1 values to pad_offsets_out (may be null) and returns the padded total. */
-int64_t mt_grouped_padded_rows(const int64_t* m_offsets_host, int64_t G, int64_t* pad_offsets_out);
-
-/* Transposed MXFP8 quantization with per-group blocks: q_t[cols, Rp] holds x^T with group g's
- * tokens at columns pad_offset[g].., zero-padded to 128; 1x32 blocks start at each group's
- * first token, so no block mixes two groups. s_t (optional, row-major [cols, Rp/32], stride
- * s_t_stride) and s_t_swz (GEMM layout, mt_swizzled_scale_bytes(cols, Rp/32) bytes). */
+/* Transposed MXFP8 quantization with per-group blocks: q_t[cols, padded_rows] holds x^T with
+ * group g's tokens at columns pad_offset[g].., zero-padded to 128; 1x32 blocks start at each
+ * group's first token, so no block mixes two groups. s_t (optional, row-major
+ * [cols, padded_rows/32], stride s_t_stride) and s_t_swz (GEMM layout,
+ * mt_swizzled_scale_bytes(cols, padded_rows/32) bytes). */
 int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
-                                        const int64_t* m_offsets_host, int64_t G,
+                                        const void* plan, int64_t G, int64_t padded_rows,
                                         uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
-                                        void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+                                        mt_stream_t stream);
 
 /* The same transposed copy plus, from the same read of x, the plain row-wise copy that
  * mt_quantize_mxfp8 would produce: q [rows, cols], s (optional, row-major [rows, cols/32], stride
@@ -191,10 +197,10 @@ int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t col
  * operand (dy^T per group); the reference's GroupedLinear quantizes and transposes in separate
  * steps (miniTransformer/module/group_linear.py:87-108, 231-238). */
 int mt_grouped_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
-                              const int64_t* m_offsets_host, int64_t G,
+                              const void* plan, int64_t G, int64_t padded_rows,
                               uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
                               uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
-                              void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+                              mt_stream_t stream);
 
 /* D[rows of g, 0:N] = A[rows of g, 0:K] . B_g^T for every group g. A, D and sa_swz use the
  * plain (unpadded) row numbering. B is one matrix of b_rows rows of ldb bytes; group g uses
@@ -203,44 +209,44 @@ int mt_grouped_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
  *   dgrad:   B = transposed stacked weights [N, G*K] -> b_group_rows = 0, b_group_k = K
  * N and K must be multiples of 128. */
 int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
-                          int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G,
+                          int64_t b_rows, int64_t ldb, const void* plan, int64_t G, int64_t rows,
                           int64_t N, int64_t K, int64_t b_group_rows, int64_t b_group_k,
-                          void* d, int d_dtype, int64_t ldd,
-                          void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+                          void* d, int d_dtype, int64_t ldd, mt_stream_t stream);
 
-/* mt_grouped_gemm_mxfp8 without caller-provided scratch. No counterpart in the reference.
+/* mt_grouped_gemm_mxfp8 without a caller-provided plan buffer. No counterpart in the reference.
  *
- * Some callers have no way to hand over scratch memory: every free byte of the GPU already
- * belongs to someone else's allocator (a training framework's caching pool, an inference
- * server with a fixed memory plan), or they sit in a latency-critical loop where a
- * cudaMalloc / cudaFree would synchronise the whole device. For them the tile tables of the
- * grouped GEMM live in a fixed array inside the library image: about 82 KB of device memory
- * on every GPU that loads the library, held until the process exits. The call allocates
- * nothing, neither on the device nor through any library.
+ * Some callers have no way to hand over device memory for the plan: every free byte of the
+ * GPU already belongs to someone else's allocator (a training framework's caching pool, an
+ * inference server with a fixed memory plan), or they sit in a latency-critical loop where a
+ * cudaMalloc / cudaFree would synchronise the whole device. For them the plan lives in a fixed
+ * array inside the library image: about 0.3 MB of device memory on every GPU that loads the
+ * library, held until the process exits. The call takes the device offsets array directly,
+ * builds the plan into that array and runs the GEMM; it allocates nothing, neither on the
+ * device nor through any library.
  *
  * Limits: at most MT_STATIC_MAX_GROUPS groups and MT_STATIC_MAX_ROWS rows; larger problems
  * are rejected with MT_ERR_INVALID_ARG and a message naming the limit.
- * All calls on one GPU share the one array. Each call rewrites the part it uses, so nothing
- * needs clearing between calls, but two calls whose kernels can overlap on the GPU (different
- * streams) race on it: serialise them.
+ * All calls on one GPU share the one array. Each call rebuilds the plan before it uses it, so
+ * nothing needs clearing between calls, but two calls whose kernels can overlap on the GPU
+ * (different streams) race on it: serialise them.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
  * make that first call before starting any stream capture.
- * Arguments, results and tolerances are those of mt_grouped_gemm_mxfp8. */
+ * Other arguments, results and tolerances are those of mt_grouped_gemm_mxfp8. */
 #define MT_STATIC_MAX_GROUPS 1024
 #define MT_STATIC_MAX_ROWS 1048576
 int mt_grouped_gemm_mxfp8_static(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
-                                 int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G,
+                                 int64_t b_rows, int64_t ldb, const int64_t* m_offsets, int64_t G, int64_t rows,
                                  int64_t N, int64_t K, int64_t b_group_rows, int64_t b_group_k,
                                  void* d, int d_dtype, int64_t ldd, mt_stream_t stream);
 
 /* Per-group weight gradients: D_g[N_out, K_out] (+)= A_t[:, cols_g] . B_t[:, cols_g]^T with
- * cols_g = [pad_offsets_host[g], pad_offsets_host[g+1]) of the padded token axis (outputs of
- * mt_grouped_transpose_quantize_mxfp8 on dy and x). The G outputs are stored back to back;
- * an empty group yields zeros. */
+ * cols_g = [pad_offset[g], pad_offset[g+1]) of the padded token axis (outputs of
+ * mt_grouped_transpose_quantize_mxfp8 on dy and x with the same plan). The G outputs are
+ * stored back to back; an empty group yields zeros. */
 int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const uint8_t* b_t, const uint8_t* sb_t_swz,
-                           const int64_t* pad_offsets_host, int64_t G, int64_t N_out, int64_t K_out,
-                           void* d, int d_dtype, int accumulate,
-                           void* scratch, int64_t scratch_bytes, mt_stream_t stream);
+                           const void* plan, int64_t G, int64_t rows, int64_t padded_rows,
+                           int64_t N_out, int64_t K_out, void* d, int d_dtype, int accumulate,
+                           mt_stream_t stream);
 
 /* Reads and clears the device-side status word the kernels raise when a bounded wait
  * expires (0 = clean). Synchronises the given stream. */

@@ -7,15 +7,23 @@ import os
 import re
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# MT_B200_LIB points at another build of the same library (A/B timing of kernel variants)
-LIB_PATH = os.environ.get("MT_B200_LIB") or os.path.join(_HERE, "libmt_b200.so")
-HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "mt_b200.h")
+LIB_PATH = os.path.join(_HERE, "libmt_b200.so")
+INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
+HEADER_PATHS = (os.path.join(INCLUDE_DIR, "mt_b200.h"), os.path.join(INCLUDE_DIR, "mt_b200_test.h"))
 
 MT_BF16, MT_F32 = 0, 1
 MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16 = 1, 2, 4
 
 _c = ctypes
 _vp, _i64, _int = _c.c_void_p, _c.c_int64, _c.c_int
+
+
+class GemmOpts(ctypes.Structure):
+    """mt_gemm_opts of include/mt_b200.h."""
+    _fields_ = [("sm_margin", _int), ("d_amax", _vp)]
+
+
+_opts = _c.POINTER(GemmOpts)
 
 _SIGNATURES = {
     "mt_version": (_int, []),
@@ -25,24 +33,24 @@ _SIGNATURES = {
     "mt_quantize_nvfp4": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
     "mt_quantize_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
     "mt_swizzle_scales": (_int, [_vp, _i64, _i64, _i64, _vp, _vp]),
-    "mt_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
-    "mt_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
-    "mt_set_sm_margin": (_int, [_int]),
+    "mt_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _opts, _vp]),
+    "mt_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _opts, _vp]),
     "mt_gemm_nvfp4_kslab": (_int, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int,
-                                   _int, _vp]),
-    "mt_gemm_mxfp8_kslab": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _vp]),
+                                   _int, _opts, _vp]),
+    "mt_gemm_mxfp8_kslab": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int,
+                                   _opts, _vp]),
+    "mt_test_bounded_wait": (_int, [_i64, _vp]),
     "mt_gemm_nvfp4_check": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
     "mt_gemm_mxfp8_check": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _int, _i64, _int, _vp]),
-    "mt_grouped_scratch_bytes": (_i64, [_i64, _i64]),
-    "mt_grouped_padded_rows": (_i64, [_c.POINTER(_i64), _i64, _c.POINTER(_i64)]),
-    "mt_grouped_quantize_mxfp8": (_int, [_vp, _i64, _i64, _c.POINTER(_i64), _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp,
-                                         _vp, _i64, _vp]),
-    "mt_grouped_transpose_quantize_mxfp8": (_int, [_vp, _i64, _i64, _c.POINTER(_i64), _i64, _vp, _vp, _i64, _vp, _vp, _i64, _vp]),
-    "mt_grouped_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _c.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
-                                     _vp, _int, _i64, _vp, _i64, _vp]),
-    "mt_grouped_gemm_mxfp8_static": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _c.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
+    "mt_grouped_plan_bytes": (_i64, [_i64, _i64]),
+    "mt_grouped_plan_build": (_int, [_vp, _i64, _i64, _vp, _i64, _vp]),
+    "mt_grouped_quantize_mxfp8": (_int, [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "mt_grouped_transpose_quantize_mxfp8": (_int, [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
+    "mt_grouped_gemm_mxfp8": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                     _vp, _int, _i64, _vp]),
+    "mt_grouped_gemm_mxfp8_static": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                             _vp, _int, _i64, _vp]),
-    "mt_grouped_wgrad_mxfp8": (_int, [_vp, _vp, _vp, _vp, _c.POINTER(_i64), _i64, _i64, _i64, _vp, _int, _int, _vp, _i64, _vp]),
+    "mt_grouped_wgrad_mxfp8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _int, _int, _vp]),
     "mt_read_device_status": (_int, [_c.POINTER(_int), _vp]),
 }
 
@@ -53,11 +61,13 @@ class MtError(RuntimeError):
     """A C-ABI call returned a negative status."""
 
 
-def declared_symbols(header_path: str = HEADER_PATH):
-    """Names of every function the public header declares."""
-    text = open(header_path).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mt_[a-z0-9_]+)\s*\(", text)))
+def declared_symbols(header_paths=HEADER_PATHS):
+    """Names of every function the headers under include/ declare."""
+    names = set()
+    for path in header_paths:
+        text = re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
+        names.update(re.findall(r"\b(mt_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def load():

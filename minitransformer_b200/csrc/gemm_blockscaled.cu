@@ -25,8 +25,9 @@
 // Grouped modes: a tile is described by (group, row block, column block) and the operand /
 // output bases are looked up per group (TileCoord / PairTile).
 #include <algorithm>
-#include <vector>
+#include <climits>
 
+#include "grouped_plan.cuh"
 #include "mt_common.cuh"
 
 namespace mt {
@@ -58,6 +59,8 @@ struct GemmArgs {
   int* status;
   // tiling
   int tiles_m, tiles_n, num_tiles;
+  const int32_t* entries_dev;    // MODE_GROUPED_ROWS: device count of (row block, group) entries; the tile
+                                 // count is *entries_dev * tiles_n (num_tiles is only its upper bound)
   // grouping
   int mode;
   int num_groups;
@@ -71,10 +74,15 @@ struct GemmArgs {
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
-  int debug_skip_store;          // timing experiments (MT_GEMM_DEBUG_SKIP_STORE, results are wrong when set):
-                                 // bit 0 the epilogue drains tensor memory but writes nothing, bit 1 scale
-                                 // factors are copied for the first K step only, bit 2 B tiles are not loaded, bit 3 the
+  float* d_amax;                 // optional: atomic max of |stored value| (pair kernel, no accumulation)
+#ifdef MT_TIMING_KNOBS
+  int knobs;                     // builds with -DMT_TIMING_KNOBS only (results are wrong when set): bit 0 the
+                                 // epilogue drains tensor memory but writes nothing, bit 1 scale factors are
+                                 // copied for the first K step only, bit 2 B tiles are not loaded, bit 3 the
                                  // epilogue stages the output in shared memory but issues no TMA store
+#endif
+  int sm_margin;                 // host only: SMs the persistent grid leaves idle (room for a collective's
+                                 // kernel that should run beside the GEMM instead of behind it)
   int band;                      // pair kernel: tile rows per band of the tile order (0 = row index fastest over all rows)
   // Pair kernel, operands split along K into slabs stored one after another (what an all-gather
   // of per-rank transposed shards produces): K step k of A lies in slab k / a_slab_steps, whose
@@ -84,6 +92,16 @@ struct GemmArgs {
   int64_t a_slab_rows, b_slab_rows;
   int64_t a_slab_chunks, b_slab_chunks;
 };
+
+// Timing experiments exist only in builds with -DMT_TIMING_KNOBS (a separate library used for
+// A/B measurements); the shipped library reads no tuning variable from the environment.
+#ifdef MT_TIMING_KNOBS
+#define MT_KNOB(args, bit) (((args).knobs & (bit)) != 0)
+static int env_knob(const char* name, int dflt) { const char* e = getenv(name); return e ? atoi(e) : dflt; }
+#else
+#define MT_KNOB(args, bit) false
+static int env_knob(const char*, int dflt) { return dflt; }
+#endif
 
 template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
 struct GemmCfg {
@@ -144,10 +162,37 @@ __device__ __forceinline__ void issue_mma(uint32_t tmem_d, uint64_t adesc, uint6
   }
 }
 
+// Running abs-max of what a thread stores: bf16 outputs are tracked two per word with the packed
+// bf16 instruction (sign bits are garbage until amax_finish strips them), fp32 outputs as fp32.
+struct AmaxAcc {
+  uint32_t packed = 0;
+  float f = 0.0f;
+};
+__device__ __forceinline__ void amax_bf16x2(AmaxAcc& m, uint32_t w) {
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(m.packed) : "r"(m.packed), "r"(w));
+}
+__device__ __forceinline__ float amax_finish(const AmaxAcc& m) {
+  const uint32_t p = m.packed & 0x7FFF7FFFu;
+  return fmaxf(m.f, fmaxf(__uint_as_float(p << 16), __uint_as_float(p & 0xFFFF0000u)));
+}
+// Warp-wide maximum of the threads' abs-max values -> one atomic max on the fp32 scalar (values
+// are non-negative, so their bit patterns order like unsigned integers).
+__device__ __forceinline__ void amax_publish(float* d_amax, const AmaxAcc& m, int lane) {
+  const uint32_t bits = __reduce_max_sync(0xffffffffu, __float_as_uint(amax_finish(m)));
+  if (lane == 0 && bits != 0) atomicMax(reinterpret_cast<unsigned int*>(d_amax), bits);
+}
+
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 // One thread's 32 consecutive fp32 accumulators of one output row -> alpha / bias /
-// accumulate -> global memory (bf16 or fp32), vectorised when aligned and in range.
+// accumulate -> global memory (bf16 or fp32): whole 32-byte sectors per store when the row is
+// 32-byte aligned, 16-byte stores when 16-byte aligned, scalar stores at ragged edges.
 __device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_t (&r)[32], float alpha, bool has_k,
-                                                int64_t off, int64_t col0) {
+                                                int64_t off, int64_t col0, AmaxAcc& am) {
   float v[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = has_k ? __fmul_rn(alpha, __uint_as_float(r[i])) : 0.0f;
@@ -157,9 +202,20 @@ __device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_
       v[i] += (a.bias_dtype == MT_F32) ? static_cast<const float*>(a.bias)[col0 + i]
                                        : __bfloat162float(static_cast<const __nv_bfloat16*>(a.bias)[col0 + i]);
   }
+  const bool track = a.d_amax != nullptr;
   if (a.d_dtype == MT_F32) {
     float* dst = static_cast<float*>(a.d) + off;
-    if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    if (track)
+      for (int i = 0; i < nvalid; ++i) am.f = fmaxf(am.f, fabsf(v[i]));
+    if (nvalid == 32 && !a.accumulate && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(v[8 * i + j]);
+        st_global_v8(dst + 8 * i, w);
+      }
+    } else if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
       float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -173,11 +229,12 @@ __device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_
   } else {
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + off;
     if (nvalid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
+      const uint4* s4 = reinterpret_cast<const uint4*>(dst);
+      uint32_t ow[16];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         if (a.accumulate) {
-          uint4 p = d4[i];
+          uint4 p = s4[i];
           const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -185,18 +242,31 @@ __device__ __forceinline__ void store_row_chunk(const GemmArgs& a, const uint32_
             v[8 * i + 2 * j + 1] += __uint_as_float(pw[j] & 0xFFFF0000u);
           }
         }
-        uint32_t ow[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-          ow[j] = *reinterpret_cast<uint32_t*>(&h);
+          ow[4 * i + j] = *reinterpret_cast<uint32_t*>(&h);
+          if (track) amax_bf16x2(am, ow[4 * i + j]);
         }
-        d4[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
+      if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const uint32_t w[8] = {ow[8 * i], ow[8 * i + 1], ow[8 * i + 2], ow[8 * i + 3],
+                                 ow[8 * i + 4], ow[8 * i + 5], ow[8 * i + 6], ow[8 * i + 7]};
+          st_global_v8(dst + 16 * i, w);
+        }
+      } else {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d4[i] = make_uint4(ow[4 * i], ow[4 * i + 1], ow[4 * i + 2], ow[4 * i + 3]);
       }
     } else {
       for (int i = 0; i < nvalid; ++i) {
         float o = a.accumulate ? __bfloat162float(dst[i]) + v[i] : v[i];
-        dst[i] = __float2bfloat16_rn(o);
+        const __nv_bfloat16 h = __float2bfloat16_rn(o);
+        if (track) am.f = fmaxf(am.f, fabsf(__bfloat162float(h)));
+        dst[i] = h;
       }
     }
   }
@@ -217,7 +287,8 @@ __device__ __forceinline__ float bias_at(const GemmArgs& a, int64_t col) {
 __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUtensorMap* map_d,
                                                         const uint32_t (&acc)[4][32], int ncols, uint8_t* stage,
                                                         int lane, int64_t row0, int64_t map_rows, int64_t colw,
-                                                        float alpha, bool has_k) {
+                                                        float alpha, bool has_k, AmaxAcc& am) {
+  const bool track = a.d_amax != nullptr;
   const uint32_t swz = (lane >> 1) & 3;
   const bool f32 = a.d_dtype == MT_F32;
   const int cols_per = f32 ? 16 : 32;
@@ -244,6 +315,7 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
           }
           __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
           w[t] = *reinterpret_cast<uint32_t*>(&h);
+          if (track) amax_bf16x2(am, w[t]);
         }
         *reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
@@ -259,6 +331,7 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
             const int64_t gc = colw + col;
             if (gc < a.N) v[t] += bias_at(a, gc);
           }
+          if (track) am.f = fmaxf(am.f, fabsf(v[t]));
         }
         *reinterpret_cast<float4*>(buf + lane * 64 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
       }
@@ -267,7 +340,7 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
     __syncwarp();
     const int64_t c0 = colw + (int64_t)ch * cols_per;
     if (lane == 0) {
-      if (row0 < map_rows && c0 < a.N && !(a.debug_skip_store & 8)) {   // bit 3: stage but do not store
+      if (row0 < map_rows && c0 < a.N && !MT_KNOB(a, 8)) {
         if (f32 && a.accumulate) tma_reduce_add_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
         else tma_store_2d(map_d, buf, (int32_t)c0, (int32_t)row0);
       }
@@ -312,8 +385,8 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int tile) {
     t.d_row_hi = a.M;
     t.d_col0 = t.b_row0;
   } else if (a.mode == MODE_GROUPED_ROWS) {
-    // entries (row block, group) for every group that owns rows of the block; n-block major
-    const int nb = tile / a.tiles_m, e = tile - nb * a.tiles_m;
+    // entries (row block, group) for every group that owns rows of the block; column block fastest
+    const int e = tile / a.tiles_n, nb = tile - e * a.tiles_n;
     const int g = a.tile_group[e];
     t.a_row0 = (int64_t)a.tile_rb[e] * G_BLOCK_M;
     t.b_row0 = (int64_t)g * a.b_group_rows + (int64_t)nb * BLOCK_N;
@@ -364,6 +437,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = a.entries_dev ? min(a.num_tiles, *a.entries_dev * a.tiles_n) : a.num_tiles;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -387,7 +461,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
     if (elect_one()) {
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < a.num_tiles && alive; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
         const TileCoord t = tile_coord<kFormat, BLOCK_N>(a, tile);
         for (int k = 0; k < t.num_k; ++k, ++it) {
           const int s = it % STAGES;
@@ -423,7 +497,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
       bool alive = true;
       const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
       const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
-      for (int tile = blockIdx.x; tile < a.num_tiles && alive; tile += gridDim.x, ++tile_it) {
+      for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++tile_it) {
         const TileCoord t = tile_coord<kFormat, BLOCK_N>(a, tile);
         const int as = tile_it % ACC_STAGES;
         const uint32_t aph = (tile_it / ACC_STAGES) & 1;
@@ -468,13 +542,11 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
       alpha = __fdiv_rn(__fmul_rn(*a.amax_a, *a.amax_b), 6.0f * 6.0f * 448.0f * 448.0f);
     uint32_t tile_it = 0;
     bool alive = true;
-    for (int tile = blockIdx.x; tile < a.num_tiles && alive; tile += gridDim.x, ++tile_it) {
+    AmaxAcc am;
+    for (int tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x, ++tile_it) {
       const TileCoord t = tile_coord<kFormat, BLOCK_N>(a, tile);
       const int as = tile_it % ACC_STAGES;
       const uint32_t aph = (tile_it / ACC_STAGES) & 1;
-      if (t.num_k == 0) {
-        // empty contraction: the MMA warp still signals the barrier pair; result is all zeros
-      }
       if (!mbar_wait_bounded(&acc_full[as], aph, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
       tc_fence_after();
       const int64_t row = t.d_row0 + q * 32 + lane;
@@ -485,12 +557,13 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_blockscaled_kernel(const __
         tc_ld_32x32(tmem_base + Cfg::TMEM_ACC + as * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16) + c * 32, r);
         tc_wait_ld();
         const int64_t col0 = t.d_col0 + c * 32;
-        if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, t.num_k > 0, t.d_base + row * a.ldd + col0, col0);
+        if (row_ok && col0 < a.N) store_row_chunk(a, r, alpha, t.num_k > 0, t.d_base + row * a.ldd + col0, col0, am);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
     }
+    if (a.d_amax != nullptr) amax_publish(a.d_amax, am, lane);
   }
 
   tc_fence_before();
@@ -695,6 +768,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = a.entries_dev ? min(a.num_tiles, *a.entries_dev * a.tiles_n) : a.num_tiles;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -724,7 +798,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     if (elect_one()) {
       uint32_t it = 0;
       bool alive = true;
-      for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs) {
+      for (int tile = pair; tile < num_tiles && alive; tile += num_pairs) {
         const PairTile t = pair_tile<kFormat, BN>(a, tile);
         const int32_t a_row = (int32_t)t.a_row0 + (int)rank * 128;
         const int32_t b_row = (int32_t)t.b_row0 + (int)rank * (BN / 2);
@@ -737,7 +811,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.status, DS_EMPTY_WAIT)) { alive = false; break; }
-          const bool skip_b = (a.debug_skip_store & 4) != 0;   // bit 2: timing experiment without B loads
+          const bool skip_b = MT_KNOB(a, 4);
           if (leader) mbar_expect_tx(&full_bar[s], 2 * (Cfg::STAGE_BYTES - (skip_b ? Cfg::B_BYTES : 0)));
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
           // slab of each operand this K step falls in, and the step inside the slab
@@ -765,7 +839,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       bool alive = true;
       const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
       const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
-      for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
+      for (int tile = pair; tile < num_tiles && alive; tile += num_pairs, ++tile_it) {
         const PairTile t = pair_tile<kFormat, BN>(a, tile);
         const int num_k = t.num_k;
         const int as = tile_it % ACC;
@@ -779,7 +853,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
           tc_fence_after();
-          if (!(a.debug_skip_store & 2) || k == 0) {   // bit 1: timing experiment without scale copies
+          if (!MT_KNOB(a, 2) || k == 0) {
 #pragma unroll
           for (int c = 0; c < CH; ++c)
             tc_copy_sf_pair(tmem_base + Cfg::TMEM_SFA + 4 * c, umma_desc_sf(sfa_base + s * Cfg::SFA_BYTES + c * 512));
@@ -816,7 +890,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       alpha = __fdiv_rn(__fmul_rn(*a.amax_a, *a.amax_b), 6.0f * 6.0f * 448.0f * 448.0f);
     uint32_t tile_it = 0;
     bool alive = true;
-    for (int tile = pair; tile < a.num_tiles && alive; tile += num_pairs, ++tile_it) {
+    AmaxAcc am;
+    for (int tile = pair; tile < num_tiles && alive; tile += num_pairs, ++tile_it) {
       const PairTile t = pair_tile<kFormat, BN>(a, tile);
       const int num_k = t.num_k;
       const int as = tile_it % ACC;
@@ -839,7 +914,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-      if (a.debug_skip_store & 1) continue;
+      if (MT_KNOB(a, 1)) continue;
       // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
       // so a block that straddles a group boundary takes the direct, row-masked path (as do
       // unaligned outputs and bf16 accumulation).
@@ -849,13 +924,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         for (int c = 0; c < 4; ++c) {
           const int64_t col0 = colw + c * 32;
           if (c * 32 < ncols && row_ok && col0 < a.N)
-            store_row_chunk(a, acc[c], alpha, num_k > 0, t.d_base + row * a.ldd + col0, col0);
+            store_row_chunk(a, acc[c], alpha, num_k > 0, t.d_base + row * a.ldd + col0, col0, am);
         }
         continue;
       }
       store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
-                         t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0);
+                         t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
     }
+    if (a.d_amax != nullptr) amax_publish(a.d_amax, am, lane);
   }
 
   if (warp >= 2 && lane == 0) bulk_wait_all();  // output stores issued by this lane are complete
@@ -885,10 +961,6 @@ static int sm_count() {
   return n;
 }
 
-// SMs the persistent GEMM grids leave idle (mt_set_sm_margin): room for a collective's kernel
-// that should run beside the GEMM instead of waiting for its CTAs to retire.
-static int g_sm_margin = 0;
-
 template <int kFormat, int BLOCK_N, int STAGES, int ACC_STAGES>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, cudaStream_t st) {
   using Cfg = GemmCfg<kFormat, BLOCK_N, STAGES, ACC_STAGES>;
@@ -899,7 +971,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmA
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
     attr_set[slot] = true;
   }
-  const int grid = std::min(args.num_tiles, std::max(1, sm_count() - g_sm_margin));
+  const int grid = std::min(args.num_tiles, std::max(1, sm_count() - args.sm_margin));
   kern<<<grid, G_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, args);
   MT_CUDA(cudaGetLastError());
   return MT_OK;
@@ -929,26 +1001,23 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count() / 2; }
     max_pairs = n;
   }
-  const int pairs = std::min(args.num_tiles, std::max(1, max_pairs - (g_sm_margin + 1) / 2));
+  const int pairs = std::min(args.num_tiles, std::max(1, max_pairs - (args.sm_margin + 1) / 2));
   kern<<<2 * pairs, P_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, msa, msb, md, args);
   MT_CUDA(cudaGetLastError());
   return MT_OK;
 }
 
-// MT_GEMM_PAIR=0 forces the single-CTA kernel everywhere (tuning aid).
+// Timing-knob builds only: MT_GEMM_PAIR=0 forces the single-CTA kernel everywhere.
 static bool pair_enabled() {
   static int use_pair = -1;
-  if (use_pair < 0) {
-    const char* e = getenv("MT_GEMM_PAIR");
-    use_pair = e ? atoi(e) : 1;
-  }
+  if (use_pair < 0) use_pair = env_knob("MT_GEMM_PAIR", 1);
   return use_pair != 0;
 }
 
-// MT_GEMM_PAIR_N = 192 or 256 overrides the pair kernel's tile width (tuning aid); 0 = heuristic.
+// Timing-knob builds only: MT_GEMM_PAIR_N = 192 or 256 overrides the pair kernel's tile width.
 static int forced_pair_n() {
   static int forced_bn = -1;
-  if (forced_bn < 0) { const char* e = getenv("MT_GEMM_PAIR_N"); forced_bn = e ? atoi(e) : 0; }
+  if (forced_bn < 0) forced_bn = env_knob("MT_GEMM_PAIR_N", 0);
   return (forced_bn == 192 || forced_bn == 256) ? forced_bn : 0;
 }
 
@@ -960,9 +1029,11 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
                            int64_t ldd, int accumulate, GemmArgs& args, cudaStream_t st, int64_t a_slabs = 1,
                            int64_t b_slabs = 1) {
   static int band = -2;
-  if (band == -2) { const char* e = getenv("MT_GEMM_BAND"); band = e ? atoi(e) : -1; }
+  if (band == -2) band = env_knob("MT_GEMM_BAND", -1);
   args.band = band;
-  { static int skip = -1; if (skip < 0) { const char* e = getenv("MT_GEMM_DEBUG_SKIP_STORE"); skip = e ? atoi(e) : 0; } args.debug_skip_store = skip; }
+#ifdef MT_TIMING_KNOBS
+  { static int knobs = -1; if (knobs < 0) knobs = env_knob("MT_GEMM_KNOBS", 0); args.knobs = knobs; }
+#endif
   // a_slabs / b_slabs > 1: the operand is `slabs` matrices [rows, ld_bytes / slabs] stored one
   // after another, each with its own scale-chunk list (args.kc_* counts chunks per slab)
   const int64_t steps_total = (args.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB;
@@ -989,8 +1060,8 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   // Output through shared memory + TMA stores when the output rows are 16-byte aligned;
   // fp32 accumulation uses the TMA add-reduction, bf16 accumulation the direct path.
   const size_t es = d_dtype == MT_F32 ? 4 : 2;
-  static int allow_tma_store = -1;  // MT_GEMM_TMA_STORE=0 forces the direct path (tuning aid)
-  if (allow_tma_store < 0) { const char* e = getenv("MT_GEMM_TMA_STORE"); allow_tma_store = e ? atoi(e) : 1; }
+  static int allow_tma_store = -1;  // timing-knob builds only: MT_GEMM_TMA_STORE=0 forces the direct path
+  if (allow_tma_store < 0) allow_tma_store = env_knob("MT_GEMM_TMA_STORE", 1);
   CUtensorMap md = ma;
   args.tma_store = (allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16)) ? allow_tma_store : 0;
   args.map_rows = d_rows;
@@ -1008,22 +1079,23 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
                     : launch_gemm_pair<FMT_MXFP8, 256, 5>(ma, mb, msa, msb, md, args, st);
 }
 
-// Environment override used while tuning: MT_GEMM_BLOCK_N = 128 or 256.
+// Timing-knob builds only: MT_GEMM_BLOCK_N = 128 or 256 overrides the single-CTA tile width.
 static int pick_block_n(int64_t N) {
   static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("MT_GEMM_BLOCK_N");
-    forced = e ? atoi(e) : 0;
-  }
+  if (forced < 0) forced = env_knob("MT_GEMM_BLOCK_N", 0);
   if (forced == 128 || forced == 256) return forced;
   return N > 128 ? 256 : 128;
 }
 
 static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const float* amax_a, const uint8_t* b,
                        const uint8_t* sb, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,
-                       int64_t ldd, const void* bias, int bias_dtype, int accumulate, cudaStream_t st,
-                       int64_t a_slabs = 1, int64_t b_slabs = 1) {
+                       int64_t ldd, const void* bias, int bias_dtype, int accumulate, const mt_gemm_opts* opts,
+                       cudaStream_t st, int64_t a_slabs = 1, int64_t b_slabs = 1) {
   const char* name = format == FMT_NVFP4 ? "mt_gemm_nvfp4" : "mt_gemm_mxfp8";
+  const int sm_margin = opts ? opts->sm_margin : 0;
+  float* d_amax = opts ? opts->d_amax : nullptr;
+  MT_REQUIRE(sm_margin >= 0 && sm_margin < 128, "%s: sm_margin %d is not a valid SM count", name, sm_margin);
+  MT_REQUIRE(!(d_amax && accumulate), "%s: d_amax is not available together with accumulate", name);
   MT_REQUIRE(a_slabs >= 1 && b_slabs >= 1, "%s: slab counts must be positive", name);
   MT_REQUIRE(d != nullptr, "%s: null output pointer", name);
   MT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative shape", name);
@@ -1070,6 +1142,8 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   args.status = device_status_ptr();
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
   args.mode = MODE_DENSE;
+  args.sm_margin = sm_margin;
+  args.d_amax = d_amax;
   args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
   // K == 0 never reaches this point; tensor maps below need K_bytes >= 16
   if (pair_enabled() && M > G_BLOCK_M && N > 128) {
@@ -1107,57 +1181,23 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
 // ------------------------------------------------------------------------------------------
 // grouped GEMMs (per-expert weights), MXFP8
 // ------------------------------------------------------------------------------------------
-static int64_t grouped_entries_upper_bound(int64_t rows, int64_t groups) { return (rows + 127) / 128 + groups; }
-
-// `host_table` is host memory for 2 * grouped_entries_upper_bound(rows, G) int32 values (the
-// tile table is assembled there before it is copied into `scratch`).
+// `plan` is a device buffer written by build_grouped_plan for (rows, G): the tile entries, their
+// count and the group offsets are read from it by the kernel; the host only knows upper bounds.
 static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* sa, const uint8_t* b, const uint8_t* sb,
-                             int64_t b_rows, int64_t ldb_bytes, const int64_t* m_offsets_host, int64_t G, int64_t N_out,
+                             int64_t b_rows, int64_t ldb_bytes, const void* plan, int64_t G, int64_t R, int64_t N_out,
                              int64_t Kc, int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
-                             void* scratch, int64_t scratch_bytes, int32_t* host_table, cudaStream_t st) {
-  MT_REQUIRE(m_offsets_host && G > 0 && G <= 65536, "%s: bad group description", name);
-  const int64_t R = m_offsets_host[G];
-  MT_REQUIRE(m_offsets_host[0] == 0 && R >= 0, "%s: offsets must start at 0", name);
-  for (int64_t g = 0; g < G; ++g)
-    MT_REQUIRE(m_offsets_host[g + 1] >= m_offsets_host[g], "%s: offsets must be non-decreasing", name);
+                             cudaStream_t st) {
+  MT_REQUIRE(G > 0 && G <= PLAN_MAX_GROUPS && R >= 0 && R <= PLAN_MAX_ROWS, "%s: bad group description", name);
   MT_REQUIRE(d_dtype == MT_BF16 || d_dtype == MT_F32, "%s: output dtype %d not supported", name, d_dtype);
-  MT_REQUIRE(N_out % 128 == 0, "%s: N (%lld) must be a multiple of 128", name, (long long)N_out);
-  MT_REQUIRE(Kc % 128 == 0, "%s: K (%lld) must be a multiple of 128", name, (long long)Kc);
+  MT_REQUIRE(N_out > 0 && N_out % 128 == 0, "%s: N (%lld) must be a positive multiple of 128", name, (long long)N_out);
+  MT_REQUIRE(Kc > 0 && Kc % 128 == 0, "%s: K (%lld) must be a positive multiple of 128", name, (long long)Kc);
   MT_REQUIRE(ldd >= N_out, "%s: ldd smaller than N", name);
   if (R == 0) return MT_OK;
-  MT_REQUIRE(a && sa && b && sb && d && scratch, "%s: null pointer", name);
-  MT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sa) && aligned16(sb) && aligned16(scratch),
+  MT_REQUIRE(a && sa && b && sb && d && plan, "%s: null pointer", name);
+  MT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sa) && aligned16(sb) && aligned16(plan),
              "%s: operands must be 16-byte aligned", name);
-
-  // entries: for every row block (256 rows for the pair kernel, else 128), every group owning
-  // at least one of its rows
-  const bool pair = pair_enabled() && N_out >= 256 && R > 128;
-  const int pbn = forced_pair_n() ? forced_pair_n() : 256;
-  const int64_t blk = pair ? 256 : 128;
-  const int64_t rbs = (R + blk - 1) / blk;
-  const int64_t max_entries = grouped_entries_upper_bound(R, G);
-  const int64_t need = (int64_t)sizeof(int64_t) * (G + 1) + 2 * (int64_t)sizeof(int32_t) * max_entries;
-  MT_REQUIRE(scratch_bytes >= need, "%s: scratch too small (%lld < %lld bytes)", name, (long long)scratch_bytes,
-             (long long)need);
-  int32_t* table = host_table;
-  int64_t n = 0, g = 0;
-  for (int64_t rb = 0; rb < rbs; ++rb) {
-    const int64_t lo = rb * blk, hi = std::min<int64_t>(lo + blk, R);
-    while (g < G && m_offsets_host[g + 1] <= lo) ++g;  // skip groups that end before this block
-    for (int64_t gg = g; gg < G && m_offsets_host[gg] < hi; ++gg) {
-      if (m_offsets_host[gg + 1] <= m_offsets_host[gg]) continue;  // empty group
-      if (m_offsets_host[gg + 1] <= lo) continue;
-      table[n] = (int32_t)rb;
-      table[max_entries + n] = (int32_t)gg;
-      ++n;
-    }
-  }
-  uint8_t* sc = static_cast<uint8_t*>(scratch);
-  int64_t* d_offsets = reinterpret_cast<int64_t*>(sc);
-  int32_t* d_table = reinterpret_cast<int32_t*>(sc + sizeof(int64_t) * (G + 1));
-  MT_CUDA(cudaMemcpyAsync(d_offsets, m_offsets_host, sizeof(int64_t) * (G + 1), cudaMemcpyHostToDevice, st));
-  MT_CUDA(cudaMemcpyAsync(d_table, table, sizeof(int32_t) * 2 * max_entries, cudaMemcpyHostToDevice, st));
-  if (n == 0) return MT_OK;
+  const PlanView pv = plan_view(const_cast<void*>(plan), R, G);
+  const int64_t max_entries = plan_entries_upper_bound(R, G);
 
   GemmArgs args{};
   args.sa = sa; args.sb = sb;
@@ -1170,22 +1210,28 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
   args.mode = MODE_GROUPED_ROWS;
   args.num_groups = (int)G;
-  args.group_offsets = d_offsets;
-  args.tile_rb = d_table;
-  args.tile_group = d_table + max_entries;
+  args.group_offsets = pv.offsets;
   args.b_group_rows = b_group_rows;
   args.b_group_k_bytes = b_group_k;
   args.k_elems_per_byte_x2 = 2;
+  // entries: for every row block (256 rows for the pair kernel, else 128), every group owning
+  // at least one of its rows
+  const bool pair = pair_enabled() && N_out >= 256 && R > 128;
   if (pair) {
-    args.tiles_m = (int)n;
+    const int pbn = forced_pair_n() ? forced_pair_n() : 256;
+    args.tile_rb = pv.e256_rb; args.tile_group = pv.e256_group;
+    args.entries_dev = &pv.header->n_entries256;
+    args.tiles_m = (int)max_entries;
     args.tiles_n = (int)((N_out + pbn - 1) / pbn);
-    args.num_tiles = args.tiles_m * args.tiles_n;
+    args.num_tiles = (int)std::min<int64_t>(max_entries * args.tiles_n, INT32_MAX);
     return launch_pair_any(FMT_MXFP8, pbn, a, R, Kc, b, b_rows, ldb_bytes, d, d_dtype, R, N_out, ldd, 0, args, st);
   }
   const int bn = N_out % 256 == 0 ? 256 : 128;
-  args.tiles_m = (int)n;
+  args.tile_rb = pv.e128_rb; args.tile_group = pv.e128_group;
+  args.entries_dev = &pv.header->n_entries128;
+  args.tiles_m = (int)max_entries;
   args.tiles_n = (int)(N_out / bn);
-  args.num_tiles = args.tiles_m * args.tiles_n;
+  args.num_tiles = (int)std::min<int64_t>(max_entries * args.tiles_n, INT32_MAX);
   CUtensorMap ma, mb;
   int rc = make_tensor_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a, (uint64_t)Kc, (uint64_t)R, (uint64_t)Kc, G_BLOCK_KB,
                               G_BLOCK_M, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -1200,44 +1246,38 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
 
 extern "C" {
 
-int64_t mt_grouped_scratch_bytes(int64_t rows, int64_t groups) {
-  if (rows < 0 || groups < 0) return 0;
-  const int64_t e = mt::grouped_entries_upper_bound(rows, groups);
-  // large enough for any grouped entry point: offsets + (row block, group) table for the GEMMs,
-  // 16-byte tile records for the transposed quantize
-  return ((int64_t)sizeof(int64_t) * (groups + 1) + 16 * e + 255) / 256 * 256;
-}
-
 int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
-                          int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G, int64_t N, int64_t K,
-                          int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd, void* scratch,
-                          int64_t scratch_bytes, mt_stream_t stream) {
-  MT_REQUIRE(m_offsets_host && G > 0 && G <= 65536, "mt_grouped_gemm_mxfp8: bad group description");
-  std::vector<int32_t> table(2 * mt::grouped_entries_upper_bound(std::max<int64_t>(m_offsets_host[G], 0), G));
-  return mt::grouped_rows_gemm("mt_grouped_gemm_mxfp8", a, sa_swz, b, sb_swz, b_rows, ldb, m_offsets_host, G, N, K,
-                               b_group_rows, b_group_k, d, d_dtype, ldd, scratch, scratch_bytes, table.data(),
-                               static_cast<cudaStream_t>(stream));
+                          int64_t b_rows, int64_t ldb, const void* plan, int64_t G, int64_t rows, int64_t N, int64_t K,
+                          int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
+                          mt_stream_t stream) {
+  return mt::grouped_rows_gemm("mt_grouped_gemm_mxfp8", a, sa_swz, b, sb_swz, b_rows, ldb, plan, G, rows, N, K,
+                               b_group_rows, b_group_k, d, d_dtype, ldd, static_cast<cudaStream_t>(stream));
 }
 
 // ---- the same grouped GEMM for callers that cannot allocate device memory ----
-// Its tile tables live in this fixed array inside the library image (one copy per GPU that
-// loads the library, held until the process exits) instead of caller-provided scratch.
-#define MT_STATIC_ENTRIES (MT_STATIC_MAX_ROWS / 128 + MT_STATIC_MAX_GROUPS)
-#define MT_STATIC_SCRATCH_BYTES \
-  ((8 * (MT_STATIC_MAX_GROUPS + 1) + 8 * MT_STATIC_ENTRIES + 255) / 256 * 256)
-static __device__ __align__(256) unsigned char g_grouped_static_scratch[MT_STATIC_SCRATCH_BYTES];
+// Its plan lives in this fixed array inside the library image (one copy per GPU that loads the
+// library, held until the process exits) instead of a caller-provided buffer.
+#define MT_STATIC_PLAN_ENTRIES ((MT_STATIC_MAX_ROWS + 127) / 128 + MT_STATIC_MAX_GROUPS)
+#define MT_STATIC_PLAN_R16(n) (((n) + 15) / 16 * 16)
+#define MT_STATIC_PLAN_BYTES                                                                       \
+  ((64 + 2 * MT_STATIC_PLAN_R16(8 * (MT_STATIC_MAX_GROUPS + 1)) + 4 * MT_STATIC_PLAN_R16(4 * MT_STATIC_PLAN_ENTRIES) + \
+    16 * MT_STATIC_PLAN_ENTRIES + 255) / 256 * 256)
+static __device__ __align__(256) unsigned char g_grouped_static_plan[MT_STATIC_PLAN_BYTES];
 
 int mt_grouped_gemm_mxfp8_static(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
-                                 int64_t b_rows, int64_t ldb, const int64_t* m_offsets_host, int64_t G, int64_t N,
-                                 int64_t K, int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype, int64_t ldd,
-                                 mt_stream_t stream) {
+                                 int64_t b_rows, int64_t ldb, const int64_t* m_offsets, int64_t G, int64_t rows,
+                                 int64_t N, int64_t K, int64_t b_group_rows, int64_t b_group_k, void* d, int d_dtype,
+                                 int64_t ldd, mt_stream_t stream) {
   const char* name = "mt_grouped_gemm_mxfp8_static";
-  MT_REQUIRE(m_offsets_host && G > 0, "%s: bad group description", name);
+  MT_REQUIRE(m_offsets && G > 0 && rows >= 0, "%s: bad group description", name);
   MT_REQUIRE(G <= MT_STATIC_MAX_GROUPS, "%s: %lld groups exceed the built-in limit of %d; use mt_grouped_gemm_mxfp8 "
-             "with caller-provided scratch", name, (long long)G, MT_STATIC_MAX_GROUPS);
-  MT_REQUIRE(m_offsets_host[G] <= MT_STATIC_MAX_ROWS, "%s: %lld rows exceed the built-in limit of %d; use "
-             "mt_grouped_gemm_mxfp8 with caller-provided scratch", name, (long long)m_offsets_host[G], MT_STATIC_MAX_ROWS);
-  // The array's name is only a host-side handle; the kernel needs its device address, which is
+             "with a caller-provided plan", name, (long long)G, MT_STATIC_MAX_GROUPS);
+  MT_REQUIRE(rows <= MT_STATIC_MAX_ROWS, "%s: %lld rows exceed the built-in limit of %d; use mt_grouped_gemm_mxfp8 "
+             "with a caller-provided plan", name, (long long)rows, MT_STATIC_MAX_ROWS);
+  static_assert(MT_STATIC_PLAN_BYTES >= 0, "static plan size");
+  if (mt::plan_bytes(rows, G) > (int64_t)MT_STATIC_PLAN_BYTES)
+    return mt::fail(MT_ERR_INVALID_ARG, "%s: plan does not fit the built-in array", name);
+  // The array's name is only a host-side handle; the kernels need its device address, which is
   // looked up once per device (with that device current) and remembered.
   static void* dev_ptr[64] = {};
   int dev = -1;
@@ -1245,30 +1285,31 @@ int mt_grouped_gemm_mxfp8_static(const uint8_t* a, const uint8_t* sa_swz, const 
   MT_REQUIRE(dev >= 0 && dev < 64, "%s: device ordinal %d not supported", name, dev);
   if (dev_ptr[dev] == nullptr) {
     void* p = nullptr;
-    MT_CUDA(cudaGetSymbolAddress(&p, g_grouped_static_scratch));
+    MT_CUDA(cudaGetSymbolAddress(&p, g_grouped_static_plan));
     dev_ptr[dev] = p;
   }
-  static thread_local int32_t host_table[2 * MT_STATIC_ENTRIES];
-  return mt::grouped_rows_gemm(name, a, sa_swz, b, sb_swz, b_rows, ldb, m_offsets_host, G, N, K, b_group_rows, b_group_k,
-                               d, d_dtype, ldd, dev_ptr[dev], MT_STATIC_SCRATCH_BYTES, host_table,
-                               static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the plan is rebuilt by every call (a tiny kernel ahead of the GEMM on the same stream), so
+  // nothing of an earlier call's contents is relied on
+  int rc = mt::build_grouped_plan(m_offsets, G, rows, dev_ptr[dev], st);
+  if (rc != MT_OK) return rc;
+  return mt::grouped_rows_gemm(name, a, sa_swz, b, sb_swz, b_rows, ldb, dev_ptr[dev], G, rows, N, K, b_group_rows,
+                               b_group_k, d, d_dtype, ldd, st);
 }
 
 int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const uint8_t* b_t, const uint8_t* sb_t_swz,
-                           const int64_t* pad_offsets_host, int64_t G, int64_t N_out, int64_t K_out, void* d,
-                           int d_dtype, int accumulate, void* scratch, int64_t scratch_bytes, mt_stream_t stream) {
+                           const void* plan, int64_t G, int64_t rows, int64_t padded_rows, int64_t N_out,
+                           int64_t K_out, void* d, int d_dtype, int accumulate, mt_stream_t stream) {
   using namespace mt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const char* name = "mt_grouped_wgrad_mxfp8";
-  MT_REQUIRE(pad_offsets_host && G > 0 && G <= 65536, "%s: bad group description", name);
-  MT_REQUIRE(pad_offsets_host[0] == 0, "%s: offsets must start at 0", name);
-  for (int64_t g = 0; g < G; ++g)
-    MT_REQUIRE(pad_offsets_host[g + 1] >= pad_offsets_host[g] && pad_offsets_host[g + 1] % 128 == 0,
-               "%s: padded offsets must be non-decreasing multiples of 128", name);
+  MT_REQUIRE(G > 0 && G <= PLAN_MAX_GROUPS && rows >= 0 && rows <= PLAN_MAX_ROWS, "%s: bad group description", name);
+  MT_REQUIRE(padded_rows >= 0 && padded_rows % 128 == 0 && padded_rows <= rows + 127 * G,
+             "%s: padded row count %lld is not a multiple of 128 within [0, rows + 127 G]", name, (long long)padded_rows);
   MT_REQUIRE(d_dtype == MT_BF16 || d_dtype == MT_F32, "%s: output dtype %d not supported", name, d_dtype);
   MT_REQUIRE(N_out > 0 && K_out > 0, "%s: empty output", name);
-  MT_REQUIRE(d && scratch && scratch_bytes >= (int64_t)sizeof(int64_t) * (G + 1), "%s: null output or scratch too small", name);
-  const int64_t Rp = pad_offsets_host[G];
+  MT_REQUIRE(d != nullptr, "%s: null output", name);
+  const int64_t Rp = padded_rows;
   if (Rp == 0) {
     if (!accumulate) {
       const size_t es = d_dtype == MT_F32 ? 4 : 2;
@@ -1276,11 +1317,10 @@ int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const ui
     }
     return MT_OK;
   }
-  MT_REQUIRE(a_t && sa_t_swz && b_t && sb_t_swz, "%s: null pointer", name);
-  MT_REQUIRE(aligned16(a_t) && aligned16(b_t) && aligned16(sa_t_swz) && aligned16(sb_t_swz) && aligned16(scratch),
+  MT_REQUIRE(a_t && sa_t_swz && b_t && sb_t_swz && plan, "%s: null pointer", name);
+  MT_REQUIRE(aligned16(a_t) && aligned16(b_t) && aligned16(sa_t_swz) && aligned16(sb_t_swz) && aligned16(plan),
              "%s: operands must be 16-byte aligned", name);
-  int64_t* d_offsets = static_cast<int64_t*>(scratch);
-  MT_CUDA(cudaMemcpyAsync(d_offsets, pad_offsets_host, sizeof(int64_t) * (G + 1), cudaMemcpyHostToDevice, st));
+  const PlanView pv = plan_view(const_cast<void*>(plan), rows, G);
 
   GemmArgs args{};
   args.sa = sa_t_swz; args.sb = sb_t_swz;
@@ -1292,7 +1332,7 @@ int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const ui
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
   args.mode = MODE_GROUPED_K;
   args.num_groups = (int)G;
-  args.group_offsets = d_offsets;
+  args.group_offsets = pv.pad_offsets;
   args.d_group_stride = N_out * K_out;
   args.k_elems_per_byte_x2 = 2;
   if (pair_enabled() && N_out > 128 && K_out > 128) {
@@ -1319,37 +1359,32 @@ int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const ui
 
 int mt_gemm_nvfp4(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, const uint8_t* b,
                   const uint8_t* sb_swz, const float* amax_b, int64_t M, int64_t N, int64_t K, void* d, int d_dtype,
-                  int64_t ldd, const void* bias, int bias_dtype, int accumulate, mt_stream_t stream) {
+                  int64_t ldd, const void* bias, int bias_dtype, int accumulate, const mt_gemm_opts* opts,
+                  mt_stream_t stream) {
   return mt::gemm_common(mt::FMT_NVFP4, a, sa_swz, amax_a, b, sb_swz, amax_b, M, N, K, d, d_dtype, ldd, bias,
-                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream));
-}
-
-int mt_set_sm_margin(int sms) {
-  MT_REQUIRE(sms >= 0 && sms < 148, "mt_set_sm_margin: %d is not a valid SM count", sms);
-  mt::g_sm_margin = sms;
-  return MT_OK;
+                         bias_dtype, accumulate, opts, static_cast<cudaStream_t>(stream));
 }
 
 int mt_gemm_nvfp4_kslab(const uint8_t* a, const uint8_t* sa_swz, const float* amax_a, int64_t a_slabs, const uint8_t* b,
                         const uint8_t* sb_swz, const float* amax_b, int64_t b_slabs, int64_t M, int64_t N, int64_t K,
                         void* d, int d_dtype, int64_t ldd, const void* bias, int bias_dtype, int accumulate,
-                        mt_stream_t stream) {
+                        const mt_gemm_opts* opts, mt_stream_t stream) {
   return mt::gemm_common(mt::FMT_NVFP4, a, sa_swz, amax_a, b, sb_swz, amax_b, M, N, K, d, d_dtype, ldd, bias,
-                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream), a_slabs, b_slabs);
+                         bias_dtype, accumulate, opts, static_cast<cudaStream_t>(stream), a_slabs, b_slabs);
 }
 
 int mt_gemm_mxfp8_kslab(const uint8_t* a, const uint8_t* sa_swz, int64_t a_slabs, const uint8_t* b, const uint8_t* sb_swz,
                         int64_t b_slabs, int64_t M, int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd,
-                        const void* bias, int bias_dtype, int accumulate, mt_stream_t stream) {
+                        const void* bias, int bias_dtype, int accumulate, const mt_gemm_opts* opts, mt_stream_t stream) {
   return mt::gemm_common(mt::FMT_MXFP8, a, sa_swz, nullptr, b, sb_swz, nullptr, M, N, K, d, d_dtype, ldd, bias,
-                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream), a_slabs, b_slabs);
+                         bias_dtype, accumulate, opts, static_cast<cudaStream_t>(stream), a_slabs, b_slabs);
 }
 
 int mt_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz, int64_t M,
                   int64_t N, int64_t K, void* d, int d_dtype, int64_t ldd, const void* bias, int bias_dtype,
-                  int accumulate, mt_stream_t stream) {
+                  int accumulate, const mt_gemm_opts* opts, mt_stream_t stream) {
   return mt::gemm_common(mt::FMT_MXFP8, a, sa_swz, nullptr, b, sb_swz, nullptr, M, N, K, d, d_dtype, ldd, bias,
-                         bias_dtype, accumulate, static_cast<cudaStream_t>(stream));
+                         bias_dtype, accumulate, opts, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -6,6 +6,7 @@
 #include <cuda_fp8.h>
 
 #include "mt_common.cuh"
+#include "../../include/mt_b200_test.h"
 
 namespace mt {
 

@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "mt_common.cuh"
+#include "../../include/mt_b200_test.h"
 
 namespace mt {
 
@@ -79,11 +80,33 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_byt
   return MT_OK;
 }
 
+// One thread waits on a barrier that nothing signals; the bounded wait gives up after
+// `timeout_ns`, raises the status bit and the kernel returns.
+__global__ void bounded_wait_probe_kernel(int* status, uint64_t timeout_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    mbar_wait_bounded(&bar, 0, &abort_flag, status, DS_TMA_WAIT, timeout_ns);
+  }
+}
+
 }  // namespace mt
 
 extern "C" {
 
-int mt_version(void) { return 100; }
+int mt_test_bounded_wait(int64_t timeout_ns, mt_stream_t stream) {
+  MT_REQUIRE(timeout_ns > 0 && timeout_ns <= 100000000, "mt_test_bounded_wait: limit must be within (0, 100 ms]");
+  int* p = mt::device_status_ptr();
+  if (!p) return mt::fail(MT_ERR_CUDA, "device status word not reachable");
+  mt::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, (uint64_t)timeout_ns);
+  MT_CUDA(cudaGetLastError());
+  return MT_OK;
+}
+
+int mt_version(void) { return 200; }
 
 const char* mt_last_error_string(void) { return mt::g_error; }
 

@@ -7,8 +7,8 @@
 // column pass staged through shared memory so that global stores stay 16-byte and
 // row-contiguous. There is no per-tensor scale in this format, hence no abs-max pre-pass.
 #include <algorithm>
-#include <vector>
 
+#include "grouped_plan.cuh"
 #include "quantize_common.cuh"
 
 namespace mt {
@@ -33,6 +33,7 @@ struct Mxfp8Args {
   // grouped transposed mode: tile t covers input rows [tiles[t].row_start, +rows_valid) of one
   // group and writes 128 zero-padded token columns starting at tiles[t].out_col
   const int4* tiles;   // {row_start, rows_valid, out_col, last_tile}
+  const int32_t* num_tiles_dev;   // device count of valid entries of `tiles`
   int64_t out_cols;    // padded token count (row length of q_t)
 };
 
@@ -50,7 +51,9 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
   int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
   int4 gt = make_int4(0, QT_ROWS, 0, 0);
   if (kGrouped) {
+    if ((int)blockIdx.y >= *a.num_tiles_dev) return;   // uniform for the CTA: the plan holds fewer tiles
     gt = a.tiles[blockIdx.y];
+    if ((int64_t)gt.z + QT_ROWS > a.out_cols) return;   // the caller's padded count disagrees with the plan
     m0 = gt.x;
   }
 
@@ -301,43 +304,23 @@ extern "C" int mt_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, uint
 }
 
 
-extern "C" int64_t mt_grouped_padded_rows(const int64_t* m_offsets_host, int64_t G, int64_t* pad_offsets_out) {
-  if (!m_offsets_host || G <= 0) return 0;
-  int64_t off = 0;
-  if (pad_offsets_out) pad_offsets_out[0] = 0;
-  for (int64_t g = 0; g < G; ++g) {
-    const int64_t m = m_offsets_host[g + 1] - m_offsets_host[g];
-    off += (m + 127) / 128 * 128;
-    if (pad_offsets_out) pad_offsets_out[g + 1] = off;
-  }
-  return off;
-}
-
 namespace mt {
-static int grouped_quantize_mxfp8(const char* name, const void* x, int64_t rows, int64_t cols,
-                                  const int64_t* m_offsets_host, int64_t G, uint8_t* q, uint8_t* s, int64_t s_stride,
+// `plan` is the device buffer build_grouped_plan wrote for (rows, G); `padded_rows` is the padded
+// token count the caller sized q_t with (every group rounded up to 128 tokens).
+static int grouped_quantize_mxfp8(const char* name, const void* x, int64_t rows, int64_t cols, const void* plan,
+                                  int64_t G, int64_t padded_rows, uint8_t* q, uint8_t* s, int64_t s_stride,
                                   uint8_t* s_swz, uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
-                                  void* scratch, int64_t scratch_bytes, cudaStream_t st) {
-  MT_REQUIRE(m_offsets_host && G > 0, "%s: bad group description", name);
-  MT_REQUIRE(m_offsets_host[0] == 0 && m_offsets_host[G] == rows, "%s: offsets must run from 0 to rows", name);
+                                  cudaStream_t st) {
+  MT_REQUIRE(G > 0 && G <= PLAN_MAX_GROUPS && rows >= 0 && rows <= PLAN_MAX_ROWS, "%s: bad group description", name);
   MT_REQUIRE(cols > 0 && cols % 32 == 0, "%s: cols (%lld) must be a positive multiple of 32", name, (long long)cols);
-  std::vector<int4> tiles;
-  int64_t out_col = 0;
-  for (int64_t g = 0; g < G; ++g) {
-    const int64_t m = m_offsets_host[g + 1] - m_offsets_host[g];
-    MT_REQUIRE(m >= 0, "%s: offsets must be non-decreasing", name);
-    for (int64_t i = 0; i < m; i += 128) {
-      tiles.push_back(make_int4((int)(m_offsets_host[g] + i), (int)std::min<int64_t>(128, m - i), (int)out_col, 0));
-      out_col += 128;
-    }
-  }
-  if (tiles.empty()) return MT_OK;
-  tiles.back().w = 1;
-  MT_REQUIRE(x && q_t && s_t_swz && scratch, "%s: null pointer", name);
-  MT_REQUIRE(aligned16(x) && aligned16(q_t) && aligned16(s_t_swz) && aligned16(scratch), "%s: pointers must be 16-byte aligned", name);
-  MT_REQUIRE(scratch_bytes >= (int64_t)(tiles.size() * sizeof(int4)), "%s: scratch too small", name);
+  MT_REQUIRE(padded_rows >= 0 && padded_rows % 128 == 0 && padded_rows <= rows + 127 * G,
+             "%s: padded row count %lld is not a multiple of 128 within [0, rows + 127 G]", name, (long long)padded_rows);
+  if (rows == 0 || padded_rows == 0) return MT_OK;
+  const int64_t out_col = padded_rows;
+  MT_REQUIRE(x && q_t && s_t_swz && plan, "%s: null pointer", name);
+  MT_REQUIRE(aligned16(x) && aligned16(q_t) && aligned16(s_t_swz) && aligned16(plan), "%s: pointers must be 16-byte aligned", name);
   MT_REQUIRE(!s_t || (s_t_stride >= out_col / 32 && s_t_stride % 4 == 0), "%s: bad s_t stride", name);
-  MT_CUDA(cudaMemcpyAsync(scratch, tiles.data(), tiles.size() * sizeof(int4), cudaMemcpyHostToDevice, st));
+  const PlanView pv = plan_view(const_cast<void*>(plan), rows, G);
 
   Mxfp8Args args{};
   args.rows = rows; args.cols = cols;
@@ -353,32 +336,33 @@ static int grouped_quantize_mxfp8(const char* name, const void* x, int64_t rows,
   }
   args.status = device_status_ptr();
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
-  args.tiles = static_cast<const int4*>(scratch);
+  args.tiles = pv.qtiles;
+  args.num_tiles_dev = &pv.header->n_qtiles;
   args.out_cols = out_col;
   CUtensorMap map;
   int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)cols, (uint64_t)rows,
                               (uint64_t)cols * 2, QT_COLS, QT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != MT_OK) return rc;
-  dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)tiles.size());
+  // one grid row per 128-token tile: the padded count bounds the number of tiles; rows of the grid
+  // beyond the plan's tile count return at once
+  dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)(out_col / 128));
   return row_too ? launch_mxfp8<true, true, true>(map, args, grid, st) : launch_mxfp8<true, true>(map, args, grid, st);
 }
 }  // namespace mt
 
-extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols,
-                                                   const int64_t* m_offsets_host, int64_t G, uint8_t* q_t,
-                                                   uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, void* scratch,
-                                                   int64_t scratch_bytes, mt_stream_t stream) {
-  return mt::grouped_quantize_mxfp8("mt_grouped_transpose_quantize_mxfp8", x, rows, cols, m_offsets_host, G, nullptr,
-                                    nullptr, 0, nullptr, q_t, s_t, s_t_stride, s_t_swz, scratch, scratch_bytes,
+extern "C" int mt_grouped_transpose_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, const void* plan, int64_t G,
+                                                   int64_t padded_rows, uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride,
+                                                   uint8_t* s_t_swz, mt_stream_t stream) {
+  return mt::grouped_quantize_mxfp8("mt_grouped_transpose_quantize_mxfp8", x, rows, cols, plan, G, padded_rows, nullptr,
+                                    nullptr, 0, nullptr, q_t, s_t, s_t_stride, s_t_swz,
                                     static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int mt_grouped_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, const int64_t* m_offsets_host,
-                                         int64_t G, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
-                                         uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, void* scratch,
-                                         int64_t scratch_bytes, mt_stream_t stream) {
+extern "C" int mt_grouped_quantize_mxfp8(const void* x, int64_t rows, int64_t cols, const void* plan, int64_t G,
+                                         int64_t padded_rows, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                                         uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                                         mt_stream_t stream) {
   MT_REQUIRE(q != nullptr, "mt_grouped_quantize_mxfp8: null q");
-  return mt::grouped_quantize_mxfp8("mt_grouped_quantize_mxfp8", x, rows, cols, m_offsets_host, G, q, s, s_stride, s_swz,
-                                    q_t, s_t, s_t_stride, s_t_swz, scratch, scratch_bytes,
-                                    static_cast<cudaStream_t>(stream));
+  return mt::grouped_quantize_mxfp8("mt_grouped_quantize_mxfp8", x, rows, cols, plan, G, padded_rows, q, s, s_stride,
+                                    s_swz, q_t, s_t, s_t_stride, s_t_swz, static_cast<cudaStream_t>(stream));
 }

@@ -1,6 +1,7 @@
 """Thin torch-tensor front end over the C-ABI kernels: allocates outputs with torch, passes
 raw pointers and the current CUDA stream, raises on any error. No arithmetic happens here."""
 import contextlib
+import threading
 from dataclasses import dataclass
 from typing import Optional
 
@@ -147,15 +148,35 @@ def _gemm_out(M, N, out_dtype, out, accumulate, device):
     return out
 
 
+_GEMM_OPTS = threading.local()
+
+
 @contextlib.contextmanager
-def sm_margin(sms: int):
-    """GEMMs launched inside leave `sms` SMs idle, so that a collective in flight on another
-    stream runs beside them instead of behind them."""
-    _lib.call("mt_set_sm_margin", int(sms))
+def gemm_options(sm_margin: int = 0, d_amax: Optional[torch.Tensor] = None):
+    """Per-call options of the GEMMs launched inside by this thread (mt_gemm_opts):
+    sm_margin: SMs each launch leaves idle, so that a collective in flight on another stream
+    runs beside it instead of behind it; d_amax: fp32 device scalar (zeroed by the caller) that
+    the GEMM raises to the largest |value| it stores."""
+    prev = getattr(_GEMM_OPTS, "value", None)
+    _GEMM_OPTS.value = (int(sm_margin), d_amax)
     try:
         yield
     finally:
-        _lib.call("mt_set_sm_margin", 0)
+        _GEMM_OPTS.value = prev
+
+
+def sm_margin(sms: int):
+    return gemm_options(sm_margin=sms)
+
+
+def _opts():
+    cur = getattr(_GEMM_OPTS, "value", None)
+    if cur is None or (cur[0] == 0 and cur[1] is None):
+        return None
+    margin, amax = cur
+    if amax is not None:
+        assert amax.dtype == torch.float32 and amax.is_cuda and amax.numel() == 1
+    return _lib.ctypes.byref(_lib.GemmOpts(margin, None if amax is None else amax.data_ptr()))
 
 
 def _slabs(q):
@@ -182,7 +203,7 @@ def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat
         _lib.call("mt_gemm_nvfp4_kslab", qa.data_ptr(), sa_swz.data_ptr(), amax_a.data_ptr(), a_slabs, qb.data_ptr(),
                   sb_swz.data_ptr(), amax_b.data_ptr(), b_slabs, M, N, ka * 2, out.data_ptr(),
                   _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
-                  0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+                  0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _opts(), _stream())
         return out
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1] * 2
     assert qb.shape[1] * 2 == K
@@ -202,7 +223,7 @@ def gemm_nvfp4(qa, sa_swz, amax_a, qb, sb_swz, amax_b, *, out_dtype=torch.bfloat
     _lib.call("mt_gemm_nvfp4", qa.data_ptr(), sa_swz.data_ptr(), amax_a.data_ptr(), qb.data_ptr(),
               sb_swz.data_ptr(), amax_b.data_ptr(), M, N, K, out.data_ptr(), _out_dtype_code(out_dtype),
               out.stride(0), _ptr(bias), 0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate),
-              _stream())
+              _opts(), _stream())
     return out
 
 
@@ -216,7 +237,7 @@ def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, ac
         _count(1)
         _lib.call("mt_gemm_mxfp8_kslab", qa.data_ptr(), sa_swz.data_ptr(), a_slabs, qb.data_ptr(), sb_swz.data_ptr(),
                   b_slabs, M, N, ka, out.data_ptr(), _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
-                  0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+                  0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _opts(), _stream())
         return out
     M, N, K = qa.shape[0], qb.shape[0], qa.shape[1]
     assert qb.shape[1] == K
@@ -229,42 +250,73 @@ def gemm_mxfp8(qa, sa_swz, qb, sb_swz, *, out_dtype=torch.bfloat16, out=None, ac
         return out
     _lib.call("mt_gemm_mxfp8", qa.data_ptr(), sa_swz.data_ptr(), qb.data_ptr(), sb_swz.data_ptr(), M, N, K,
               out.data_ptr(), _out_dtype_code(out_dtype), out.stride(0), _ptr(bias),
-              0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _stream())
+              0 if bias is None else _out_dtype_code(bias.dtype), int(accumulate), _opts(), _stream())
     return out
 
 
 # ---- grouped (per-expert) MXFP8 path ----
-# The same m_splits list is used by every grouped call of a training step (fc1 / fc2, forward and
-# backward): its prefix sums and their ctypes form are kept for the last few distinct lists.
-_OFFSETS_CACHE: dict = {}
+class PadOffsets(list):
+    """Padded token offsets of the groups (a plain list) that also remember the split sizes
+    they were derived from, so that a later grouped call finds the same plan."""
+    splits: tuple = ()
 
 
-def _offsets_array(m_splits):
-    import ctypes
-    key = tuple(m_splits)
-    hit = _OFFSETS_CACHE.get(key)
+class GroupedPlan:
+    """Device-side description of one m_splits list, shared by every grouped call that uses the
+    list (fc1 / fc2, forward and backward): the plan buffer mt_grouped_plan_build fills, plus
+    the host-side numbers needed to size outputs (row total, padded offsets)."""
+
+    def __init__(self, m_splits, device):
+        self.splits = tuple(int(m) for m in m_splits)
+        self.groups = len(self.splits)
+        off, pad = [0], [0]
+        for m in self.splits:
+            assert m >= 0, "negative group size"
+            off.append(off[-1] + m)
+            pad.append(pad[-1] + (m + 127) // 128 * 128)
+        self.offsets, self.pad_offsets = off, PadOffsets(pad)
+        self.pad_offsets.splits = self.splits
+        self.rows, self.padded_rows = off[-1], pad[-1]
+        # the offsets reach the device by one small asynchronous copy from pinned memory; the
+        # tile tables are derived there
+        host = torch.tensor(off, dtype=torch.int64).pin_memory()
+        self._host = host                      # kept until the copy has certainly been issued and consumed
+        self.offsets_dev = host.to(device, non_blocking=True)
+        n = int(_lib.load().mt_grouped_plan_bytes(self.rows, self.groups))
+        assert n > 0, "group description out of range"
+        self.buffer = torch.empty(n, dtype=torch.uint8, device=device)
+        _lib.call("mt_grouped_plan_build", self.offsets_dev.data_ptr(), self.groups, self.rows, self.buffer.data_ptr(),
+                  n, _stream())
+        _count(1)
+
+    def ptr(self):
+        return self.buffer.data_ptr()
+
+
+# The same m_splits list is used by every grouped call of a training step: plans are kept for the
+# last few distinct lists per device (and stream, since the plan is built on the current stream).
+_PLAN_CACHE: dict = {}
+
+
+def grouped_plan(m_splits, device) -> GroupedPlan:
+    if isinstance(m_splits, GroupedPlan):
+        return m_splits
+    device = torch.device(device)
+    key = (tuple(int(m) for m in m_splits), device.index, _stream())
+    hit = _PLAN_CACHE.get(key)
     if hit is None:
-        off = [0]
-        for m in key:
-            off.append(off[-1] + int(m))
-        pad = [0]
-        for m in key:
-            pad.append(pad[-1] + (int(m) + 127) // 128 * 128)
-        if len(_OFFSETS_CACHE) >= 8:
-            _OFFSETS_CACHE.pop(next(iter(_OFFSETS_CACHE)))
-        hit = _OFFSETS_CACHE[key] = ((ctypes.c_int64 * len(off))(*off), off, pad)
-    return hit[0], hit[1]
+        if len(_PLAN_CACHE) >= 8:
+            _PLAN_CACHE.pop(next(iter(_PLAN_CACHE)))
+        hit = _PLAN_CACHE[key] = GroupedPlan(key[0], device)
+    return hit
 
 
 def grouped_padded_offsets(m_splits):
     """Token offsets after padding every group to a multiple of 128 tokens."""
-    _offsets_array(m_splits)
-    return _OFFSETS_CACHE[tuple(m_splits)][2]
-
-
-def _grouped_scratch(rows: int, groups: int, device) -> torch.Tensor:
-    n = int(_lib.load().mt_grouped_scratch_bytes(rows, groups))
-    return torch.empty(max(n, 256), dtype=torch.uint8, device=device)
+    pad = [0]
+    for m in m_splits:
+        pad.append(pad[-1] + (int(m) + 127) // 128 * 128)
+    return pad
 
 
 def grouped_transpose_quantize_mxfp8(x: torch.Tensor, m_splits, want_linear_scales: bool = False):
@@ -272,19 +324,17 @@ def grouped_transpose_quantize_mxfp8(x: torch.Tensor, m_splits, want_linear_scal
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     R, K = x.shape
-    arr, off = _offsets_array(m_splits)
-    assert off[-1] == R, "m_splits must sum to the number of rows"
-    pad = grouped_padded_offsets(m_splits)
-    Rp = pad[-1]
+    plan = grouped_plan(m_splits, x.device)
+    assert plan.rows == R, "m_splits must sum to the number of rows"
+    Rp = plan.padded_rows
     dev = x.device
     q_t = torch.empty((K, Rp), dtype=torch.uint8, device=dev)
     s_t_swz = torch.empty(swizzled_scale_bytes(K, Rp // 32), dtype=torch.uint8, device=dev)
     s_t = torch.empty((K, Rp // 32), dtype=torch.uint8, device=dev) if want_linear_scales else None
-    scratch = _grouped_scratch(R, len(m_splits), dev)
-    _lib.call("mt_grouped_transpose_quantize_mxfp8", x.data_ptr(), R, K, arr, len(m_splits), q_t.data_ptr(),
-              _ptr(s_t), Rp // 32, s_t_swz.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream())
+    _lib.call("mt_grouped_transpose_quantize_mxfp8", x.data_ptr(), R, K, plan.ptr(), plan.groups, Rp, q_t.data_ptr(),
+              _ptr(s_t), Rp // 32, s_t_swz.data_ptr(), _stream())
     _count(1 if Rp else 0)
-    return q_t, s_t_swz, s_t, pad
+    return q_t, s_t_swz, s_t, plan.pad_offsets
 
 
 def grouped_quantize_mxfp8(x: torch.Tensor, m_splits):
@@ -294,10 +344,9 @@ def grouped_quantize_mxfp8(x: torch.Tensor, m_splits):
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     R, K = x.shape
-    arr, off = _offsets_array(m_splits)
-    assert off[-1] == R, "m_splits must sum to the number of rows"
-    pad = grouped_padded_offsets(m_splits)
-    Rp = pad[-1]
+    plan = grouped_plan(m_splits, x.device)
+    assert plan.rows == R, "m_splits must sum to the number of rows"
+    Rp = plan.padded_rows
     dev = x.device
     q = torch.empty((R, K), dtype=torch.uint8, device=dev)
     s = torch.empty((R, K // 32), dtype=torch.uint8, device=dev)
@@ -306,12 +355,10 @@ def grouped_quantize_mxfp8(x: torch.Tensor, m_splits):
     q_t = torch.empty((K, Rp), dtype=torch.uint8, device=dev)
     s_t_swz = torch.empty(swizzled_scale_bytes(K, Rp // 32), dtype=torch.uint8, device=dev)
     if R:
-        scratch = _grouped_scratch(R, len(m_splits), dev)
-        _lib.call("mt_grouped_quantize_mxfp8", x.data_ptr(), R, K, arr, len(m_splits), q.data_ptr(), s.data_ptr(),
-                  K // 32, s_swz.data_ptr(), q_t.data_ptr(), None, Rp // 32, s_t_swz.data_ptr(), scratch.data_ptr(),
-                  scratch.numel(), _stream())
+        _lib.call("mt_grouped_quantize_mxfp8", x.data_ptr(), R, K, plan.ptr(), plan.groups, Rp, q.data_ptr(),
+                  s.data_ptr(), K // 32, s_swz.data_ptr(), q_t.data_ptr(), None, Rp // 32, s_t_swz.data_ptr(), _stream())
         _count(1)
-    return Quantized(q, s, s_swz), (q_t, s_t_swz, pad)
+    return Quantized(q, s, s_swz), (q_t, s_t_swz, plan.pad_offsets)
 
 
 def grouped_gemm_mxfp8(qa, sa_swz, qb, sb_swz, m_splits, *, n_out: int, transposed_weights: bool,
@@ -321,9 +368,9 @@ def grouped_gemm_mxfp8(qa, sa_swz, qb, sb_swz, m_splits, *, n_out: int, transpos
     transposed_weights=True:  qb = transposed stacked weights [n_out, G*K] (dgrad)."""
     _require_cuda(qa, "qa")
     R, K = qa.shape
-    G = len(m_splits)
-    arr, off = _offsets_array(m_splits)
-    assert off[-1] == R
+    plan = grouped_plan(m_splits, qa.device)
+    G = plan.groups
+    assert plan.rows == R
     if transposed_weights:
         assert qb.shape == (n_out, G * K)
         b_rows, ldb, grp_rows, grp_k = n_out, G * K, 0, K
@@ -331,32 +378,30 @@ def grouped_gemm_mxfp8(qa, sa_swz, qb, sb_swz, m_splits, *, n_out: int, transpos
         assert qb.shape == (G * n_out, K)
         b_rows, ldb, grp_rows, grp_k = G * n_out, K, n_out, 0
     out = torch.empty((R, n_out), dtype=out_dtype, device=qa.device)
-    scratch = _grouped_scratch(R, G, qa.device)
     _lib.call("mt_grouped_gemm_mxfp8", qa.data_ptr(), sa_swz.data_ptr(), qb.data_ptr(), sb_swz.data_ptr(), b_rows, ldb,
-              arr, G, n_out, K, grp_rows, grp_k, out.data_ptr(), _out_dtype_code(out_dtype), n_out,
-              scratch.data_ptr(), scratch.numel(), _stream())
+              plan.ptr(), G, R, n_out, K, grp_rows, grp_k, out.data_ptr(), _out_dtype_code(out_dtype), n_out, _stream())
     _count(1 if R else 0)
     return out
 
 
-def grouped_wgrad_mxfp8(qa_t, sa_t_swz, qb_t, sb_t_swz, pad_offsets, *, out_dtype=torch.float32, out=None,
+def grouped_wgrad_mxfp8(qa_t, sa_t_swz, qb_t, sb_t_swz, m_splits, *, out_dtype=torch.float32, out=None,
                         accumulate=False):
     """Per-group D_g[N, K] = qa_t[N, cols_g] . qb_t[K, cols_g]^T; returns [G, N, K]."""
-    import ctypes
     _require_cuda(qa_t, "qa_t")
-    G = len(pad_offsets) - 1
+    if isinstance(m_splits, PadOffsets):   # the padded offsets a grouped quantize returned
+        m_splits = m_splits.splits
+    plan = grouped_plan(m_splits, qa_t.device)
+    G = plan.groups
     N, K = qa_t.shape[0], qb_t.shape[0]
-    assert qa_t.shape[1] == qb_t.shape[1] == pad_offsets[-1]
+    assert qa_t.shape[1] == qb_t.shape[1] == plan.padded_rows
     if out is None:
         assert not accumulate
         out = torch.empty((G, N, K), dtype=out_dtype, device=qa_t.device)
     else:
         assert out.shape == (G, N, K) and out.dtype == out_dtype and out.is_contiguous()
-    arr = (ctypes.c_int64 * (G + 1))(*pad_offsets)
-    scratch = _grouped_scratch(pad_offsets[-1], G, qa_t.device)
     _lib.call("mt_grouped_wgrad_mxfp8", qa_t.data_ptr(), sa_t_swz.data_ptr(), qb_t.data_ptr(), sb_t_swz.data_ptr(),
-              arr, G, N, K, out.data_ptr(), _out_dtype_code(out_dtype), int(accumulate), scratch.data_ptr(),
-              scratch.numel(), _stream())
+              plan.ptr(), G, plan.rows, plan.padded_rows, N, K, out.data_ptr(), _out_dtype_code(out_dtype),
+              int(accumulate), _stream())
     _count(1)
     return out
 

@@ -55,10 +55,12 @@ def stacked_view(tensors: Sequence[torch.Tensor]):
     weights allocated from one block, or their main_grad buffers), or None when they do not."""
     if not tensors:
         return None
-    # the full adjacency walk costs one Python call per tensor: remember its verdict for this
-    # exact set of tensor objects at these addresses
-    first, last = tensors[0], tensors[-1]
-    key = (tuple(map(id, tensors)), first.data_ptr(), last.data_ptr(), first.dtype)
+    # the full adjacency walk (contiguity, storage, dtype per tensor) is remembered per set of
+    # tensors at these exact addresses: every address is part of the key, so re-pointing any
+    # one of them (`.data = ...`, a replaced main_grad) is noticed
+    first = tensors[0]
+    key = (tuple(t.data_ptr() for t in tensors), tuple(first.shape), tuple(first.stride()), first.dtype,
+           first.device)
     ok = _STACKED_OK.get(key)
     if ok is None:
         ok = _adjacent(tensors)

@@ -49,7 +49,9 @@ class _QuantizedGroupedLinear(torch.autograd.Function):
             qres_x, x_t = op.grouped_quantize_with_transpose(x, qlinear_params.x_params, m_splits)
         else:
             qres_x = op.quantize(x, qlinear_params.x_params, return_transpose=False)
-        if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
+        # (a cache filled under no_grad holds no transposed copy: refill it before a training pass)
+        if (is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None
+                or (is_grad_enabled and weight_qresult_cache.data_t is None)):
             # expert weights allocated by this module sit back to back: no stacking copy
             w_all = stacked_view(weights)
             if w_all is None:

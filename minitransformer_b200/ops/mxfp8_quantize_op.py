@@ -87,6 +87,6 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
         """a = grouped_transpose_quantize(dy), b = grouped_transpose_quantize(x) ->
         per-expert weight gradients [G, N, K] (or a list of G views)."""
         (qa, sa, pad), (qb, sb, pad_b) = a, b
-        assert pad == pad_b
+        assert list(pad) == list(pad_b) and pad.splits == pad_b.splits
         w = kernels.grouped_wgrad_mxfp8(qa, sa, qb, sb, pad, out_dtype=out_dtype, out=out, accumulate=accumulate)
         return w if single_output else list(w.unbind(0))

@@ -35,25 +35,37 @@ def test_invalid_arguments_are_rejected_with_a_message():
     p = (p + 15) // 16 * 16
     rc = lib.mt_quantize_nvfp4(p, 16, 24, 0, p, p, p, p, 1, None, None, None, 1, None, None)
     assert rc == -1 and b"multiple of 16" in lib.mt_last_error_string()
-    rc = lib.mt_gemm_nvfp4(p, p, p, p, p, p, 128, 128, 40, p, 0, 128, None, 0, 0, None)
+    rc = lib.mt_gemm_nvfp4(p, p, p, p, p, p, 128, 128, 40, p, 0, 128, None, 0, 0, None, None)
     assert rc == -1 and b"multiple of 32" in lib.mt_last_error_string()
-    rc = lib.mt_gemm_mxfp8(p, p, p, p, 128, 128, 64, p, 7, 128, None, 0, 0, None)
+    rc = lib.mt_gemm_mxfp8(p, p, p, p, 128, 128, 64, p, 7, 128, None, 0, 0, None, None)
     assert rc == -1 and b"dtype" in lib.mt_last_error_string()
     with pytest.raises(_lib.MtError):
         _lib.call("mt_swizzle_scales", None, 1, 1, 1, None, None)
     # K-slab operands: every slab must hold whole 128-byte K steps, and the shapes must be ones
     # the CTA-pair kernel takes
-    rc = lib.mt_gemm_nvfp4_kslab(p, p, p, 3, p, p, p, 1, 512, 512, 1024, p, 0, 512, None, 0, 0, None)
+    rc = lib.mt_gemm_nvfp4_kslab(p, p, p, 3, p, p, p, 1, 512, 512, 1024, p, 0, 512, None, 0, 0, None, None)
     assert rc == -1 and b"slab" in lib.mt_last_error_string()
-    rc = lib.mt_gemm_mxfp8_kslab(p, p, 2, p, p, 1, 128, 512, 1024, p, 0, 512, None, 0, 0, None)
+    rc = lib.mt_gemm_mxfp8_kslab(p, p, 2, p, p, 1, 128, 512, 1024, p, 0, 512, None, 0, 0, None, None)
     assert rc == -1 and b"M > 128" in lib.mt_last_error_string()
-    rc = lib.mt_gemm_mxfp8_kslab(p, p, 0, p, p, 1, 512, 512, 1024, p, 0, 512, None, 0, 0, None)
+    rc = lib.mt_gemm_mxfp8_kslab(p, p, 0, p, p, 1, 512, 512, 1024, p, 0, 512, None, 0, 0, None, None)
     assert rc == -1 and b"positive" in lib.mt_last_error_string()
-    assert lib.mt_set_sm_margin(-1) == -1 and b"SM count" in lib.mt_last_error_string()
-    assert lib.mt_set_sm_margin(16) == 0 and lib.mt_set_sm_margin(0) == 0
-    off = (ctypes.c_int64 * 3)(0, 5, 9)
-    rc = lib.mt_grouped_quantize_mxfp8(p, 9, 64, off, 2, None, None, 2, None, p, None, 4, p, p, 4096, None)
+    bad = _lib.GemmOpts(-1, None)
+    rc = lib.mt_gemm_mxfp8(p, p, p, p, 256, 256, 128, p, 0, 256, None, 0, 0, ctypes.byref(bad), None)
+    assert rc == -1 and b"SM count" in lib.mt_last_error_string()
+    both = _lib.GemmOpts(0, p)
+    rc = lib.mt_gemm_mxfp8(p, p, p, p, 256, 256, 128, p, 1, 256, None, 0, 1, ctypes.byref(both), None)
+    assert rc == -1 and b"accumulate" in lib.mt_last_error_string()
+    rc = lib.mt_grouped_quantize_mxfp8(p, 9, 64, p, 2, 256, None, None, 2, None, p, None, 8, p, None)
     assert rc == -1 and b"null q" in lib.mt_last_error_string()
+    # grouped plan: sizes and argument checks (the plan itself is built on the device)
+    assert lib.mt_grouped_plan_bytes(131072, 128) >= 64 + 2 * 129 * 8 + (1024 + 128) * 32
+    assert lib.mt_grouped_plan_bytes(-1, 4) == 0 and lib.mt_grouped_plan_bytes(16, 0) == 0
+    rc = lib.mt_grouped_plan_build(p, 2, 9, p, 16, None)
+    assert rc == -1 and b"too small" in lib.mt_last_error_string()
+    rc = lib.mt_grouped_wgrad_mxfp8(p, p, p, p, p, 2, 9, 100, 128, 128, p, 1, 0, None)
+    assert rc == -1 and b"multiple of 128" in lib.mt_last_error_string()
+    rc = lib.mt_test_bounded_wait(0, None)
+    assert rc == -1 and b"limit" in lib.mt_last_error_string()
 
 
 def test_front_end_refuses_cpu_tensors():
@@ -76,16 +88,14 @@ def test_stacked_view_of_adjacent_parameters_is_copy_free():
     assert view.data_ptr() == block.data_ptr() and torch.equal(view, block)
     assert stacked_view([torch.randn(3, 5) for _ in range(3)]) is None
     assert stacked_view([block[0], block[2]]) is None
-    # the verdict is remembered per set of tensor objects: replacing one of them must be noticed
+    # the verdict is remembered per set of addresses: re-pointing a middle tensor must be noticed
+    params[2].data = torch.randn(3, 5)
+    assert stacked_view(params) is None
     params[2] = torch.nn.Parameter(torch.randn(3, 5))
     assert stacked_view(params) is None
 
 
-def test_group_offset_arrays_are_cached_per_split_list():
+def test_padded_offsets_of_a_split_list():
     from minitransformer_b200 import kernels
-    a1, off1 = kernels._offsets_array([3, 0, 5])
-    a2, off2 = kernels._offsets_array((3, 0, 5))
-    assert a1 is a2 and off1 == [0, 3, 3, 8]
     assert kernels.grouped_padded_offsets([3, 0, 5]) == [0, 128, 128, 256]
-    a3, off3 = kernels._offsets_array([3, 1, 5])
-    assert a3 is not a1 and off3 == [0, 3, 4, 9] and list(a3) == off3
+    assert kernels.grouped_padded_offsets([128, 129]) == [0, 128, 384]

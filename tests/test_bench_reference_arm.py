@@ -1,5 +1,5 @@
 """The CPU arm of bench.py (`--impl reference`) runs without a GPU: one JSON line with the keys
-the benchmark contract names, timed on the numpy restatement of the reference emulation."""
+the benchmark contract names, timed on the reference's own emulation when oracle/_ref/ has been made, else on the numpy restatement."""
 import json
 import os
 import subprocess
@@ -21,7 +21,7 @@ def test_reference_arm_prints_one_contract_line():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["n_gpus"] == 1 and d["steps"] == 1
     assert d["metric"] == "nvfp4_linear_fwd_bwd_tflops" and d["unit"] == "TFLOP/s" and d["higher_is_better"] is True
-    assert d["value"] > 0 and d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["kind"] == "port"
+    assert d["value"] > 0 and d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["kind"] in ("reference", "port")
     assert d["e2e"] == {"value": d["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["config"]["tokens"] == 8192 and d["config"]["out_features"] == 14336
 

@@ -1,16 +1,13 @@
 """The grouped GEMM entry point that brings its own scratch memory.
 
-Some users of this library cannot pass scratch buffers: another allocator already owns all
-free GPU memory, or they are inside a loop where a device allocation (and the device-wide
-synchronisation it implies) is not acceptable. `mt_grouped_gemm_mxfp8_static` serves them from
-a fixed array inside the library. This file checks, through the C ABI, that it returns what
-`mt_grouped_gemm_mxfp8` returns for the same operands, twice in a row with different group
+Some users of this library cannot pass a buffer for the grouped plan: another allocator already
+owns all free GPU memory, or they are inside a loop where a device allocation (and the
+device-wide synchronisation it implies) is not acceptable. `mt_grouped_gemm_mxfp8_static` serves
+them from a fixed array inside the library. This file checks, through the C ABI, that it returns
+what `mt_grouped_gemm_mxfp8` returns for the same operands, twice in a row with different group
 layouts (the array keeps the first call's tables), and that problems beyond its built-in
 limits are refused with a clear message. It is named to be collected last.
 """
-import ctypes
-
-import numpy as np
 import pytest
 import torch
 
@@ -21,10 +18,11 @@ TOL = 1e-3  # relative Frobenius error, the tolerance of the other GEMM tests
 
 
 def _offsets(m_splits):
+    """Group offsets as a device int64 tensor, and the row total."""
     off = [0]
     for m in m_splits:
         off.append(off[-1] + m)
-    return (ctypes.c_int64 * len(off))(*off), off[-1]
+    return torch.tensor(off, dtype=torch.int64, device="cuda"), off[-1]
 
 
 def _run_both(m_splits, Kd, N, seed):
@@ -39,14 +37,16 @@ def _run_both(m_splits, Kd, N, seed):
     stream = torch.cuda.current_stream().cuda_stream
 
     want = torch.zeros(R, N, dtype=torch.bfloat16, device="cuda")
-    scratch = torch.empty(int(lib.mt_grouped_scratch_bytes(R, G)), dtype=torch.uint8, device="cuda")
+    plan = torch.empty(int(lib.mt_grouped_plan_bytes(R, G)), dtype=torch.uint8, device="cuda")
+    _lib.check(lib.mt_grouped_plan_build(arr.data_ptr(), G, R, plan.data_ptr(), plan.numel(), stream),
+               "mt_grouped_plan_build")
     _lib.check(lib.mt_grouped_gemm_mxfp8(qx.data.data_ptr(), qx.scale_swz.data_ptr(), qw.data.data_ptr(),
-                                         qw.scale_swz.data_ptr(), G * N, Kd, arr, G, N, Kd, N, 0,
-                                         want.data_ptr(), _lib.MT_BF16, N, scratch.data_ptr(), scratch.numel(), stream),
+                                         qw.scale_swz.data_ptr(), G * N, Kd, plan.data_ptr(), G, R, N, Kd, N, 0,
+                                         want.data_ptr(), _lib.MT_BF16, N, stream),
                "mt_grouped_gemm_mxfp8")
     got = torch.zeros(R, N, dtype=torch.bfloat16, device="cuda")
     _lib.check(lib.mt_grouped_gemm_mxfp8_static(qx.data.data_ptr(), qx.scale_swz.data_ptr(), qw.data.data_ptr(),
-                                                qw.scale_swz.data_ptr(), G * N, Kd, arr, G, N, Kd, N, 0,
+                                                qw.scale_swz.data_ptr(), G * N, Kd, arr.data_ptr(), G, R, N, Kd, N, 0,
                                                 got.data_ptr(), _lib.MT_BF16, N, stream),
                "mt_grouped_gemm_mxfp8_static")
     torch.cuda.synchronize()
@@ -70,9 +70,11 @@ def test_static_scratch_entry_point_refuses_oversized_problems():
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     p = buf.data_ptr()
     too_many = 1025
-    arr, _ = _offsets([0] * too_many)
-    rc = lib.mt_grouped_gemm_mxfp8_static(p, p, p, p, 128, 128, arr, too_many, 128, 128, 128, 0, p, _lib.MT_BF16, 128, None)
+    arr, rows = _offsets([0] * too_many)
+    rc = lib.mt_grouped_gemm_mxfp8_static(p, p, p, p, 128, 128, arr.data_ptr(), too_many, rows, 128, 128, 128, 0, p,
+                                          _lib.MT_BF16, 128, None)
     assert rc == -1 and b"limit of 1024" in lib.mt_last_error_string()
-    arr, _ = _offsets([1048576 + 128])
-    rc = lib.mt_grouped_gemm_mxfp8_static(p, p, p, p, 128, 128, arr, 1, 128, 128, 128, 0, p, _lib.MT_BF16, 128, None)
+    arr, rows = _offsets([1048576 + 128])
+    rc = lib.mt_grouped_gemm_mxfp8_static(p, p, p, p, 128, 128, arr.data_ptr(), 1, rows, 128, 128, 128, 0, p,
+                                          _lib.MT_BF16, 128, None)
     assert rc == -1 and b"limit of 1048576" in lib.mt_last_error_string()
