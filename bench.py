@@ -1,6 +1,7 @@
 """Benchmark of the quantized-linear hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --profile-case gemm|gemm_mxfp8|quant|quant_mxfp8|grouped
 
 One step = one forward + backward of the NVFP4 Linear of the reference recipe (Hadamard
 transform on the transposed activation / gradient copies) on synthetic data:
@@ -339,6 +340,130 @@ def _other_configs_single_gpu(torch, dev, steps=5, warmup=3):
     return out
 
 
+def tp_parity_check(group, T=2048, H=1024, Fd=4096, recipe="fp4_subchannel_scaling", peer=True):
+    """Parity of the tensor-parallel path on the ranks of `group` (one GPU each), run in-process
+    before the timed loop of `--gpus N` and by tests/test_gpu_tp.py:
+      * bit-exact: the quantized all-gather (codes, GEMM-layout scales, per-tensor abs-max)
+        equals quantizing the gathered tensor, and the wgrad GEMM over gathered K slabs equals
+        the GEMM on the interleaved transposed copy;
+      * within tolerance: column-parallel fc1 -> row-parallel fc2 forward + backward against
+        the same layers built from this rank's weight shards and run without any collective on
+        the full activations (partial sums reduced in fp32), once more with memory_saving.
+    The shape takes the copy-free gather on every world size up to 8. peer=True builds the layers
+    with ub_overlap_ag / ub_overlap_rs (exchanges over NVLink peer memory by this library's own
+    kernels, what the benchmark times); peer=False keeps them on the process group. Returns a
+    dict; raises nothing, the caller decides."""
+    import torch
+    import torch.distributed as dist
+    from minitransformer_b200 import kernels as K
+    from minitransformer_b200.module import config
+    from minitransformer_b200.module.linear import Linear, _QuantizedLinear
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    rcp = config.QuantizeRecipe(recipe)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    w1 = (torch.randn(Fd, H, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    w2 = (torch.randn(H, Fd, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    dy = (torch.randn(T, H, generator=g) * 1e-3).to(torch.bfloat16).cuda()
+    w1s, w2s = w1.chunk(world, 0)[rank].contiguous(), w2.chunk(world, 1)[rank].contiguous()
+
+    def relf(a, b):
+        return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+
+    # this rank's share of the work, with no process group: full activations, sharded weights
+    p0 = config.get_qlinear_params_from_predefined(rcp)
+    kw = dict(bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=p0)
+    e1, e2 = Linear(H, w1s.shape[0], **kw), Linear(w2s.shape[1], H, **kw)
+    with torch.no_grad():
+        e1.weight.copy_(w1s)
+        e2.weight.copy_(w2s)
+    xe = x.clone().requires_grad_(True)
+    he = e1(xe)
+    ye = e2(he)
+    ye.backward(dy)
+    y_sum, dx_sum = ye.detach().float(), xe.grad.float()
+    dist.all_reduce(y_sum, group=group)
+    dist.all_reduce(dx_sum, group=group)
+
+    errs, exact = {}, True
+    runs = {}
+    for mem_saving in (False, True):
+        p = config.get_qlinear_params_from_predefined(rcp)
+        p.memory_saving = mem_saving
+        kw = dict(bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=p, tp_group=group,
+                  sequence_parallel=True, ub_overlap_ag=peer, ub_overlap_rs=peer)
+        fc1 = Linear(H, Fd, parallel_mode="column", ub_name="parity_fc1", **kw)
+        fc2 = Linear(Fd, H, parallel_mode="row", ub_name="parity_fc2", **kw)
+        with torch.no_grad():
+            fc1.weight.copy_(w1s)
+            fc2.weight.copy_(w2s)
+        xd = x.chunk(world, 0)[rank].clone().requires_grad_(True)
+        h = fc1(xd)
+        y = fc2(h)
+        y.backward(dy.chunk(world, 0)[rank].contiguous())
+        torch.cuda.synchronize()
+        tag = "_memory_saving" if mem_saving else ""
+        errs["h" + tag] = relf(h, he)
+        errs["y" + tag] = relf(y, y_sum.chunk(world, 0)[rank])
+        errs["dx" + tag] = relf(xd.grad, dx_sum.chunk(world, 0)[rank])
+        errs["dw1" + tag] = relf(fc1.weight.grad, e1.weight.grad)
+        errs["dw2" + tag] = relf(fc2.weight.grad, e2.weight.grad)
+        runs[mem_saving] = (h.detach(), fc1.weight.grad, fc2.weight.grad)
+    # the local GEMMs see identical operands in both modes
+    exact &= all(torch.equal(a, b) for a, b in zip(runs[False], runs[True]))
+    exact &= torch.equal(runs[False][0], he.detach())
+
+    # quantized gather == quantize(gathered), in the form the GEMMs read
+    p = config.get_qlinear_params_from_predefined(rcp)
+    xs = x.chunk(world, 0)[rank].contiguous()
+    qf = p.quantize_op.quantize(x, p.x_params, return_transpose=True)
+    pg = None
+    if peer:
+        from minitransformer_b200.distributed.peer import get_peer_group
+        pg = get_peer_group(group, x.device)
+    qs = _QuantizedLinear.quantize_optionally_allgather(p.quantize_op, xs, p.x_params, True, True, True, group,
+                                                        weight_shape=(Fd, H), peer_group=pg, site="parity:x")
+    for hnd in tuple(getattr(qs, "_pending_handles", ())) + tuple(getattr(qs, "_pending_handles_t", ())):
+        hnd.wait()
+    copy_free = qs.data_t is not None and qs.data_t.dim() == 3
+    exact &= torch.equal(qs.data.view(torch.uint8), qf.data.view(torch.uint8))
+    if copy_free:
+        exact &= torch.equal(qs.scale_swz.view(-1), qf.scale_swz.view(-1))
+        exact &= torch.equal(qs.data_t.view(torch.uint8).permute(1, 0, 2).reshape(H, -1), qf.data_t.view(torch.uint8))
+        if qf.global_amax_row is not None:
+            args = lambda q: (q.data_t, q.scale_t_swz, q.global_amax_col)
+            d_plain = K.gemm_nvfp4(*args(qf), *args(qf), out_dtype=torch.float32)
+            d_slab = K.gemm_nvfp4(*args(qf), *args(qs), out_dtype=torch.float32)
+            d_slab2 = K.gemm_nvfp4(*args(qs), *args(qs), out_dtype=torch.float32)
+        else:
+            args = lambda q: (q.data_t.view(torch.uint8), q.scale_t_swz)
+            d_plain = K.gemm_mxfp8(*args(qf), *args(qf), out_dtype=torch.float32)
+            d_slab = K.gemm_mxfp8(*args(qf), *args(qs), out_dtype=torch.float32)
+            d_slab2 = K.gemm_mxfp8(*args(qs), *args(qs), out_dtype=torch.float32)
+        exact &= torch.equal(d_plain, d_slab) and torch.equal(d_plain, d_slab2)
+    else:
+        exact &= torch.equal(qs.scale.view(torch.uint8), qf.scale.view(torch.uint8)[: qs.scale.shape[0]])
+        exact &= torch.equal(qs.data_t.view(torch.uint8), qf.data_t.view(torch.uint8))
+    if qf.global_amax_row is not None:
+        exact &= float(qs.global_amax_row) == float(qf.global_amax_row)
+        exact &= float(qs.global_amax_col) == float(qf.global_amax_col)
+    status = K.read_device_status()
+
+    # local GEMMs see identical quantized operands (1e-3); the two reduce-scattered results carry
+    # the rounding of bf16 partial sums (1e-2)
+    tight = max(v for k, v in errs.items() if k.split("_")[0] in ("h", "dw1", "dw2"))
+    loose = max(v for k, v in errs.items() if k.split("_")[0] in ("y", "dx"))
+    ok = bool(exact) and tight <= 1e-3 and loose <= 1e-2 and status == 0
+    flags = torch.tensor([1.0 if ok else 0.0, 1.0 if exact else 0.0, -tight, -loose], device="cuda")
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=group)
+    return {"tp": world, "ok": bool(flags[0] > 0.5), "bit_exact": bool(flags[1] > 0.5),
+            "max_rel_frob": float(-flags[2]), "max_rel_frob_reduced_outputs": float(-flags[3]),
+            "tolerance": {"local_gemms": 1e-3, "reduce_scattered": 1e-2}, "copy_free_gather": bool(copy_free),
+            "shape": {"tokens": T, "hidden": H, "ffn": Fd}, "recipe": recipe, "memory_saving_checked": True,
+            "exchange": "peer memory (own kernels)" if pg is not None else "process group (NCCL)",
+            "rank_errors": errs if rank == 0 else None}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -370,6 +495,22 @@ def run_gpu_arm(args):
         return t.pin_memory() if pin else t
 
     gemm_ms, quant_ms = [], []
+    parity = base = None
+    if n > 1:
+        # parity first: the sharded path must reproduce the per-rank emulation before it is timed
+        parity = tp_parity_check(tp_group, peer=os.environ.get("MT_BENCH_TP_EXCHANGE", "peer") != "nccl")
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": n, "parity": parity, "error": "tensor-parallel parity failed"}),
+                      flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
+        # base of the strong-scaling series: the same MLP unsharded, timed on rank 0 alone
+        if rank == 0:
+            base = _tp_workload_single_gpu(torch, Linear, params, dev, kernels)
+            torch.cuda.empty_cache()
+        dist.barrier()
 
     if n == 1:
         T, K_in, N_out = C2["tokens"], C2["in_features"], C2["out_features"]
@@ -492,13 +633,16 @@ def run_gpu_arm(args):
     else:
         T, H, Fd = C4["tokens"], C4["hidden"], C4["ffn"]
         assert T % n == 0 and Fd % n == 0
+        peer = os.environ.get("MT_BENCH_TP_EXCHANGE", "peer") != "nccl"   # "nccl": the process-group exchanges, for comparison
         x_h, dy_h = randn_bf16((T // n, H), 1.0, pin=True), randn_bf16((T // n, H), 1e-3, pin=True)
         fc1 = Linear(H, Fd, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
                      parallel_mode="column", sequence_parallel=True, tp_group=tp_group, fuse_wgrad_accumulation=True,
-                     init_method=lambda t: torch.nn.init.normal_(t, std=0.02))
+                     init_method=lambda t: torch.nn.init.normal_(t, std=0.02), ub_overlap_ag=peer, ub_overlap_rs=peer,
+                     ub_name="fc1")
         fc2 = Linear(Fd, H, bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
                      parallel_mode="row", sequence_parallel=True, tp_group=tp_group, fuse_wgrad_accumulation=True,
-                     init_method=lambda t: torch.nn.init.normal_(t, std=0.02))
+                     init_method=lambda t: torch.nn.init.normal_(t, std=0.02), ub_overlap_ag=peer, ub_overlap_rs=peer,
+                     ub_name="fc2")
         for m in (fc1, fc2):
             m.weight.main_grad = torch.zeros_like(m.weight, dtype=torch.float32)
         x, dy = x_h.to(dev), dy_h.to(dev)
@@ -577,6 +721,11 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
         }
+        if n > 1:
+            line["parity"] = parity
+            line["scaling_base_ms"] = base["ms_per_step"]
+            line["scaling_base"] = base["workload"] + ", timed on rank 0 before the sharded run"
+            line["efficiency_vs_tp1"] = base["ms_per_step"] / (n * ms_step)
         if n == 1:
             g_avg = sum(g_ms) / len(g_ms)
             T_, H_, F_ = C2["tokens"], C2["in_features"], C2["out_features"]
@@ -622,13 +771,78 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(what: str) -> None:
+    """Small, self-contained kernel workloads for `ncu` captures (one kernel family each, a few
+    launches, a few hundred MB on the device; the quantize inputs exceed the 126 MB L2):
+      gemm         NVFP4 pair GEMM 4096x9472x4096 (8 full waves), 3 launches
+      gemm_mxfp8   MXFP8 pair GEMM, same shape
+      quant        abs-max + NVFP4 cast/transpose (RHT) of 8192x14336
+      quant_mxfp8  MXFP8 cast/transpose of 8192x14336
+      grouped      MXFP8 GroupedLinear fc1+fc2 fwd+bwd, 128 experts, 2 steps"""
+    import torch
+    from minitransformer_b200 import kernels as K
+    dev = "cuda"
+    torch.manual_seed(0)
+    if what in ("gemm", "gemm_mxfp8"):
+        M, N, Kd = 4096, 9472, 4096   # 16 x 37 pair tiles = 8 x 74: no partial last wave
+        x = torch.randn(M, Kd, device=dev).to(torch.bfloat16)
+        w = (torch.randn(N, Kd, device=dev) * 0.02).to(torch.bfloat16)
+        if what == "gemm":
+            a, b = K.quantize_nvfp4(x, return_transpose=False), K.quantize_nvfp4(w, return_transpose=False)
+            for _ in range(3):
+                K.gemm_nvfp4(a.data, a.scale_swz, a.amax_row, b.data, b.scale_swz, b.amax_row)
+        else:
+            a, b = K.quantize_mxfp8(x, return_transpose=False), K.quantize_mxfp8(w, return_transpose=False)
+            for _ in range(3):
+                K.gemm_mxfp8(a.data, a.scale_swz, b.data, b.scale_swz)
+    elif what == "quant":
+        x = (torch.randn(8192, 14336, device=dev) * 1e-3).to(torch.bfloat16)
+        for _ in range(3):
+            K.quantize_nvfp4(x, with_rht=True)
+    elif what == "quant_mxfp8":
+        x = torch.randn(8192, 14336, device=dev).to(torch.bfloat16)
+        for _ in range(3):
+            K.quantize_mxfp8(x)
+    elif what == "grouped":
+        # GroupedLinear fc1 + fc2 forward+backward: 128 experts, 131072 rows, Zipf(1.1) group sizes
+        import numpy as np
+        from minitransformer_b200.module import config as mt_config
+        from minitransformer_b200.module.group_linear import GroupedLinear
+        params = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+        G, R, H, Fd = 128, 131072, 2048, 768
+        rng = np.random.default_rng(1234)
+        p = 1.0 / np.arange(1, G + 1) ** 1.1
+        m_splits = np.bincount(rng.choice(G, size=R, p=p / p.sum()), minlength=G).tolist()
+        kw = dict(bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params,
+                  fuse_wgrad_accumulation=True, init_method=lambda t: torch.nn.init.normal_(t, std=0.02))
+        fc1, fc2 = GroupedLinear(G, H, Fd, **kw), GroupedLinear(G, Fd, H, **kw)
+        for m in (fc1, fc2):
+            block = torch.zeros(G, m.out_features, m.in_features, dtype=torch.float32, device=dev)
+            for i in range(G):
+                getattr(m, f"weight{i}").main_grad = block[i]
+        x = torch.randn(R, H, device=dev).to(torch.bfloat16)
+        dy = (torch.randn(R, H, device=dev) * 1e-3).to(torch.bfloat16)
+        for _ in range(2):
+            xd = x.detach().requires_grad_(True)
+            fc2(fc1(xd, m_splits, is_first_microbatch=True), m_splits, is_first_microbatch=True).backward(dy)
+    else:
+        raise SystemExit(f"unknown case {what!r}")
+    torch.cuda.synchronize()
+    print("done, device status", K.read_device_status())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--profile-case", default=None,
+                    help="run one small kernel workload for a profiler capture and exit (see run_profile_case)")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)

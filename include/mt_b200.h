@@ -106,10 +106,27 @@ int mt_swizzle_scales(const uint8_t* s, int64_t rows, int64_t k_blocks, int64_t 
  *              |value| it stores in d, after rounding to d's type. Zero it before the launch.
  *              The next layer's NVFP4 quantize can take it as its per-tensor abs-max instead
  *              of re-reading d (the QuantizeInputMetaBase.amax hook,
- *              miniTransformer/ops/quantization.py:90-94). Not available with accumulate. */
+ *              miniTransformer/ops/quantization.py:90-94). Not available with accumulate.
+ *   n_dest, my_rank, dest, dest_rows   (n_dest > 1) scatter of the output rows over the ranks of a
+ *              tensor-parallel group, the first half of a reduce-scatter done by the GEMM
+ *              itself: output rows [r * dest_rows, (r + 1) * dest_rows) are not written to d but
+ *              stored over NVLink into rank r's staging buffer dest[r] (a mapped peer address,
+ *              see mt_ipc_import; dest[my_rank] is local), a bf16 matrix
+ *              [n_dest * dest_rows, N] with row pitch N, at rows my_rank * dest_rows + (row
+ *              inside the slice). After a peer barrier every rank sums the n_dest slices of its
+ *              own staging buffer with mt_peer_reduce_bf16. Needs bf16 output without
+ *              accumulate or bias, M == n_dest * dest_rows, dest_rows % 256 == 0, N % 8 == 0;
+ *              d may be null. Replaces the reduce-scatter of bf16 partial sums after a
+ *              row-parallel GEMM (miniTransformer/module/linear.py:322-328, 404-410) with
+ *              stores that travel while later tiles are still being computed. */
+#define MT_MAX_PEERS 8
 typedef struct mt_gemm_opts {
   int sm_margin;
   float* d_amax;
+  int n_dest;
+  int my_rank;
+  void* dest[MT_MAX_PEERS];
+  int64_t dest_rows;
 } mt_gemm_opts;
 
 /* Block-scaled GEMM  D[M,N] = alpha * (A . B^T) (+ bias[N]) (+ D when accumulate), both
@@ -247,6 +264,54 @@ int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const ui
                            const void* plan, int64_t G, int64_t rows, int64_t padded_rows,
                            int64_t N_out, int64_t K_out, void* d, int d_dtype, int accumulate,
                            mt_stream_t stream);
+
+/* ---- Tensor-parallel exchange over NVLink peer memory (ranks of one node, one GPU per process) ----
+ * These replace the NCCL collectives of the sequence-parallel Linear on one NVSwitch node
+ * (miniTransformer/distributed/distributed.py:43-121 as used by module/linear.py:231-240,
+ * 322-328, 356-365, 404-410) with kernels of this library that read and write the peers' memory
+ * directly. Every rank allocates its buffers itself (any cudaMalloc'ed memory), exports them with
+ * mt_ipc_export, exchanges the handles through its own channel (a process group, a file), and
+ * maps the peers' buffers with mt_ipc_import. The entry points take tables of n addresses
+ * indexed by rank; entry `me` is the rank's own buffer. All waits on peers are bounded (2 s);
+ * on expiry bit 64 of the device status word is raised (mt_read_device_status).
+ *
+ * Control block: MT_PEER_CTRL_BYTES bytes per rank, zeroed once before every rank's first call
+ * (with a host-side barrier between the zeroing and the first use). `channel` (0..7) separates
+ * call sequences that may overlap in time (different streams); on one channel every rank must
+ * issue the same sequence of calls with the same, strictly increasing `epoch` (start at 1). */
+#define MT_PEER_CTRL_BYTES 4096
+#define MT_MAX_GATHER_SEGS 8
+#define MT_IPC_HANDLE_BYTES 64
+int mt_ipc_export(const void* ptr, uint8_t* handle_out /* MT_IPC_HANDLE_BYTES */, int64_t* offset_out);
+int mt_ipc_import(const uint8_t* handle, int64_t offset, void** ptr_out);
+int mt_ipc_close(void* ptr, int64_t offset);
+
+/* All ranks' work enqueued before the barrier on `stream` (on each rank's own stream) is complete
+ * and visible to every rank's work enqueued after it. One 32-thread kernel. */
+int mt_peer_barrier(const void* const* ctrl, int n, int me, int channel, uint32_t epoch, mt_stream_t stream);
+
+/* vals[0..nvals) (device fp32, nvals <= 4, non-negative values) <- element-wise maximum over all
+ * ranks; also a barrier. The per-tensor abs-max of a token-sharded activation before its shards
+ * are quantized (the MAX all-reduce of miniTransformer/ops/quantization.py:100-119 `reduce_amax`). */
+int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, uint32_t epoch,
+                          float* vals, int nvals, mt_stream_t stream);
+
+/* All-gather by pulling: for every segment s < nseg and every rank r < n, copies shard_bytes[s]
+ * bytes from shared[r] + src_offsets[s] to dsts[s] + r * shard_bytes[s]. The quantize kernels
+ * write a rank's shard (codes, scales, transposed codes, transposed scales) straight into its
+ * shared buffer; after a peer barrier this one launch assembles the gathered tensors in the
+ * layout the GEMMs read. `ctas` bounds the SMs used (the copy is NVLink-bound; 32 to 64 suffice).
+ * Sizes, offsets and addresses are multiples of 16 bytes. The caller keeps a shard unchanged
+ * until a later barrier shows that every rank has pulled it. */
+int mt_peer_gather(const void* const* shared, int n, int me, const int64_t* src_offsets, void* const* dsts,
+                   const int64_t* shard_bytes, int nseg, int ctas, mt_stream_t stream);
+
+/* out[rows, cols] (bf16) = sum over s < n of stage[s][rows, cols] (bf16, fp32 accumulation in rank
+ * order, one rounding): the second half of the reduce-scatter started by a GEMM with
+ * mt_gemm_opts.n_dest, run after a peer barrier. amax_out (optional, zeroed by the caller) is
+ * raised to max |out|. */
+int mt_peer_reduce_bf16(const void* stage, int n, int64_t rows, int64_t cols, void* out, float* amax_out,
+                        mt_stream_t stream);
 
 /* Reads and clears the device-side status word the kernels raise when a bounded wait
  * expires (0 = clean). Synchronises the given stream. */

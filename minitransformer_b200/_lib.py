@@ -13,6 +13,7 @@ HEADER_PATHS = (os.path.join(INCLUDE_DIR, "mt_b200.h"), os.path.join(INCLUDE_DIR
 
 MT_BF16, MT_F32 = 0, 1
 MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16 = 1, 2, 4
+MT_MAX_PEERS, MT_PEER_CTRL_BYTES, MT_IPC_HANDLE_BYTES = 8, 4096, 64
 
 _c = ctypes
 _vp, _i64, _int = _c.c_void_p, _c.c_int64, _c.c_int
@@ -20,7 +21,8 @@ _vp, _i64, _int = _c.c_void_p, _c.c_int64, _c.c_int
 
 class GemmOpts(ctypes.Structure):
     """mt_gemm_opts of include/mt_b200.h."""
-    _fields_ = [("sm_margin", _int), ("d_amax", _vp)]
+    _fields_ = [("sm_margin", _int), ("d_amax", _vp), ("n_dest", _int), ("my_rank", _int), ("dest", _vp * 8),
+                ("dest_rows", _i64)]
 
 
 _opts = _c.POINTER(GemmOpts)
@@ -51,6 +53,14 @@ _SIGNATURES = {
     "mt_grouped_gemm_mxfp8_static": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                             _vp, _int, _i64, _vp]),
     "mt_grouped_wgrad_mxfp8": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _int, _int, _vp]),
+    "mt_ipc_export": (_int, [_vp, _vp, _c.POINTER(_i64)]),
+    "mt_ipc_import": (_int, [_vp, _i64, _c.POINTER(_vp)]),
+    "mt_ipc_close": (_int, [_vp, _i64]),
+    "mt_peer_barrier": (_int, [_c.POINTER(_vp), _int, _int, _int, _c.c_uint32, _vp]),
+    "mt_peer_allreduce_max": (_int, [_c.POINTER(_vp), _int, _int, _int, _c.c_uint32, _vp, _int, _vp]),
+    "mt_peer_gather": (_int, [_c.POINTER(_vp), _int, _int, _c.POINTER(_i64), _c.POINTER(_vp), _c.POINTER(_i64), _int, _int,
+                              _vp]),
+    "mt_peer_reduce_bf16": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp]),
     "mt_read_device_status": (_int, [_c.POINTER(_int), _vp]),
 }
 

@@ -75,6 +75,8 @@ struct GemmArgs {
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
   float* d_amax;                 // optional: atomic max of |stored value| (pair kernel, no accumulation)
+  int n_dest, my_rank;           // n_dest > 1 (pair kernel, dense, staged stores): output rows are scattered over
+  int64_t dest_rows;             // the ranks' staging buffers, dest_rows rows each (PeerMaps), instead of d
 #ifdef MT_TIMING_KNOBS
   int knobs;                     // builds with -DMT_TIMING_KNOBS only (results are wrong when set): bit 0 the
                                  // epilogue drains tensor memory but writes nothing, bit 1 scale factors are
@@ -744,6 +746,12 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& a, int tile) {
   return t;
 }
 
+// Output tensor maps of a scattering GEMM: one per destination rank, identical geometry
+// ([n_dest * dest_rows, N] bf16), different base address.
+struct alignas(64) PeerMaps {
+  CUtensorMap m[MT_MAX_PEERS];
+};
+
 template <int kFormat, int BN, int STAGES>
 // Register budget: 10 warps land 3 + 3 + 2 + 2 on the four SM sub-partitions of 16384 registers
 // each, so 168 per thread is the most that launches (more fails with "too many resources").
@@ -751,7 +759,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
     gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                  const __grid_constant__ CUtensorMap map_sfa,
                                  const __grid_constant__ CUtensorMap map_sfb,
-                                 const __grid_constant__ CUtensorMap map_d, const GemmArgs a) {
+                                 const __grid_constant__ CUtensorMap map_d, const __grid_constant__ PeerMaps maps_peer,
+                                 const GemmArgs a) {
   using Cfg = PairCfg<kFormat, BN, STAGES>;
   constexpr int CH = Cfg::CH, ACC = Cfg::ACC, NSB = Cfg::NSB;
   extern __shared__ uint8_t smem_raw[];
@@ -928,6 +937,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         }
         continue;
       }
+      if (a.n_dest > 1) {
+        // this warp's 32 rows belong to one destination rank (dest_rows is a multiple of 256):
+        // they go to that rank's staging buffer, into the slice reserved for this rank
+        const int dest = (int)(row0 / a.dest_rows);
+        const int64_t srow = (int64_t)a.my_rank * a.dest_rows + (row0 - (int64_t)dest * a.dest_rows);
+        store_block_staged(a, &maps_peer.m[dest], acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, srow, a.map_rows,
+                           colw, alpha, num_k > 0, am);
+        continue;
+      }
       store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
                          t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
     }
@@ -981,7 +999,8 @@ static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3)
 
 template <int kFormat, int BN, int STAGES>
 static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& msa,
-                            const CUtensorMap& msb, const CUtensorMap& md, const GemmArgs& args, cudaStream_t st) {
+                            const CUtensorMap& msb, const CUtensorMap& md, const PeerMaps& mp, const GemmArgs& args,
+                            cudaStream_t st) {
   using Cfg = PairCfg<kFormat, BN, STAGES>;
   auto kern = gemm_blockscaled_pair_kernel<kFormat, BN, STAGES>;
   static int max_pairs_dev[MT_MAX_DEVICES] = {};   // 0 = not yet queried on that device
@@ -1002,7 +1021,7 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
     max_pairs = n;
   }
   const int pairs = std::min(args.num_tiles, std::max(1, max_pairs - (args.sm_margin + 1) / 2));
-  kern<<<2 * pairs, P_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, msa, msb, md, args);
+  kern<<<2 * pairs, P_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, msa, msb, md, mp, args);
   MT_CUDA(cudaGetLastError());
   return MT_OK;
 }
@@ -1027,7 +1046,7 @@ static int forced_pair_n() {
 static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows, int64_t a_ld_bytes, const uint8_t* b,
                            int64_t b_rows, int64_t b_ld_bytes, void* d, int d_dtype, int64_t d_rows, int64_t d_cols,
                            int64_t ldd, int accumulate, GemmArgs& args, cudaStream_t st, int64_t a_slabs = 1,
-                           int64_t b_slabs = 1) {
+                           int64_t b_slabs = 1, void* const* dest = nullptr) {
   static int band = -2;
   if (band == -2) band = env_knob("MT_GEMM_BAND", -1);
   args.band = band;
@@ -1063,8 +1082,23 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   static int allow_tma_store = -1;  // timing-knob builds only: MT_GEMM_TMA_STORE=0 forces the direct path
   if (allow_tma_store < 0) allow_tma_store = env_knob("MT_GEMM_TMA_STORE", 1);
   CUtensorMap md = ma;
+  PeerMaps scatter_maps;
+  const PeerMaps* peer_maps = nullptr;
+  if (args.n_dest > 1) {
+    // scattered output: one map per destination staging buffer, [d_rows, d_cols] bf16 with pitch d_cols
+    for (int r = 0; r < args.n_dest; ++r) {
+      rc = make_tensor_map_2d(&scatter_maps.m[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dest[r], (uint64_t)d_cols,
+                              (uint64_t)d_rows, (uint64_t)d_cols * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc != MT_OK) return rc;
+    }
+    for (int r = args.n_dest; r < MT_MAX_PEERS; ++r) scatter_maps.m[r] = scatter_maps.m[0];
+    peer_maps = &scatter_maps;
+    d = dest[args.my_rank];
+    ldd = d_cols;
+  }
   args.tma_store = (allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16)) ? allow_tma_store : 0;
   args.map_rows = d_rows;
+  if (args.n_dest > 1 && args.tma_store != 1) return fail(MT_ERR_INVALID_ARG, "scattered output needs the staged store path");
   if (args.tma_store) {
     const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     // box: 32 rows x 64 bytes (half of a warp's staging buffer), 64-byte swizzle
@@ -1072,11 +1106,13 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
                             d_dtype == MT_F32 ? 16 : 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != MT_OK) return rc;
   }
+  static PeerMaps no_peers{};
+  const PeerMaps& mp = peer_maps ? *peer_maps : no_peers;
   if (format == FMT_NVFP4)
-    return pbn == 192 ? launch_gemm_pair<FMT_NVFP4, 192, 5>(ma, mb, msa, msb, md, args, st)
-                      : launch_gemm_pair<FMT_NVFP4, 256, 5>(ma, mb, msa, msb, md, args, st);
-  return pbn == 192 ? launch_gemm_pair<FMT_MXFP8, 192, 5>(ma, mb, msa, msb, md, args, st)
-                    : launch_gemm_pair<FMT_MXFP8, 256, 5>(ma, mb, msa, msb, md, args, st);
+    return pbn == 192 ? launch_gemm_pair<FMT_NVFP4, 192, 5>(ma, mb, msa, msb, md, mp, args, st)
+                      : launch_gemm_pair<FMT_NVFP4, 256, 5>(ma, mb, msa, msb, md, mp, args, st);
+  return pbn == 192 ? launch_gemm_pair<FMT_MXFP8, 192, 5>(ma, mb, msa, msb, md, mp, args, st)
+                    : launch_gemm_pair<FMT_MXFP8, 256, 5>(ma, mb, msa, msb, md, mp, args, st);
 }
 
 // Timing-knob builds only: MT_GEMM_BLOCK_N = 128 or 256 overrides the single-CTA tile width.
@@ -1096,6 +1132,21 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   float* d_amax = opts ? opts->d_amax : nullptr;
   MT_REQUIRE(sm_margin >= 0 && sm_margin < 128, "%s: sm_margin %d is not a valid SM count", name, sm_margin);
   MT_REQUIRE(!(d_amax && accumulate), "%s: d_amax is not available together with accumulate", name);
+  const int n_dest = opts ? opts->n_dest : 0;
+  if (n_dest > 1) {
+    MT_REQUIRE(n_dest <= MT_MAX_PEERS && opts->my_rank >= 0 && opts->my_rank < n_dest,
+               "%s: scatter over %d ranks from rank %d is out of range", name, n_dest, opts->my_rank);
+    MT_REQUIRE(d_dtype == MT_BF16 && !accumulate && bias == nullptr && d_amax == nullptr,
+               "%s: a scattered output is bf16, without accumulate, bias or d_amax", name);
+    MT_REQUIRE(opts->dest_rows > 0 && opts->dest_rows % 256 == 0 && M == n_dest * opts->dest_rows && N % 8 == 0 && K > 0,
+               "%s: a scattered output needs M == n_dest * dest_rows, dest_rows %% 256 == 0, N %% 8 == 0 (M=%lld, N=%lld, "
+               "dest_rows=%lld)", name, (long long)M, (long long)N, (long long)opts->dest_rows);
+    MT_REQUIRE(pair_enabled() && M > G_BLOCK_M && N > 128, "%s: a scattered output needs N > 128", name);
+    for (int r = 0; r < n_dest; ++r)
+      MT_REQUIRE(opts->dest[r] != nullptr && aligned16(opts->dest[r]), "%s: destination %d is null or misaligned", name, r);
+    d = opts->dest[opts->my_rank];
+    ldd = N;
+  }
   MT_REQUIRE(a_slabs >= 1 && b_slabs >= 1, "%s: slab counts must be positive", name);
   MT_REQUIRE(d != nullptr, "%s: null output pointer", name);
   MT_REQUIRE(M >= 0 && N >= 0 && K >= 0, "%s: negative shape", name);
@@ -1144,6 +1195,7 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   args.mode = MODE_DENSE;
   args.sm_margin = sm_margin;
   args.d_amax = d_amax;
+  if (n_dest > 1) { args.n_dest = n_dest; args.my_rank = opts->my_rank; args.dest_rows = opts->dest_rows; }
   args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
   // K == 0 never reaches this point; tensor maps below need K_bytes >= 16
   if (pair_enabled() && M > G_BLOCK_M && N > 128) {
@@ -1155,7 +1207,7 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
     args.tiles_n = (int)((N + pbn - 1) / pbn);
     args.num_tiles = args.tiles_m * args.tiles_n;
     return launch_pair_any(format, pbn, a, M, K_bytes, b, N, K_bytes, d, d_dtype, M, N, ldd, accumulate, args, st, a_slabs,
-                           b_slabs);
+                           b_slabs, n_dest > 1 ? opts->dest : nullptr);
   }
   const int bn = pick_block_n(N);
   args.tiles_m = (int)((M + G_BLOCK_M - 1) / G_BLOCK_M);

@@ -41,7 +41,8 @@ enum DeviceStatusBits : int {
   DS_ACC_FULL_WAIT = 4,  // epilogue waited too long for the accumulator
   DS_ACC_EMPTY_WAIT = 8, // MMA issuer waited too long for the epilogue
   DS_QUANT_WAIT = 16,    // quantize kernel waited too long for its input tile
-  DS_BAD_PLAN = 32       // grouped plan: the offsets were not a valid partition of the rows
+  DS_BAD_PLAN = 32,      // grouped plan: the offsets were not a valid partition of the rows
+  DS_PEER_WAIT = 64      // a wait on another rank's flag expired
 };
 
 // 2-D tensor map over a row-major byte/bf16 matrix. dims/strides in elements of `dtype`.

@@ -65,9 +65,33 @@ def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True):
     return amax[0:1], (amax[1:2] if need_col else amax[0:1])
 
 
+def _out_bytes(into, key: str, shape, device) -> torch.Tensor:
+    """Output buffer `key`: a view of the caller's byte range when `into` names one (the shared
+    buffer of a peer all-gather), else a fresh tensor."""
+    n = 1
+    for d in shape:
+        n *= d
+    if into is not None and key in into:
+        buf = into[key]
+        assert buf.dtype == torch.uint8 and buf.is_contiguous() and buf.numel() >= n and buf.data_ptr() % 16 == 0
+        return buf[:n].view(*shape)
+    return torch.empty(shape, dtype=torch.uint8, device=device)
+
+
+def quantized_shard_bytes(fmt: str, rows: int, cols: int):
+    """Byte sizes of (codes, GEMM-layout scales, transposed codes, transposed GEMM-layout scales) of
+    a [rows, cols] tensor in format "nvfp4" or "mxfp8"."""
+    if fmt == "nvfp4":
+        return (rows * cols // 2, swizzled_scale_bytes(rows, cols // 16), cols * (rows // 2),
+                swizzled_scale_bytes(cols, (rows + 15) // 16))
+    return (rows * cols, swizzled_scale_bytes(rows, cols // 32), cols * rows, swizzled_scale_bytes(cols, (rows + 31) // 32))
+
+
 def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with_rht: bool = False,
                    return_transpose: bool = True, amax_row: Optional[torch.Tensor] = None,
-                   amax_col: Optional[torch.Tensor] = None) -> Quantized:
+                   amax_col: Optional[torch.Tensor] = None, into=None) -> Quantized:
+    """`into` (optional): dict of uint8 byte ranges for "q", "s_swz", "q_t", "s_t_swz" that the
+    kernel writes instead of fresh tensors."""
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     M, K = x.shape
@@ -81,15 +105,15 @@ def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with
     rows_s = (M + 15) // 16 * 16 if pad16 else M
     cols_s = (K + 15) // 16 * 16 if pad16 else K
     u8 = torch.uint8
-    q = torch.empty((M, K // 2), dtype=u8, device=dev)
+    q = _out_bytes(into, "q", (M, K // 2), dev)
     s = torch.empty((rows_s, K // 16), dtype=u8, device=dev)
-    s_swz = torch.empty(swizzled_scale_bytes(M, K // 16), dtype=u8, device=dev)
+    s_swz = _out_bytes(into, "s_swz", (swizzled_scale_bytes(M, K // 16),), dev)
     q_t = s_t = s_t_swz = None
     mb = (M + 15) // 16
     if return_transpose:
-        q_t = torch.empty((K, M // 2), dtype=u8, device=dev)
+        q_t = _out_bytes(into, "q_t", (K, M // 2), dev)
         s_t = torch.empty((cols_s, mb), dtype=u8, device=dev)
-        s_t_swz = torch.empty(swizzled_scale_bytes(K, mb), dtype=u8, device=dev)
+        s_t_swz = _out_bytes(into, "s_t_swz", (swizzled_scale_bytes(K, mb),), dev)
     _lib.call("mt_quantize_nvfp4", x.data_ptr(), M, K, flags, amax_row.data_ptr(), _ptr(amax_col),
               q.data_ptr(), s.data_ptr(), K // 16, s_swz.data_ptr(),
               _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
@@ -97,21 +121,21 @@ def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with
     return Quantized(q, s, s_swz, q_t, s_t, s_t_swz, amax_row, amax_col if return_transpose else amax_row)
 
 
-def quantize_mxfp8(x: torch.Tensor, *, return_transpose: bool = True) -> Quantized:
+def quantize_mxfp8(x: torch.Tensor, *, return_transpose: bool = True, into=None) -> Quantized:
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     M, K = x.shape
     dev = x.device
     u8 = torch.uint8
-    q = torch.empty((M, K), dtype=u8, device=dev)
+    q = _out_bytes(into, "q", (M, K), dev)
     s = torch.empty((M, K // 32), dtype=u8, device=dev)
-    s_swz = torch.empty(swizzled_scale_bytes(M, K // 32), dtype=u8, device=dev)
+    s_swz = _out_bytes(into, "s_swz", (swizzled_scale_bytes(M, K // 32),), dev)
     q_t = s_t = s_t_swz = None
     mb = (M + 31) // 32
     if return_transpose:
-        q_t = torch.empty((K, M), dtype=u8, device=dev)
+        q_t = _out_bytes(into, "q_t", (K, M), dev)
         s_t = torch.empty((K, mb), dtype=u8, device=dev)
-        s_t_swz = torch.empty(swizzled_scale_bytes(K, mb), dtype=u8, device=dev)
+        s_t_swz = _out_bytes(into, "s_t_swz", (swizzled_scale_bytes(K, mb),), dev)
     _lib.call("mt_quantize_mxfp8", x.data_ptr(), M, K, q.data_ptr(), s.data_ptr(), K // 32, s_swz.data_ptr(),
               _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
     _count(1 if x.numel() else 0)
@@ -138,7 +162,21 @@ def _out_dtype_code(dt: torch.dtype) -> int:
     raise _lib.MtError(f"GEMM output dtype {dt} is not supported (bf16 or fp32)")
 
 
+class _NoOutput:
+    """Stand-in output of a scattering GEMM (its rows go to the ranks' staging buffers)."""
+    @staticmethod
+    def data_ptr():
+        return None
+
+    @staticmethod
+    def stride(_):
+        return 0
+
+
 def _gemm_out(M, N, out_dtype, out, accumulate, device):
+    if _scattering():
+        assert out is None and not accumulate and out_dtype == torch.bfloat16
+        return _NoOutput()
     if out is None:
         if accumulate:
             raise _lib.MtError("accumulate=True needs an output tensor")
@@ -152,13 +190,17 @@ _GEMM_OPTS = threading.local()
 
 
 @contextlib.contextmanager
-def gemm_options(sm_margin: int = 0, d_amax: Optional[torch.Tensor] = None):
+def gemm_options(sm_margin: Optional[int] = None, d_amax: Optional[torch.Tensor] = None, scatter=None):
     """Per-call options of the GEMMs launched inside by this thread (mt_gemm_opts):
     sm_margin: SMs each launch leaves idle, so that a collective in flight on another stream
     runs beside it instead of behind it; d_amax: fp32 device scalar (zeroed by the caller) that
-    the GEMM raises to the largest |value| it stores."""
+    the GEMM raises to the largest |value| it stores; scatter = (addresses of the ranks' staging
+    buffers, this rank, rows per rank): the output rows go to the ranks' staging buffers instead
+    of an output tensor (the GEMM call then returns None)."""
     prev = getattr(_GEMM_OPTS, "value", None)
-    _GEMM_OPTS.value = (int(sm_margin), d_amax)
+    base = prev or (0, None, None)     # nested contexts inherit what they do not set
+    _GEMM_OPTS.value = (base[0] if sm_margin is None else int(sm_margin), base[1] if d_amax is None else d_amax,
+                        base[2] if scatter is None else scatter)
     try:
         yield
     finally:
@@ -171,12 +213,23 @@ def sm_margin(sms: int):
 
 def _opts():
     cur = getattr(_GEMM_OPTS, "value", None)
-    if cur is None or (cur[0] == 0 and cur[1] is None):
+    if cur is None or (cur[0] == 0 and cur[1] is None and cur[2] is None):
         return None
-    margin, amax = cur
+    margin, amax, scatter = cur
     if amax is not None:
         assert amax.dtype == torch.float32 and amax.is_cuda and amax.numel() == 1
-    return _lib.ctypes.byref(_lib.GemmOpts(margin, None if amax is None else amax.data_ptr()))
+    o = _lib.GemmOpts(margin, None if amax is None else amax.data_ptr())
+    if scatter is not None:
+        ptrs, me, rows = scatter
+        o.n_dest, o.my_rank, o.dest_rows = len(ptrs), int(me), int(rows)
+        for i, p_ in enumerate(ptrs):
+            o.dest[i] = p_
+    return _lib.ctypes.byref(o)
+
+
+def _scattering() -> bool:
+    cur = getattr(_GEMM_OPTS, "value", None)
+    return cur is not None and cur[2] is not None
 
 
 def _slabs(q):

@@ -27,7 +27,7 @@ from ..utils.utils import cast_if_needed, divide, init_method_constant, is_rank_
 
 logger = logging.getLogger(__name__)
 
-_NUM_FN_ARGS = 14
+_NUM_FN_ARGS = 15
 
 
 class _NonQuantizedLinear(torch.autograd.Function):
@@ -36,7 +36,7 @@ class _NonQuantizedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, x_meta, w, weight_qresult_cache, bias, sequence_parallel, tp_group, tp_size,
                 parallel_mode, qlinear_params, activation_dtype, is_grad_enabled, is_first_microbatch,
-                fuse_wgrad_accumulation):
+                fuse_wgrad_accumulation, ub=None):
         x_shape = x.shape
         x = cast_if_needed(x.reshape(-1, x_shape[-1]), activation_dtype)
         bias = cast_if_needed(bias, activation_dtype)
@@ -94,6 +94,56 @@ def _sm_margin(op, sms: int):
     return ctl(sms) if (ctl is not None and sms > 0) else contextlib.nullcontext()
 
 
+def _gemm_opts(op, **kw):
+    """Context with per-call GEMM options of the op's backend (ops without them: null context)."""
+    ctl = getattr(op, "gemm_options", None)
+    return ctl(**kw) if ctl is not None else contextlib.nullcontext()
+
+
+def _peer_groups(ub, tp_group, device):
+    """(peer group for gathers, peer group for reduce-scatters, buffer name, output meta) of a
+    layer: peer-memory exchange is used when the layer was built with ub_overlap_ag /
+    ub_overlap_rs and the group's ranks can share memory; otherwise None (process-group path)."""
+    if ub is None:
+        return None, None, "", None
+    overlap_rs, overlap_ag, name, out_meta = ub
+    pg = None
+    if (overlap_rs or overlap_ag) and tp_group is not None and get_distributed_world_size(tp_group) > 1 \
+            and _env_flag("MT_TP_PEER", True):
+        from ..distributed.peer import get_peer_group
+        pg = get_peer_group(tp_group, device)
+    return (pg if overlap_ag else None), (pg if overlap_rs else None), name or "ub", out_meta
+
+
+def _scatter_possible(pg, M, N, out_dtype, bias, world) -> bool:
+    """The GEMM can push its output rows to the owning ranks: bf16 rows in slices of whole
+    256-row tiles, a tile-kernel shape, and no bias inside the GEMM."""
+    return (pg is not None and out_dtype == torch.bfloat16 and bias is None and M % (256 * world) == 0
+            and N % 8 == 0 and N > 128 and M > 128)
+
+
+def _gemm_reduce_scatter(pg, gemm, M, N, site, out_meta=None, defer=False):
+    """Reduce-scatter of a GEMM's bf16 output along its rows, started by the GEMM itself:
+    its epilogue stores every tile into the owning rank's staging buffer while later tiles are
+    computed; after a barrier each rank sums the slices it received. With defer=True the
+    barrier and the sum are returned as a callable, to be run after more work is enqueued."""
+    from .. import kernels
+    world = pg.world
+    stage = pg.alternating(f"rs:{site}:{M}x{N}", M * N * 2)
+    with kernels.gemm_options(scatter=(stage.ptrs, pg.rank, M // world)):
+        gemm()
+
+    def finish():
+        pg.barrier()
+        amax = None
+        if out_meta is not None:
+            amax = torch.zeros(1, dtype=torch.float32, device=pg.device)
+            out_meta.amax = amax
+        return pg.reduce_bf16(stage, M // world, N, amax)
+
+    return finish if defer else finish()
+
+
 def _interleave_gathered_transpose(stacked: torch.Tensor, world: int) -> torch.Tensor:
     """[world * R, C_local] (rank-major stack of per-rank transposed shards) -> [R, world * C_local]."""
     r = stacked.shape[0] // world
@@ -110,7 +160,11 @@ class _QuantizedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, x_meta, w, weight_qresult_cache, bias, sequence_parallel, tp_group, tp_size,
                 parallel_mode, qlinear_params, activation_dtype, is_grad_enabled, is_first_microbatch,
-                fuse_wgrad_accumulation):
+                fuse_wgrad_accumulation, ub=None):
+        """ub: None, or (overlap_rs, overlap_ag, name, out_meta) from a layer built with the
+        userbuffer flags: the exchanges then run over peer memory (distributed/peer.py) where the
+        shapes allow, else over the process group. out_meta (a QuantizeInputMeta or None)
+        receives the abs-max of the output for the next layer's quantize."""
         op: quantization.QuantizeOpBase = qlinear_params.quantize_op
         assert op is not None, "QLinearParams.quantize_op is not set"
         x_shape = x.shape
@@ -119,13 +173,14 @@ class _QuantizedLinear(torch.autograd.Function):
         bias = cast_if_needed(bias, activation_dtype)
 
         gather_required = parallel_mode == "column" and sequence_parallel
+        pg_ag, pg_rs, site, out_meta = _peer_groups(ub, tp_group, x.device)
         # the gather (when there is one, in its copy-free form) is left in flight while the weight
         # is quantized below, and awaited just before the GEMM
         qres_x = _QuantizedLinear.quantize_optionally_allgather(
             op, x, qlinear_params.x_params, transpose_required=is_grad_enabled,
             allgather_required=gather_required, allgather_quantize=qlinear_params.allgather_quantize,
             tp_group=tp_group, keep_transpose_local=qlinear_params.memory_saving and gather_required,
-            weight_shape=tuple(w.shape), async_gather=True)
+            weight_shape=tuple(w.shape), async_gather=True, input_meta=x_meta, peer_group=pg_ag, site=f"{site}:x")
 
         # weights are re-quantized on the first microbatch (or when the caller gives no hint)
         if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
@@ -137,12 +192,29 @@ class _QuantizedLinear(torch.autograd.Function):
         for h in getattr(qres_x, "_pending_handles", ()):
             h.wait()
         x_t_handles = getattr(qres_x, "_pending_handles_t", ())
+        M, N = qres_x.data.shape[0], w.shape[0]
+        scatter = (parallel_mode == "row" and sequence_parallel and
+                   _scatter_possible(pg_rs, M, N, out_dtype, bias, get_distributed_world_size(tp_group)))
+        amax_y = None
+        if out_meta is not None and not scatter and (parallel_mode != "row" or tp_size == 1):
+            amax_y = torch.zeros(1, dtype=torch.float32, device=x.device)
+
+        def fprop():
+            return op.qgemm(qres_x.data, qres_w.data, qlinear_params.mm_fprop, out_dtype, qres_x.scale, qres_w.scale,
+                            bias, accumulate=False, global_amax_qx=qres_x.global_amax_row,
+                            global_amax_qw=qres_w.global_amax_row, qparams_x=qlinear_params.x_params,
+                            qparams_w=qlinear_params.w_params)
+
         # the gather of x^T (needed by wgrad only) may still be running: leave it SMs
         with _sm_margin(op, _overlap_sm_margin() if x_t_handles else 0):
-            y = op.qgemm(qres_x.data, qres_w.data, qlinear_params.mm_fprop, out_dtype, qres_x.scale, qres_w.scale,
-                         bias, accumulate=False, global_amax_qx=qres_x.global_amax_row,
-                         global_amax_qw=qres_w.global_amax_row, qparams_x=qlinear_params.x_params,
-                         qparams_w=qlinear_params.w_params)
+            if scatter:
+                y = _gemm_reduce_scatter(pg_rs, fprop, M, N, f"{site}:y", out_meta)
+            elif amax_y is not None:
+                with _gemm_opts(op, d_amax=amax_y):
+                    y = fprop()
+                out_meta.amax = amax_y
+            else:
+                y = fprop()
         if not is_grad_enabled:
             for h in x_t_handles:
                 h.wait()
@@ -157,6 +229,7 @@ class _QuantizedLinear(torch.autograd.Function):
             ctx.is_first_microbatch = is_first_microbatch
             ctx.fuse_wgrad_accumulation = fuse_wgrad_accumulation
             ctx.activation_dtype = activation_dtype
+            ctx.ub = ub
             ctx.x_t_is_local_shard = bool(getattr(qres_x, "_t_is_local_shard", False))
             ctx.x_t_handles = x_t_handles          # awaited in backward, before wgrad reads x^T
             ctx.x_t_sources = getattr(qres_x, "_pending_sources", None)
@@ -165,7 +238,9 @@ class _QuantizedLinear(torch.autograd.Function):
             ctx.save_for_backward(qres_x.data_t, qres_x.scale_t, qres_x.global_amax_col,
                                   qres_w.data_t, qres_w.scale_t, qres_w.global_amax_col, w)
 
-        if parallel_mode == "row" and sequence_parallel:
+        if scatter:
+            pass                                   # already reduced and scattered
+        elif parallel_mode == "row" and sequence_parallel:
             y, _ = reduce_scatter_along_first_dim(y, tp_group)
         elif parallel_mode == "row" and tp_size > 1:
             y, _ = allreduce(y, tp_group)
@@ -184,10 +259,11 @@ class _QuantizedLinear(torch.autograd.Function):
         b_grad = dy.sum(dim=0) if ctx.use_bias else None
 
         gather_required = ctx.parallel_mode == "row" and ctx.sequence_parallel
+        pg_ag, pg_rs, site, _ = _peer_groups(ctx.ub, ctx.tp_group, dy.device)
         qres_dy = _QuantizedLinear.quantize_optionally_allgather(
             op, dy, p.g_params, transpose_required=True, allgather_required=gather_required,
             allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group, weight_shape=tuple(w.shape),
-            async_gather=True)
+            async_gather=True, peer_group=pg_ag, site=f"{site}:dy")
         for h in getattr(qres_dy, "_pending_handles", ()):
             h.wait()
         dy_t_handles = getattr(qres_dy, "_pending_handles_t", ())
@@ -198,11 +274,25 @@ class _QuantizedLinear(torch.autograd.Function):
         if ctx.x_t_is_local_shard:
             pending_x_t = _QuantizedLinear._start_gather_transposed(qx_t, sx_t, ctx.tp_group)
 
+        M, N = qres_dy.data.shape[0], qw_t.shape[0]
+        scatter = (ctx.parallel_mode == "column" and ctx.sequence_parallel and
+                   _scatter_possible(pg_rs, M, N, out_dtype_dgrad, None, get_distributed_world_size(ctx.tp_group)))
+
+        def dgrad_gemm():
+            return op.qgemm(qres_dy.data, qw_t, p.mm_dgrad, out_dtype_dgrad, qres_dy.scale, sw_t, None, None,
+                            accumulate=False, global_amax_qx=qres_dy.global_amax_row, global_amax_qw=amax_w_col,
+                            qparams_x=p.g_params, qparams_w=p.w_params)
+
         # a gather of dy^T or of x^T (memory-saving mode) may be in flight: leave it SMs
+        finish_dgrad = None
         with _sm_margin(op, _overlap_sm_margin() if (dy_t_handles or pending_x_t is not None) else 0):
-            dgrad = op.qgemm(qres_dy.data, qw_t, p.mm_dgrad, out_dtype_dgrad, qres_dy.scale, sw_t, None, None,
-                             accumulate=False, global_amax_qx=qres_dy.global_amax_row, global_amax_qw=amax_w_col,
-                             qparams_x=p.g_params, qparams_w=p.w_params)
+            if scatter:
+                # the tiles travel to their owners while the GEMM runs; the barrier and the local
+                # sum wait until the wgrad GEMM has been enqueued behind it
+                finish_dgrad = _gemm_reduce_scatter(pg_rs, dgrad_gemm, M, N, f"{site}:dx", defer=True)
+                dgrad = None
+            else:
+                dgrad = dgrad_gemm()
         for h in tuple(dy_t_handles) + tuple(getattr(ctx, "x_t_handles", ())):
             h.wait()
 
@@ -210,7 +300,9 @@ class _QuantizedLinear(torch.autograd.Function):
             qx_t, sx_t = _QuantizedLinear._finish_gather_transposed(pending_x_t, ctx.tp_group)
 
         handle = None
-        if ctx.parallel_mode == "column" and ctx.sequence_parallel:
+        if scatter:
+            pass
+        elif ctx.parallel_mode == "column" and ctx.sequence_parallel:
             dgrad, handle = reduce_scatter_along_first_dim(dgrad, ctx.tp_group, True)
         elif ctx.parallel_mode == "column" and ctx.tp_size > 1:
             dgrad, handle = allreduce(dgrad, ctx.tp_group, True)
@@ -236,6 +328,8 @@ class _QuantizedLinear(torch.autograd.Function):
 
         if handle is not None:
             handle.wait()
+        if finish_dgrad is not None:
+            dgrad = finish_dgrad()
         dgrad = dgrad.view(-1, *ctx.x_shape[1:])
         return (dgrad, None, wgrad, None, b_grad) + (None,) * (_NUM_FN_ARGS - 5)
 
@@ -243,7 +337,7 @@ class _QuantizedLinear(torch.autograd.Function):
     @staticmethod
     def quantize_optionally_allgather(quantize_op, x, qparams, transpose_required, allgather_required,
                                       allgather_quantize, tp_group, keep_transpose_local=False, weight_shape=None,
-                                      async_gather=False):
+                                      async_gather=False, input_meta=None, peer_group=None, site="ub"):
         """Quantizes x, gathering it across the tensor-parallel group first (bf16) or after
         (quantized) when the layer is sequence-parallel.
 
@@ -255,7 +349,7 @@ class _QuantizedLinear(torch.autograd.Function):
         after the gather."""
         if not allgather_required:
             return quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=False,
-                                        tp_group=tp_group)
+                                        tp_group=tp_group, input_meta=input_meta)
         assert tp_group is not None
         if not (allgather_quantize and quantize_op.supports_allgather):
             x, _ = gather_along_first_dim(x, tp_group)
@@ -264,10 +358,15 @@ class _QuantizedLinear(torch.autograd.Function):
         world = get_distributed_world_size(tp_group)
         block = qparams.quant_tile_shape[1] if qparams.quant_tile_shape else 32
         assert x.shape[0] % block == 0, "token shard must be a multiple of the quantization block"
-        r = quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=True,
-                                 tp_group=tp_group)
         rows = x.shape[0]
         gather_t = transpose_required and not keep_transpose_local
+        fmt = getattr(quantize_op, "format_name", None)
+        if (peer_group is not None and fmt is not None and weight_shape is not None and min(weight_shape) > 128
+                and _QuantizedLinear._gemm_ready_shapes(fmt, rows, x.shape[1], world, transpose_required)):
+            return _QuantizedLinear._peer_gather_gemm_ready(peer_group, quantize_op, fmt, x, qparams, tp_group,
+                                                            gather_t, transpose_required, input_meta, site)
+        r = quantize_op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=True,
+                                 tp_group=tp_group, input_meta=input_meta)
         if (weight_shape is not None and min(weight_shape) > 128
                 and _QuantizedLinear._gemm_ready_gather_possible(r, rows, x.shape[1], world, transpose_required)):
             return _QuantizedLinear._gather_gemm_ready(r, tp_group, gather_t, transpose_required, async_gather)
@@ -281,6 +380,68 @@ class _QuantizedLinear(torch.autograd.Function):
             out.scale_t = _interleave_gathered_transpose(g[3], world)
         elif transpose_required:
             out.data_t, out.scale_t = r.data_t, r.scale_t[: x.shape[1]]
+            out._t_is_local_shard = True
+        return out
+
+    @staticmethod
+    def _gemm_ready_shapes(fmt, rows, features, world, transpose_required):
+        """Shape rules of the copy-free gather, known before anything is quantized: shards of
+        whole 128-row scale chunks, K slabs of whole 128-byte K steps for the transposed copy
+        (2 codes per byte in NVFP4), GEMM shapes the CTA-pair kernel takes."""
+        if rows % 128 or rows * world <= 128 or features <= 128 or features % 128:
+            return False
+        t_row_bytes = rows // 2 if fmt == "nvfp4" else rows
+        return not (transpose_required and t_row_bytes % 128)
+
+    @staticmethod
+    def _peer_gather_gemm_ready(pg, op, fmt, x, qparams, tp_group, gather_t, transpose_required, input_meta, site):
+        """The copy-free quantized gather over peer memory: this rank's shard is quantized
+        straight into its slot of a buffer every rank has mapped (with the abs-max MAX-reduced by
+        a one-warp exchange first, where the format has one); after a barrier one copy kernel
+        pulls the other ranks' row-wise codes and scales, and a second one, on a side stream,
+        the transposed copies that only the wgrad GEMM needs."""
+        from .. import kernels
+        world, (rows, cols) = pg.world, x.shape
+        sizes = kernels.quantized_shard_bytes(fmt, rows, cols)
+        offs, total = [], 0
+        for n in sizes:
+            offs.append(total)
+            total += (n + 255) // 256 * 256
+        shared = pg.alternating(f"ag:{site}:{fmt}:{rows}x{cols}", total)
+        keys = ("q", "s_swz", "q_t", "s_t_swz")
+        into = {k: shared.tensor[o:o + n] for k, o, n in zip(keys, offs, sizes) if transpose_required or k in keys[:2]}
+        meta = quantization.QuantizeInputMeta(
+            amax=getattr(input_meta, "amax", None), amax_col=getattr(input_meta, "amax_col", None), into=into,
+            amax_reduce=pg.allreduce_max_)
+        r = op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=True, tp_group=tp_group,
+                        input_meta=meta)
+        pg.barrier()
+        dev, u8 = x.device, torch.uint8
+        data = torch.empty((world * rows, sizes[0] // rows), dtype=u8, device=dev)
+        scale = torch.empty(world * sizes[1], dtype=u8, device=dev)
+        pg.gather(shared, [(offs[0], data, sizes[0]), (offs[1], scale, sizes[1])])
+        if r.data.dtype != u8:
+            data = data.view(r.data.dtype)
+        scale._mt_swz = scale
+        out = quantization.QuantizeResult(data, scale, None, None, r.global_amax_row, r.global_amax_col, scale, None)
+        out._pending_handles = ()
+        out._pending_handles_t = ()
+        if gather_t:
+            data_t = torch.empty((world, cols, sizes[2] // cols), dtype=u8, device=dev)
+            scale_t = torch.empty(world * sizes[3], dtype=u8, device=dev)
+            segs = [(offs[2], data_t, sizes[2]), (offs[3], scale_t, sizes[3])]
+            ctas = max(8, _overlap_sm_margin())
+            out._pending_handles_t = (pg.on_side_stream(lambda: pg.gather(shared, segs, ctas=ctas), keep=(data_t, scale_t)),)
+            if r.data_t.dtype != u8:
+                data_t = data_t.view(r.data_t.dtype)
+            scale_t._mt_swz = scale_t
+            out.data_t, out.scale_t, out.scale_t_swz = data_t, scale_t, scale_t
+        elif transpose_required:
+            # memory-saving mode keeps this rank's shard of x^T until backward: out of the slot,
+            # which later gathers rewrite
+            s_t = r.scale_t.clone()
+            s_t._mt_swz = r.scale_t_swz.clone()
+            out.data_t, out.scale_t, out.scale_t_swz = r.data_t.clone(), s_t, s_t._mt_swz
             out._t_is_local_shard = True
         return out
 
@@ -422,9 +583,16 @@ class Linear(LayerLinearBaseModule):
         self.use_bias, self.return_bias = bias, return_bias
         self.apply_bias = bias and not return_bias
         self.ub_overlap_rs, self.ub_overlap_ag = ub_overlap_rs, ub_overlap_ag
+        # ub_overlap_rs: the reduce-scatter after a row-parallel GEMM (and after the dgrad GEMM of a
+        # column-parallel layer) is done by the GEMM's own epilogue over NVLink peer memory;
+        # ub_overlap_ag: quantized activations are gathered by peer copies (distributed/peer.py)
         if ub_overlap_rs or ub_overlap_ag:
             assert ub_name is not None, "Userbuffer name [string] is not set."
         self.ub_name = self.layer_name = ub_name
+        # emit_output_amax: the forward GEMM (or the reduce step after it) also computes max |y|;
+        # `output_meta` then holds it for the next layer's `inp_meta` (no abs-max pass over y)
+        self.emit_output_amax = False
+        self.output_meta: Optional[quantization.QuantizeInputMeta] = None
         self.get_rng_state_tracker, self.rng_tracker_name = get_rng_state_tracker, rng_tracker_name
         self.layer_number = layer_number
         self.qlinear_params = self.set_qlinear_params(qlinear_params=qlinear_params, layer_number=layer_number,
@@ -524,6 +692,11 @@ class Linear(LayerLinearBaseModule):
                  bias if self.apply_bias and not self.gemm_bias_unfused_add else None,
                  self.sequence_parallel, self.tp_group, self.tp_size, self.parallel_mode, self.qlinear_params,
                  self.activation_dtype, grad, is_first_microbatch, self.fuse_wgrad_accumulation]
+        self.output_meta = quantization.QuantizeInputMeta() if self.emit_output_amax else None
+        ub = None
+        if self.ub_overlap_rs or self.ub_overlap_ag or self.output_meta is not None:
+            ub = (self.ub_overlap_rs, self.ub_overlap_ag, self.ub_name, self.output_meta)
+        args.append(ub)
         out = (fn.apply if grad else fn.forward)(*args)
         if self.gemm_bias_unfused_add:
             out = out + cast_if_needed(bias, self.activation_dtype)

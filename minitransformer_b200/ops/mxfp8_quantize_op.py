@@ -17,6 +17,8 @@ mxfp8_scale_t = torch.uint8  # E8M0 byte = exponent + 127
 
 
 class Mxfp8QuantizeOp(Q.QuantizeOpBase):
+    format_name = "mxfp8"
+
     @property
     def supports_allgather(self) -> bool:
         return True  # no per-tensor scale: shards quantize independently
@@ -24,7 +26,7 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
     def quantize(self, x, qparams, return_transpose=False, reduce_amax=False, tp_group=None, input_meta=None):
         assert qparams.quant_tile_shape in (None, (1, 32)), "MXFP8 uses 1x32 tiles"
         x = _as_2d_bf16(x)
-        r = kernels.quantize_mxfp8(x, return_transpose=return_transpose)
+        r = kernels.quantize_mxfp8(x, return_transpose=return_transpose, into=getattr(input_meta, "into", None))
         r.scale._mt_swz = r.scale_swz
         data_t = None
         if return_transpose:
@@ -36,6 +38,10 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
     def sm_margin(self, sms: int):
         """Context in which this op's GEMMs leave `sms` SMs idle (for a collective in flight)."""
         return kernels.sm_margin(sms)
+
+    def gemm_options(self, **kw):
+        """Context with per-call options of this op's GEMMs (kernels.gemm_options)."""
+        return kernels.gemm_options(**kw)
 
     def qgemm(self, qx, qw, m_params, out_dtype, sx, sw, bias=None, out=None, accumulate=False,
               global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):

@@ -37,6 +37,8 @@ def _swizzled(scale: torch.Tensor, rows: int) -> torch.Tensor:
 
 
 class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
+    format_name = "nvfp4"
+
     @property
     def supports_allgather(self) -> bool:
         # Row-wise 1x16 blocks never cross a token shard, so quantizing shards with the
@@ -49,13 +51,26 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
         assert not qparams.pow_2_scales, "NVFP4 block scales are E4M3, not powers of two"
         x = _as_2d_bf16(x)
         rht = bool(qparams.with_rht) and return_transpose
-        amax_row, amax_col = kernels.amax_bf16(x, with_rht=rht, need_col=return_transpose)
+        known = getattr(input_meta, "amax", None)
+        known_col = getattr(input_meta, "amax_col", None)
+        if known is not None and (not rht or known_col is not None):
+            # the producer already knows max |x|: no abs-max pass over x
+            assert known.numel() == 1 and known.dtype == torch.float32
+            both = torch.cat([known.reshape(1), (known_col if rht else known).reshape(1)])
+            amax_row, amax_col = both[0:1], both[1:2]
+        else:
+            amax_row, amax_col = kernels.amax_bf16(x, with_rht=rht, need_col=return_transpose)
         if reduce_amax:
-            # both scalars live in one 2-element buffer: one tiny collective
-            allreduce_max_(amax_row._base if amax_row._base is not None else amax_row, tp_group)
+            # both scalars live in one 2-element buffer: one tiny exchange
+            both = amax_row._base if amax_row._base is not None else amax_row
+            reduce = getattr(input_meta, "amax_reduce", None)
+            if reduce is not None:
+                reduce(both)
+            else:
+                allreduce_max_(both, tp_group)
         r = kernels.quantize_nvfp4(x, tile=qparams.quant_tile_shape, with_2d=qparams.with_2d_quantization,
                                    with_rht=rht, return_transpose=return_transpose,
-                                   amax_row=amax_row, amax_col=amax_col)
+                                   amax_row=amax_row, amax_col=amax_col, into=getattr(input_meta, "into", None))
         scale = r.scale.view(nvfp4_scale_t)
         scale._mt_swz = r.scale_swz
         scale_t = None
@@ -68,6 +83,10 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
     def sm_margin(self, sms: int):
         """Context in which this op's GEMMs leave `sms` SMs idle (for a collective in flight)."""
         return kernels.sm_margin(sms)
+
+    def gemm_options(self, **kw):
+        """Context with per-call options of this op's GEMMs (kernels.gemm_options)."""
+        return kernels.gemm_options(**kw)
 
     def qgemm(self, qx, qw, m_params, out_dtype, sx, sw, bias=None, out=None, accumulate=False,
               global_amax_qx=None, global_amax_qw=None, qparams_x=None, qparams_w=None):

@@ -80,6 +80,23 @@ class QuantizeInputMetaBase:
     amax: Optional[torch.Tensor] = None
 
 
+@dataclasses.dataclass
+class QuantizeInputMeta(QuantizeInputMetaBase):
+    """What the sm_100a backends take through the `input_meta` hook:
+    amax: fp32 device scalar, max |x| of exactly the tensor being quantized, computed by its
+        producer (a GEMM with mt_gemm_opts.d_amax, or the reduce step of a fused reduce-scatter);
+        the quantizer then skips its own abs-max pass where that is all it needs (NVFP4 without
+        the Hadamard transform). amax_col: the abs-max of the transformed transposed copy, when
+        the producer knows it too.
+    into: byte ranges ("q", "s_swz", "q_t", "s_t_swz") the outputs are written into instead of
+        fresh tensors (a rank's slot of a peer all-gather buffer).
+    amax_reduce: callable that MAX-reduces the 2-element abs-max buffer across the ranks in
+        place, used instead of the process-group all-reduce when reduce_amax is set."""
+    amax_col: Optional[torch.Tensor] = None
+    into: Optional[dict] = None
+    amax_reduce: Optional[object] = None
+
+
 class QuantizeOpBase:
     """Interface of a quantize + GEMM backend."""
 

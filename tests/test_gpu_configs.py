@@ -114,3 +114,60 @@ def test_config5_small_llama_style_step_mxfp8_vs_bf16():
     cos = float(torch.nn.functional.cosine_similarity(grads[0], grads[1], dim=0))
     assert cos > 0.97, cos
     assert K.read_device_status() == 0
+
+
+def _check_linear_slices(name, x, w, dy, y, dx, dw):
+    """One Linear of the decoder at size against the MXFP8 oracle, on slices small enough for
+    numpy: y on a token x feature block (row-wise copies of x and w), dx on a token x input
+    block (row-wise dy, transposed copy of w), dw on a feature x input block (transposed copies
+    of dy and x over ALL tokens). Blocks of the transposed copies run along the sliced-away
+    dimension, so quantizing the slice gives exactly the rows of the full copy."""
+    f32 = lambda t: t.detach().float().cpu().numpy()
+    T, Kd = x.shape
+    N = w.shape[0]
+    r0, n0, k0 = T // 2 - 64, min(N - 128, 3 * 128), Kd // 2
+    rs, ns, ks = slice(r0, r0 + 128), slice(n0, n0 + 128), slice(k0, k0 + 128)
+    qx = mxfp8.quantize(f32(x[rs]), return_transpose=False)
+    qw = mxfp8.quantize(f32(w[ns]), return_transpose=False)
+    ref_y = gemm.qgemm_mxfp8(qx["data"], qx["scale"], qw["data"], qw["scale"], fused=True)
+    assert gemm.rel_frobenius(f32(y[rs, ns]), ref_y) <= 1e-3, (name, "y")
+    qg = mxfp8.quantize(f32(dy[rs]), return_transpose=False)
+    qwt = mxfp8.quantize(f32(w[:, ks]), return_transpose=True)
+    ref_dx = gemm.qgemm_mxfp8(qg["data"], qg["scale"], qwt["data_t"], qwt["scale_t"], fused=True)
+    assert gemm.rel_frobenius(f32(dx[rs, ks]), ref_dx) <= 1e-3, (name, "dx")
+    qgt = mxfp8.quantize(f32(dy[:, ns]), return_transpose=True)
+    qxt = mxfp8.quantize(f32(x[:, ks]), return_transpose=True)
+    ref_dw = gemm.qgemm_mxfp8(qgt["data_t"], qgt["scale_t"], qxt["data_t"], qxt["scale_t"], out_bf16=True, fused=True)
+    assert gemm.rel_frobenius(f32(dw[ns, ks]), ref_dw) <= 1e-3, (name, "dw")
+
+
+def test_config5_one_layer_at_size_every_linear_against_oracle():
+    """One decoder layer of configuration 5 at full width (hidden 4096, 32 heads / 8 KV heads,
+    gated ffn 14336, seq 4096 x micro-batch 2 = 8192 tokens, MXFP8 recipe): the inputs and
+    gradients each of the four Linears saw in the step are captured with hooks and every Linear's
+    output, input gradient and weight gradient are compared with the oracle on slices."""
+    torch.manual_seed(1)
+    qp = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    blk = _Block(4096, 32, 8, 14336, qp)
+    seen = {}
+
+    def watch(name, mod):
+        def hook(m, inp, out):
+            rec = seen.setdefault(name, {})
+            rec["x"], rec["y"] = inp[0].detach(), out.detach()
+            inp[0].register_hook(lambda g: rec.__setitem__("dx", g.detach()))
+            out.register_hook(lambda g: rec.__setitem__("dy", g.detach()))
+        mod.register_forward_hook(hook)
+
+    for name in ("qkv", "proj", "fc1", "fc2"):
+        watch(name, getattr(blk, name))
+    x = torch.randn(2, 4096, 4096, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    out = blk(x)
+    out.backward((torch.randn_like(out.float()) * 1e-3).to(torch.bfloat16))
+    torch.cuda.synchronize()
+    for name in ("qkv", "proj", "fc1", "fc2"):
+        rec, lin = seen[name], getattr(blk, name)
+        flat = lambda t: t.reshape(-1, t.shape[-1])
+        _check_linear_slices(name, flat(rec["x"]), lin.weight.detach(), flat(rec["dy"]), flat(rec["y"]),
+                             flat(rec["dx"]), lin.weight.grad)
+    assert K.read_device_status() == 0

@@ -240,3 +240,69 @@ def test_grouped_linear_full_size_spot_checks():
         err = float((y[r0:r1].float() - ref.float()).norm() / ref.float().norm())
         assert err <= TOL, (g, err)
     assert K.read_device_status() == 0
+
+
+def test_grouped_linear_full_size_module_against_oracle():
+    """Configuration 3 at size through the GroupedLinear module (128 experts, 131072 rows, seeded
+    Zipf(1.1) sizes, hidden 2048 -> ffn 768; one expert forced to a single row and one to none):
+    forward output, input gradient and weight gradient of a large expert, the one-row expert, the
+    empty expert and the last expert against the oracle run on that expert's slice alone."""
+    G, R, Kd, N = 128, 131072, 2048, 768
+    rng = np.random.default_rng(1234)
+    p = 1.0 / np.arange(1, G + 1) ** 1.1
+    m = np.bincount(rng.choice(G, size=R, p=p / p.sum()), minlength=G)
+    m[0] += m[40] - 1 + m[41]           # expert 40 keeps one row, expert 41 none; expert 0 takes the rest
+    m[40], m[41] = 1, 0
+    m_splits = m.tolist()
+    assert sum(m_splits) == R and m_splits[127] > 0
+    tx, x = seeded_bf16((R, Kd), 71)
+    tdy, dy = seeded_bf16((R, N), 72, 1e-3)
+    gen = torch.Generator().manual_seed(73)
+    w_all = (torch.randn(G, N, Kd, generator=gen) * 0.02).to(torch.bfloat16)
+    params = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    gl = GroupedLinear(G, Kd, N, bias=False, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params,
+                       fuse_wgrad_accumulation=True)
+    block = torch.full((G, N, Kd), 3.0, dtype=torch.float32, device="cuda")   # stale values must be overwritten
+    with torch.no_grad():
+        for g in range(G):
+            getattr(gl, f"weight{g}").copy_(w_all[g])
+            getattr(gl, f"weight{g}").main_grad = block[g]
+    xd = tx.cuda().requires_grad_(True)
+    y = gl(xd, m_splits, is_first_microbatch=True)
+    y.backward(tdy.cuda())
+    torch.cuda.synchronize()
+    off = np.concatenate([[0], np.cumsum(m_splits)])
+    for g in (1, 40, 41, 127):
+        r0, r1 = int(off[g]), int(off[g + 1])
+        dw = block[g]
+        if r1 == r0:
+            assert float(dw.abs().max()) == 0.0
+            continue
+        ref = oracle_linear.mxfp8_linear_fwd_bwd(x[r0:r1], w_all[g].float().numpy(), dy[r0:r1], fused=True)
+        assert _relf(y[r0:r1], ref["y"]) <= TOL, g
+        assert _relf(xd.grad[r0:r1], ref["dx"]) <= TOL, g
+        assert _relf(dw, ref["dw"]) <= TOL, g
+    assert K.read_device_status() == 0
+
+
+def test_grouped_plan_rejects_bad_offsets_without_touching_outputs():
+    """Offsets that do not partition [0, rows) leave an empty plan: the grouped GEMM computes
+    nothing and the device status word carries the bad-plan bit (32)."""
+    from minitransformer_b200 import _lib
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    G, R, Kd, N = 3, 384, 128, 256
+    off = torch.tensor([0, 200, 100, 384], dtype=torch.int64, device="cuda")     # not monotonic
+    plan = torch.zeros(int(lib.mt_grouped_plan_bytes(R, G)), dtype=torch.uint8, device="cuda")
+    _lib.check(lib.mt_grouped_plan_build(off.data_ptr(), G, R, plan.data_ptr(), plan.numel(), st), "plan")
+    x = torch.randn(R, Kd, device="cuda").to(torch.bfloat16)
+    w = torch.randn(G * N, Kd, device="cuda").to(torch.bfloat16)
+    qx, qw = K.quantize_mxfp8(x, return_transpose=False), K.quantize_mxfp8(w, return_transpose=False)
+    out = torch.full((R, N), 5.0, dtype=torch.bfloat16, device="cuda")
+    _lib.check(lib.mt_grouped_gemm_mxfp8(qx.data.data_ptr(), qx.scale_swz.data_ptr(), qw.data.data_ptr(),
+                                         qw.scale_swz.data_ptr(), G * N, Kd, plan.data_ptr(), G, R, N, Kd, N, 0,
+                                         out.data_ptr(), _lib.MT_BF16, N, st), "gemm")
+    torch.cuda.synchronize()
+    assert float((out.float() - 5.0).abs().max()) == 0.0
+    assert K.read_device_status() == 32
+    assert K.read_device_status() == 0
