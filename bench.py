@@ -324,18 +324,33 @@ def _other_configs_single_gpu(torch, dev, steps=5, warmup=3):
     xg = torch.randn(R, H, generator=gen).to(torch.bfloat16).to(dev)
     dyg = (torch.randn(R, H, generator=gen) * 1e-3).to(torch.bfloat16).to(dev)
 
-    def moe_step():
-        for m in (fc1, fc2):
-            for prm in m.parameters():
-                prm.grad = None
+    def moe_step(first=True):
+        if not fused:
+            for m in (fc1, fc2):
+                for prm in m.parameters():
+                    prm.grad = None
         xd = xg.detach().requires_grad_(True)
-        y = fc2(fc1(xd, m_splits, is_first_microbatch=True), m_splits, is_first_microbatch=True)
+        y = fc2(fc1(xd, m_splits, is_first_microbatch=first), m_splits, is_first_microbatch=first)
         y.backward(dyg)
 
     ms = _timed_loop(torch, moe_step, steps, warmup)
+    # later microbatches of a step: quantized expert weights kept, wgrad accumulated into main_grad
+    ms_steady = _timed_loop(torch, lambda: moe_step(False), steps, 1)
+    # host time to enqueue one step (the GPU still busy with earlier ones)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        moe_step()
+    host_ms = (time.perf_counter() - t0) / 3 * 1e3
+    torch.cuda.synchronize()
     flops = 6 * 2.0 * R * H * Fd
+    q_bytes = (2 * R * (H + Fd) + 2 * 2 * G * H * Fd) * 4.0625   # x, h, dy, dh and both weight blocks, row + transposed
     out["mxfp8_grouped_linear_fwd_bwd"] = {
         "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms,
+        "steady_microbatch_weights_cached": {"value": flops / (ms_steady * 1e-3) / 1e12, "ms_per_step": ms_steady},
+        "host_enqueue_ms_per_step": host_ms,
+        "frac_of_nominal_4500": flops / (ms * 1e-3) / 1e12 / 4500.0,
+        "quantize_algorithmic_bytes_per_step": q_bytes,
         "workload": f"GroupedLinear fc1+fc2 fwd+bwd, {G} experts, {R} rows (Zipf 1.1 sizes), hidden {H}, ffn {Fd}"}
     return out
 
@@ -462,6 +477,152 @@ def tp_parity_check(group, T=2048, H=1024, Fd=4096, recipe="fp4_subchannel_scali
             "shape": {"tokens": T, "hidden": H, "ffn": Fd}, "recipe": recipe, "memory_saving_checked": True,
             "exchange": "peer memory (own kernels)" if pg is not None else "process group (NCCL)",
             "rank_errors": errs if rank == 0 else None}
+
+
+# ---------------------------------------------------------------------------------------------
+# Configuration 5: Llama-style decoder step with every Linear swapped for the drop-in module
+# ---------------------------------------------------------------------------------------------
+C5 = dict(layers=8, hidden=4096, heads=32, kv_heads=8, ffn=14336, vocab=32000, seq=4096, micro_batch=2)
+
+
+def build_llama_decoder(torch, dims, params, tp_group=None, peer=True, device="cuda"):
+    """Llama-style decoder (RMSNorm, grouped-query attention through torch SDPA, gated SiLU MLP)
+    whose linears are the drop-in Linear under `params`. With a tensor-parallel group: Megatron
+    layout with sequence parallelism (qkv and the gated fc1 column-parallel with their heads /
+    ffn columns sharded, proj and fc2 row-parallel, token-sharded activations between blocks, a
+    vocabulary-parallel head and loss). Input ids [micro_batch, seq]; returns the mean loss."""
+    import torch.distributed as dist
+    from minitransformer_b200.module.linear import Linear
+    tp = dist.get_world_size(tp_group) if tp_group is not None else 1
+    rank = dist.get_rank(tp_group) if tp_group is not None else 0
+    H, heads, kvh, ffn, vocab = dims["hidden"], dims["heads"], dims["kv_heads"], dims["ffn"], dims["vocab"]
+    hd = H // heads
+    assert heads % tp == 0 and kvh % tp == 0 and ffn % tp == 0 and vocab % tp == 0
+    init = lambda t: torch.nn.init.normal_(t, std=0.02)
+
+    def lin(i, o, mode, name):
+        kw = dict(bias=False, params_dtype=torch.bfloat16, device=device, qlinear_params=params, init_method=init)
+        if tp > 1:
+            kw.update(parallel_mode=mode, sequence_parallel=True, tp_group=tp_group, ub_overlap_ag=peer,
+                      ub_overlap_rs=peer, ub_name=name)
+        return Linear(i, o, **kw)
+
+    class RMSNorm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.ones(H, dtype=torch.bfloat16, device=device))
+
+        def forward(self, x):
+            v = x.float()
+            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5)).to(x.dtype) * self.weight
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm1, self.norm2 = RMSNorm(), RMSNorm()
+            self.qkv = lin(H, (heads + 2 * kvh) * hd, "column", "qkv")   # this rank: its heads' [q | k | v]
+            self.proj = lin(H, H, "row", "proj")
+            self.fc1 = lin(H, 2 * ffn, "column", "fc1")                   # this rank: [gate shard | up shard]
+            self.fc2 = lin(ffn, H, "row", "fc2")
+
+        def forward(self, x, B, S):                                       # x [B*S / tp, H] (token shard)
+            nh, nkv = heads // tp, kvh // tp
+            qkv = self.qkv(self.norm1(x))                                 # [B*S, (nh + 2 nkv) hd]
+            q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+            q = q.view(B, S, nh, hd).transpose(1, 2)
+            k = k.view(B, S, nkv, hd).transpose(1, 2).repeat_interleave(nh // nkv, 1)
+            v = v.view(B, S, nkv, hd).transpose(1, 2).repeat_interleave(nh // nkv, 1)
+            a = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = x + self.proj(a.transpose(1, 2).reshape(B * S, nh * hd))
+            g, u = self.fc1(self.norm2(x)).chunk(2, dim=-1)
+            return x + self.fc2(torch.nn.functional.silu(g) * u)
+
+    class Decoder(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(vocab, H, dtype=torch.bfloat16, device=device)
+            self.blocks = torch.nn.ModuleList([Block() for _ in range(dims["layers"])])
+            self.norm = RMSNorm()
+            self.head = lin(H, vocab, "column", "head")
+
+        def forward(self, ids, targets):
+            B, S = ids.shape
+            x = self.emb(ids).view(B * S, H)
+            if tp > 1:
+                x = x.chunk(tp, 0)[rank]
+            for b in self.blocks:
+                x = b(x, B, S)
+            logits = self.head(self.norm(x)).float()                      # [B*S, vocab / tp]
+            t = targets.view(-1)
+            if tp == 1:
+                return torch.nn.functional.cross_entropy(logits, t)
+            # vocabulary-parallel cross entropy
+            import torch.distributed.nn.functional as dfn
+            vs = vocab // tp
+            m = logits.max(dim=-1).values.detach()
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=tp_group)
+            z = dfn.all_reduce((logits - m[:, None]).exp().sum(-1), group=tp_group)
+            local = (t >= rank * vs) & (t < (rank + 1) * vs)
+            idx = (t - rank * vs).clamp(0, vs - 1)
+            picked = torch.where(local, logits.gather(1, idx[:, None])[:, 0] - m, torch.zeros_like(m))
+            picked = dfn.all_reduce(picked, group=tp_group)
+            return (z.log() - picked).mean()
+
+    return Decoder()
+
+
+def llama_linear_flops(dims, with_head=True):
+    """GEMM flops of one forward + backward step: 2 M N K per GEMM, three GEMMs per Linear."""
+    T, H, hd = dims["seq"] * dims["micro_batch"], dims["hidden"], dims["hidden"] // dims["heads"]
+    per_layer = (dims["heads"] + 2 * dims["kv_heads"]) * hd + H + 2 * dims["ffn"]
+    f = 3 * 2.0 * T * H * per_layer * dims["layers"] + 3 * 2.0 * T * H * dims["ffn"] * dims["layers"]
+    return f + (3 * 2.0 * T * H * dims["vocab"] if with_head else 0.0)
+
+
+def _llama_step_bench(torch, dims, tp_group, dev, steps=3, warmup=2, peer=True):
+    """Times forward + backward of the decoder (MXFP8 recipe); returns the `other_configs` entry."""
+    import torch.distributed as dist
+    from minitransformer_b200.module import config as mt_config
+    params = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.MXFP8_SUB_CHANNEL)
+    n = dist.get_world_size(tp_group) if tp_group is not None else 1
+    torch.manual_seed(1234)
+    model = build_llama_decoder(torch, dims, params, tp_group, peer=peer, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(77)
+    ids = torch.randint(0, dims["vocab"], (dims["micro_batch"], dims["seq"]), generator=g).to(dev)
+    tgt = torch.randint(0, dims["vocab"], (dims["micro_batch"], dims["seq"]), generator=g).to(dev)
+    loss = None
+
+    def step():
+        nonlocal loss
+        for p_ in model.parameters():
+            p_.grad = None
+        loss = model(ids, tgt)
+        # every rank holds the same loss; the autograd-aware all-reduces of the vocabulary-parallel
+        # loss sum the ranks' gradients, so each rank back-propagates its 1/n share
+        (loss / n).backward()
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if tp_group is not None:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    if tp_group is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=tp_group)
+    ms = float(ms.item())
+    flops = llama_linear_flops(dims)
+    return {"ms_per_step": ms, "linear_tflops_per_gpu": flops / n / (ms * 1e-3) / 1e12, "unit": UNIT,
+            "linear_flops_per_step": flops, "loss": float(loss.item()), "steps": steps, "tp": n,
+            "workload": (f"{dims['layers']}-layer Llama-style decoder fwd+bwd, MXFP8 recipe on every Linear (LM head "
+                         f"included), hidden {dims['hidden']}, {dims['heads']} heads / {dims['kv_heads']} KV heads, "
+                         f"ffn {dims['ffn']}, vocab {dims['vocab']}, seq {dims['seq']} x micro-batch "
+                         f"{dims['micro_batch']}, torch SDPA, sequence-parallel TP={n}, random-init weights, uniform ids")}
 
 
 def run_gpu_arm(args):
@@ -705,6 +866,13 @@ def run_gpu_arm(args):
     q_ms = [a.elapsed_time(b) for a, b in quant_ms[-args.steps:]] if n == 1 else []
     e2e_ms, _ = run_timed(e2e_step, max(2, min(args.steps, 10)), 2)
 
+    c5 = None
+    if n > 1 and all(C5[k] % n == 0 for k in ("heads", "kv_heads", "ffn", "vocab")):
+        # configuration 5 on the same ranks (every rank takes part; reported in the N > 1 line)
+        del fc1, fc2
+        torch.cuda.empty_cache()
+        c5 = _llama_step_bench(torch, C5, tp_group, dev, peer=peer)
+
     status = kernels.read_device_status()
     if status != 0:
         raise SystemExit(f"device status word is {status}: a bounded device-side wait expired")
@@ -726,6 +894,7 @@ def run_gpu_arm(args):
             line["scaling_base_ms"] = base["ms_per_step"]
             line["scaling_base"] = base["workload"] + ", timed on rank 0 before the sharded run"
             line["efficiency_vs_tp1"] = base["ms_per_step"] / (n * ms_step)
+            line["other_configs"] = {"llama8_mxfp8_tp_step": c5}
         if n == 1:
             g_avg = sum(g_ms) / len(g_ms)
             T_, H_, F_ = C2["tokens"], C2["in_features"], C2["out_features"]
@@ -771,6 +940,67 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def _profile_tp_step() -> None:
+    import torch
+    import torch.distributed as dist
+    from torch.profiler import ProfilerActivity, profile
+    from minitransformer_b200 import kernels as K
+    from minitransformer_b200.module import config as mt_config
+    from minitransformer_b200.module.linear import Linear
+    rank, lr = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(lr)
+    dev = torch.device("cuda", lr)
+    dist.init_process_group("nccl", device_id=dev)
+    g, n = dist.group.WORLD, dist.get_world_size()
+    peer = os.environ.get("MT_BENCH_TP_EXCHANGE", "peer") != "nccl"
+    params = mt_config.get_qlinear_params_from_predefined(mt_config.QuantizeRecipe.FP4_SUB_CHANNEL)
+    T, H, Fd = C4["tokens"], C4["hidden"], C4["ffn"]
+    x = torch.randn(T // n, H, device=dev).to(torch.bfloat16)
+    dy = (torch.randn(T // n, H, device=dev) * 1e-3).to(torch.bfloat16)
+    kw = dict(bias=False, params_dtype=torch.bfloat16, device=dev, qlinear_params=params, sequence_parallel=True,
+              tp_group=g, fuse_wgrad_accumulation=True, init_method=lambda t: torch.nn.init.normal_(t, std=0.02),
+              ub_overlap_ag=peer, ub_overlap_rs=peer)
+    fc1 = Linear(H, Fd, parallel_mode="column", ub_name="fc1", **kw)
+    fc2 = Linear(Fd, H, parallel_mode="row", ub_name="fc2", **kw)
+    for m in (fc1, fc2):
+        m.weight.main_grad = torch.zeros_like(m.weight, dtype=torch.float32)
+
+    def step():
+        xd = x.detach().requires_grad_(True)
+        fc2(fc1(xd, is_first_microbatch=True), is_first_microbatch=True).backward(dy)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"tp{n} exchange={'peer' if peer else 'nccl'} ms/step {e0.elapsed_time(e1) / 5:.3f}")
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    if rank == 0:
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=24, max_name_column_width=64))
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda e: e.time_range.start)
+        names = [e.name for e in evs]
+        per_step = len(evs) // 3
+        last = evs[-per_step:]
+        t0 = last[0].time_range.start
+        print("timeline of the last step (start us, duration us, kernel):")
+        for e in last:
+            print(f"{e.time_range.start - t0:8.0f} {e.time_range.end - e.time_range.start:7.0f}  {e.name[:90]}")
+    print("rank", rank, "device status", K.read_device_status()) if rank == 0 else K.read_device_status()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_profile_case(what: str) -> None:
     """Small, self-contained kernel workloads for `ncu` captures (one kernel family each, a few
     launches, a few hundred MB on the device; the quantize inputs exceed the 126 MB L2):
@@ -778,9 +1008,13 @@ def run_profile_case(what: str) -> None:
       gemm_mxfp8   MXFP8 pair GEMM, same shape
       quant        abs-max + NVFP4 cast/transpose (RHT) of 8192x14336
       quant_mxfp8  MXFP8 cast/transpose of 8192x14336
-      grouped      MXFP8 GroupedLinear fc1+fc2 fwd+bwd, 128 experts, 2 steps"""
+      grouped      MXFP8 GroupedLinear fc1+fc2 fwd+bwd, 128 experts, 2 steps
+      tp_step      (under torchrun, N ranks) the tensor-parallel MLP step of `--gpus N` under the torch
+                   profiler: per-kernel device time of three steps and the timeline of the last one"""
     import torch
     from minitransformer_b200 import kernels as K
+    if what == "tp_step":
+        return _profile_tp_step()
     dev = "cuda"
     torch.manual_seed(0)
     if what in ("gemm", "gemm_mxfp8"):

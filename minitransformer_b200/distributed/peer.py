@@ -44,6 +44,7 @@ class _Arena:
 
 class _EventHandle:
     """wait() makes the current stream wait for work recorded on another stream."""
+    needs_sm_margin = False     # the copy kernels use no shared memory: they share SMs with a running GEMM
 
     def __init__(self, event, keep=()):
         self.event, self.keep = event, keep

@@ -42,12 +42,32 @@ class LayerLinearBaseModule(torch.nn.Module, ABC):
         self.primary_weights_in_fp8 = None
         self.fsdp_group = None
 
-    # state-dict compatibility with TransformerEngine checkpoints
-    def get_extra_state(self) -> None:
-        return None
+    # ---- quantized primary weights ------------------------------------------------------------
+    # The reference leaves this as a placeholder (primary_weights_in_fp8 / with_fp8_params,
+    # miniTransformer/module/base.py:52-58, module/linear.py:708-715). Here: once
+    # keep_quantized_weights() has been called the layer's forward never re-quantizes its weight
+    # (whatever is_first_microbatch says) until refresh_quantized_weights() is called, typically
+    # after an optimizer step; the quantized copies travel in the state dict as extra state, so
+    # a checkpoint restores them without a quantize pass.
+    def keep_quantized_weights(self, keep: bool = True) -> None:
+        self.primary_weights_in_fp8 = bool(keep)
+        if not keep and getattr(self, "weight_qresult_cache", None) is not None:
+            self.weight_qresult_cache.clear()
+
+    def refresh_quantized_weights(self) -> None:
+        """Drops the kept quantized copies; the next forward quantizes the current weights."""
+        self.weight_qresult_cache.clear()
+
+    def get_extra_state(self):
+        cache = getattr(self, "weight_qresult_cache", None)
+        if not self.primary_weights_in_fp8 or cache is None or cache.data is None:
+            return None            # as the reference: nothing (keeps TransformerEngine checkpoints loadable)
+        return {"quantized_weight": cache.state()}
 
     def set_extra_state(self, state: Any) -> None:
-        pass
+        if isinstance(state, dict) and "quantized_weight" in state:
+            self.weight_qresult_cache.load_state(state["quantized_weight"])
+            self.primary_weights_in_fp8 = True
 
     def set_activation_dtype(self, inp: torch.Tensor) -> None:
         if torch.is_autocast_enabled():

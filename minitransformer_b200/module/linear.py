@@ -87,6 +87,13 @@ def _env_flag(name: str, default: bool) -> bool:
     return default if v is None else v not in ("0", "")
 
 
+def _margin_for(handles) -> int:
+    """SMs a GEMM leaves idle for the exchanges behind `handles`: NCCL kernels need shared memory
+    that a resident GEMM CTA leaves no room for, so they get SMs of their own; the peer copy
+    kernels of this library use none and run beside the GEMM's CTAs on the same SMs."""
+    return _overlap_sm_margin() if any(getattr(h, "needs_sm_margin", True) for h in handles) else 0
+
+
 def _sm_margin(op, sms: int):
     """Context in which the op's GEMMs leave `sms` SMs idle; ops without that control (the CPU
     stand-in of the tests) get a null context."""
@@ -182,8 +189,10 @@ class _QuantizedLinear(torch.autograd.Function):
             tp_group=tp_group, keep_transpose_local=qlinear_params.memory_saving and gather_required,
             weight_shape=tuple(w.shape), async_gather=True, input_meta=x_meta, peer_group=pg_ag, site=f"{site}:x")
 
-        # weights are re-quantized on the first microbatch (or when the caller gives no hint)
-        if is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None:
+        # weights are re-quantized on the first microbatch (or when the caller gives no hint),
+        # unless the layer keeps its quantized weights until told to refresh them
+        keep = bool(getattr(weight_qresult_cache, "keep", False)) and weight_qresult_cache.data is not None
+        if not keep and (is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None):
             qres_w = op.quantize(w, qlinear_params.w_params, return_transpose=True)
             weight_qresult_cache.store(qres_w)
         else:
@@ -206,7 +215,7 @@ class _QuantizedLinear(torch.autograd.Function):
                             qparams_w=qlinear_params.w_params)
 
         # the gather of x^T (needed by wgrad only) may still be running: leave it SMs
-        with _sm_margin(op, _overlap_sm_margin() if x_t_handles else 0):
+        with _sm_margin(op, _margin_for(x_t_handles)):
             if scatter:
                 y = _gemm_reduce_scatter(pg_rs, fprop, M, N, f"{site}:y", out_meta)
             elif amax_y is not None:
@@ -285,7 +294,7 @@ class _QuantizedLinear(torch.autograd.Function):
 
         # a gather of dy^T or of x^T (memory-saving mode) may be in flight: leave it SMs
         finish_dgrad = None
-        with _sm_margin(op, _overlap_sm_margin() if (dy_t_handles or pending_x_t is not None) else 0):
+        with _sm_margin(op, _overlap_sm_margin() if pending_x_t is not None else _margin_for(dy_t_handles)):
             if scatter:
                 # the tiles travel to their owners while the GEMM runs; the barrier and the local
                 # sum wait until the wgrad GEMM has been enqueued behind it
@@ -419,19 +428,21 @@ class _QuantizedLinear(torch.autograd.Function):
         dev, u8 = x.device, torch.uint8
         data = torch.empty((world * rows, sizes[0] // rows), dtype=u8, device=dev)
         scale = torch.empty(world * sizes[1], dtype=u8, device=dev)
-        pg.gather(shared, [(offs[0], data, sizes[0]), (offs[1], scale, sizes[1])])
+        # both pulls run on a side stream: the caller quantizes the weight meanwhile and waits for the
+        # row-wise copy just before the GEMM that reads it
+        segs_row = [(offs[0], data, sizes[0]), (offs[1], scale, sizes[1])]
+        h_row = pg.on_side_stream(lambda: pg.gather(shared, segs_row), keep=(data, scale))
         if r.data.dtype != u8:
             data = data.view(r.data.dtype)
         scale._mt_swz = scale
         out = quantization.QuantizeResult(data, scale, None, None, r.global_amax_row, r.global_amax_col, scale, None)
-        out._pending_handles = ()
+        out._pending_handles = (h_row,)
         out._pending_handles_t = ()
         if gather_t:
             data_t = torch.empty((world, cols, sizes[2] // cols), dtype=u8, device=dev)
             scale_t = torch.empty(world * sizes[3], dtype=u8, device=dev)
             segs = [(offs[2], data_t, sizes[2]), (offs[3], scale_t, sizes[3])]
-            ctas = max(8, _overlap_sm_margin())
-            out._pending_handles_t = (pg.on_side_stream(lambda: pg.gather(shared, segs, ctas=ctas), keep=(data_t, scale_t)),)
+            out._pending_handles_t = (pg.on_side_stream(lambda: pg.gather(shared, segs, ctas=32), keep=(data_t, scale_t)),)
             if r.data_t.dtype != u8:
                 data_t = data_t.view(r.data_t.dtype)
             scale_t._mt_swz = scale_t
@@ -692,6 +703,7 @@ class Linear(LayerLinearBaseModule):
                  bias if self.apply_bias and not self.gemm_bias_unfused_add else None,
                  self.sequence_parallel, self.tp_group, self.tp_size, self.parallel_mode, self.qlinear_params,
                  self.activation_dtype, grad, is_first_microbatch, self.fuse_wgrad_accumulation]
+        self.weight_qresult_cache.keep = bool(self.primary_weights_in_fp8)
         self.output_meta = quantization.QuantizeInputMeta() if self.emit_output_amax else None
         ub = None
         if self.ub_overlap_rs or self.ub_overlap_ag or self.output_meta is not None:

@@ -73,6 +73,30 @@ class QuantizeResultCache:
         assert self.data is not None and self.scale is not None, "weight cache is empty"
         return QuantizeResult(**{f.name: getattr(self, f.name) for f in dataclasses.fields(QuantizeResult)})
 
+    def clear(self) -> None:
+        for f in dataclasses.fields(QuantizeResult):
+            setattr(self, f.name, None)
+
+    def state(self) -> dict:
+        """The cached tensors as plain byte / fp32 tensors for a checkpoint."""
+        out = {}
+        for f in dataclasses.fields(QuantizeResult):
+            t = getattr(self, f.name)
+            if t is not None:
+                out[f.name] = (t.detach().clone().view(torch.uint8) if t.element_size() == 1 else t.detach().clone(),
+                               str(t.dtype))
+        return out
+
+    def load_state(self, state: dict) -> None:
+        self.clear()
+        for name, (t, dtype) in state.items():
+            dt = getattr(torch, dtype.split(".")[-1])
+            setattr(self, name, t.view(dt) if t.dtype != dt else t)
+        # the GEMM-layout scales ride along with the row-major ones
+        for lin, swz in (("scale", "scale_swz"), ("scale_t", "scale_t_swz")):
+            if getattr(self, lin) is not None and getattr(self, swz) is not None:
+                getattr(self, lin)._mt_swz = getattr(self, swz)
+
 
 @dataclasses.dataclass
 class QuantizeInputMetaBase:

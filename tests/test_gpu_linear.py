@@ -306,3 +306,36 @@ def test_grouped_plan_rejects_bad_offsets_without_touching_outputs():
     assert float((out.float() - 5.0).abs().max()) == 0.0
     assert K.read_device_status() == 32
     assert K.read_device_status() == 0
+
+
+@pytest.mark.parametrize("recipe", [config.QuantizeRecipe.FP4_SUB_CHANNEL, config.QuantizeRecipe.MXFP8_SUB_CHANNEL])
+def test_kept_quantized_weights_and_their_checkpoint(recipe):
+    """keep_quantized_weights(): the forward stops re-quantizing (whatever is_first_microbatch says)
+    until refresh_quantized_weights(); the quantized copies travel in the state dict and a fresh
+    layer that loads it computes with them, forward and backward, without a quantize pass."""
+    M, Kd, N = 256, 512, 384
+    tx, _ = seeded_bf16((M, Kd), 81)
+    tw, _ = seeded_bf16((N, Kd), 82, 0.02)
+    tdy, _ = seeded_bf16((M, N), 83, 1e-3)
+    lin = _make_linear(Kd, N, recipe, tw.cuda())
+    lin.keep_quantized_weights()
+    x = tx.cuda()
+    y0 = lin(x, is_first_microbatch=True).detach()
+    with torch.no_grad():
+        lin.weight.mul_(2)                       # the kept copies still describe the old weight
+    assert torch.equal(lin(x, is_first_microbatch=True).detach(), y0)
+    sd = lin.state_dict()
+    assert sd["_extra_state"] is not None
+    fresh = _make_linear(Kd, N, recipe, torch.zeros(N, Kd, dtype=torch.bfloat16, device="cuda"))
+    fresh.load_state_dict(sd)
+    xd = x.clone().requires_grad_(True)
+    y1 = fresh(xd)
+    assert torch.equal(y1.detach(), y0)
+    y1.backward(tdy.cuda())
+    ref = _make_linear(Kd, N, recipe, tw.cuda())
+    xr = x.clone().requires_grad_(True)
+    ref(xr).backward(tdy.cuda())
+    assert torch.equal(xd.grad, xr.grad)         # dgrad used the restored transposed copy of the old weight
+    lin.refresh_quantized_weights()
+    assert torch.equal(lin(x).detach(), 2 * y0)  # now the doubled weight: same codes, doubled scale
+    assert K.read_device_status() == 0
