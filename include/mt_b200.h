@@ -300,11 +300,14 @@ int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, u
  * bytes from shared[r] + src_offsets[s] to dsts[s] + r * shard_bytes[s]. The quantize kernels
  * write a rank's shard (codes, scales, transposed codes, transposed scales) straight into its
  * shared buffer; after a peer barrier this one launch assembles the gathered tensors in the
- * layout the GEMMs read. `ctas` bounds the SMs used (the copy is NVLink-bound; 32 to 64 suffice).
+ * layout the GEMMs read. `ctas` is the grid size. whole_sms = 0: CTAs of 128 threads, for a copy
+ * that has the GPU to itself (two per SM saturate NVLink). whole_sms = 1: CTAs of 1024 threads that
+ * each occupy one SM, for a copy that runs beside a GEMM launched with mt_gemm_opts.sm_margin =
+ * ctas (a GEMM CTA fills its SM's register file, so the two kernels cannot share SMs).
  * Sizes, offsets and addresses are multiples of 16 bytes. The caller keeps a shard unchanged
  * until a later barrier shows that every rank has pulled it. */
 int mt_peer_gather(const void* const* shared, int n, int me, const int64_t* src_offsets, void* const* dsts,
-                   const int64_t* shard_bytes, int nseg, int ctas, mt_stream_t stream);
+                   const int64_t* shard_bytes, int nseg, int ctas, int whole_sms, mt_stream_t stream);
 
 /* out[rows, cols] (bf16) = sum over s < n of stage[s][rows, cols] (bf16, fp32 accumulation in rank
  * order, one rounding): the second half of the reduce-scatter started by a GEMM with

@@ -59,7 +59,7 @@ _SIGNATURES = {
     "mt_peer_barrier": (_int, [_c.POINTER(_vp), _int, _int, _int, _c.c_uint32, _vp]),
     "mt_peer_allreduce_max": (_int, [_c.POINTER(_vp), _int, _int, _int, _c.c_uint32, _vp, _int, _vp]),
     "mt_peer_gather": (_int, [_c.POINTER(_vp), _int, _int, _c.POINTER(_i64), _c.POINTER(_vp), _c.POINTER(_i64), _int, _int,
-                              _vp]),
+                              _int, _vp]),
     "mt_peer_reduce_bf16": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp]),
     "mt_read_device_status": (_int, [_c.POINTER(_int), _vp]),
 }

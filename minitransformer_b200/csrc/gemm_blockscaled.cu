@@ -77,6 +77,7 @@ struct GemmArgs {
   float* d_amax;                 // optional: atomic max of |stored value| (pair kernel, no accumulation)
   int n_dest, my_rank;           // n_dest > 1 (pair kernel, dense, staged stores): output rows are scattered over
   int64_t dest_rows;             // the ranks' staging buffers, dest_rows rows each (PeerMaps), instead of d
+  int row_block_rotation;        // scattered output: the tile order starts this many 256-row blocks further down
 #ifdef MT_TIMING_KNOBS
   int knobs;                     // builds with -DMT_TIMING_KNOBS only (results are wrong when set): bit 0 the
                                  // epilogue drains tensor memory but writes nothing, bit 1 scale factors are
@@ -348,6 +349,43 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
       }
       // one group per chunk, empty when the chunk lies outside the output: the "all but one"
       // wait above counts groups, so the two halves must keep alternating group by group
+      bulk_commit_group();
+    }
+  }
+}
+
+// The same for a scattered (peer) output, bf16 only: 32 rows x 128 bytes per store (64 columns,
+// 128-byte swizzle, the warp's whole 4 KiB buffer), because stores that cross NVLink are far
+// more efficient in 128-byte than in 64-byte segments. The buffer is refilled once the previous
+// store has read it.
+__device__ __forceinline__ void store_block_staged_wide(const GemmArgs& a, const CUtensorMap* map_d,
+                                                        const uint32_t (&acc)[4][32], int ncols, uint8_t* stage,
+                                                        int lane, int64_t row0, int64_t map_rows, int64_t colw,
+                                                        float alpha, bool has_k) {
+  const uint32_t swz = lane & 7;
+#pragma unroll
+  for (int ch = 0; ch < 2; ++ch) {
+    if (ch * 64 >= ncols) break;
+    if (lane == 0) bulk_wait_read_all();
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                 // 16-byte piece j = columns 8j .. 8j+7 of the chunk
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int col = ch * 64 + j * 8 + t * 2;
+        const float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
+        const float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
+        __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+        w[t] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    const int64_t c0 = colw + (int64_t)ch * 64;
+    if (lane == 0) {
+      if (row0 < map_rows && c0 < a.N) tma_store_2d(map_d, stage, (int32_t)c0, (int32_t)row0);
       bulk_commit_group();
     }
   }
@@ -703,6 +741,10 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& a, int tile) {
   if (a.mode == MODE_DENSE) {
     int mb, nb;
     pair_tile_coord(a, tile, mb, nb);
+    // Scattered output: every rank starts with the row blocks of the rank after it and ends with
+    // its own, so that at any moment each destination receives from one sender only (all ranks
+    // walking the rows in the same order would have them all write to one rank at a time).
+    if (a.n_dest > 1) mb = (mb + a.row_block_rotation) % a.tiles_m;
     t.a_row0 = (int64_t)mb * 256;
     t.b_row0 = (int64_t)nb * BN;
     t.d_row_lo = 0;
@@ -942,8 +984,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         // they go to that rank's staging buffer, into the slice reserved for this rank
         const int dest = (int)(row0 / a.dest_rows);
         const int64_t srow = (int64_t)a.my_rank * a.dest_rows + (row0 - (int64_t)dest * a.dest_rows);
-        store_block_staged(a, &maps_peer.m[dest], acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, srow, a.map_rows,
-                           colw, alpha, num_k > 0, am);
+        store_block_staged_wide(a, &maps_peer.m[dest], acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, srow, a.map_rows,
+                                colw, alpha, num_k > 0);
         continue;
       }
       store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
@@ -1088,7 +1130,7 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
     // scattered output: one map per destination staging buffer, [d_rows, d_cols] bf16 with pitch d_cols
     for (int r = 0; r < args.n_dest; ++r) {
       rc = make_tensor_map_2d(&scatter_maps.m[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dest[r], (uint64_t)d_cols,
-                              (uint64_t)d_rows, (uint64_t)d_cols * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+                              (uint64_t)d_rows, (uint64_t)d_cols * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc != MT_OK) return rc;
     }
     for (int r = args.n_dest; r < MT_MAX_PEERS; ++r) scatter_maps.m[r] = scatter_maps.m[0];
@@ -1195,7 +1237,10 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   args.mode = MODE_DENSE;
   args.sm_margin = sm_margin;
   args.d_amax = d_amax;
-  if (n_dest > 1) { args.n_dest = n_dest; args.my_rank = opts->my_rank; args.dest_rows = opts->dest_rows; }
+  if (n_dest > 1) {
+    args.n_dest = n_dest; args.my_rank = opts->my_rank; args.dest_rows = opts->dest_rows;
+    args.row_block_rotation = (int)(((opts->my_rank + 1) % n_dest) * (opts->dest_rows / 256));
+  }
   args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
   // K == 0 never reaches this point; tensor maps below need K_bytes >= 16
   if (pair_enabled() && M > G_BLOCK_M && N > 128) {

@@ -108,27 +108,46 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
   return v;
 }
 
-__global__ void __launch_bounds__(512) peer_gather_kernel(const GatherArgs a) {
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+// Work is cut into units of THREADS * 128 bytes of one (segment, rank); consecutive units belong to
+// different ranks, so the CTAs running at one time pull from all peers at once (a single peer at a
+// time leaves the copy bound by the round-trip latency of one link), and every rank starts with
+// the peer after it. Two shapes: 128-thread CTAs for a copy that has the GPU to itself, and
+// 1024-thread CTAs that each claim a whole SM (through a large dynamic shared-memory request) for
+// a copy that runs beside a persistent GEMM whose grid leaves that many SMs free: a GEMM CTA
+// fills the register file of its SM, so the two kernels cannot share SMs, and a copy spread thinly
+// over all SMs would hold up the GEMM's CTAs instead.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) peer_gather_kernel(const GatherArgs a) {
+  constexpr int UNIT = THREADS * 16 * 8;   // 8 loads of 16 bytes in flight per thread
+  int64_t first = 0;   // first unit of the current segment
+  int64_t u = blockIdx.x;
   for (int s = 0; s < a.nseg; ++s) {
     const GatherSeg g = a.seg[s];
-    const int64_t vecs = g.bytes >> 4;
-    // ranks are visited starting after this one, so that the ranks do not all read the same peer at once
-    for (int k = 1; k <= a.n; ++k) {
-      const int r = (a.me + k) % a.n;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(a.src.p[r]) + g.src_off);
-      uint4* dst = reinterpret_cast<uint4*>(g.dst + (int64_t)r * g.bytes);
-      int64_t i = tid;
-      for (; i + 3 * nthreads < vecs; i += 4 * nthreads) {
-        const uint4 v0 = ld_peer_v4(src + i), v1 = ld_peer_v4(src + i + nthreads);
-        const uint4 v2 = ld_peer_v4(src + i + 2 * nthreads), v3 = ld_peer_v4(src + i + 3 * nthreads);
-        dst[i] = v0; dst[i + nthreads] = v1; dst[i + 2 * nthreads] = v2; dst[i + 3 * nthreads] = v3;
+    const int64_t chunks = (g.bytes + UNIT - 1) / UNIT;
+    const int64_t units = chunks * a.n;
+    for (; u < first + units; u += gridDim.x) {
+      const int64_t local = u - first;
+      const int r = (a.me + 1 + (int)(local % a.n)) % a.n;
+      const int64_t off = (local / a.n) * UNIT;
+      const int64_t vecs = min((int64_t)UNIT, g.bytes - off) >> 4;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(a.src.p[r]) + g.src_off + off);
+      uint4* dst = reinterpret_cast<uint4*>(g.dst + (int64_t)r * g.bytes + off);
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int64_t i = threadIdx.x + k * THREADS;
+        if (i < vecs) v[k] = ld_peer_v4(src + i);
       }
-      for (; i < vecs; i += nthreads) dst[i] = ld_peer_v4(src + i);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int64_t i = threadIdx.x + k * THREADS;
+        if (i < vecs) dst[i] = v[k];
+      }
     }
+    first += units;
   }
 }
+constexpr int GATHER_EXCLUSIVE_SMEM = 160 * 1024;   // more than half an SM: one such CTA per SM
 
 // ---- reduce of pushed partial sums ----
 // stage is [n][rows][cols] bf16 in this rank's memory (slice s written by rank s's GEMM epilogue);
@@ -254,13 +273,13 @@ int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, u
 }
 
 int mt_peer_gather(const void* const* shared, int n, int me, const int64_t* src_offsets, void* const* dsts,
-                   const int64_t* shard_bytes, int nseg, int ctas, mt_stream_t stream) {
+                   const int64_t* shard_bytes, int nseg, int ctas, int whole_sms, mt_stream_t stream) {
   const char* name = "mt_peer_gather";
   int rc = mt::check_peers(name, shared, n, me);
   if (rc != MT_OK) return rc;
   MT_REQUIRE(src_offsets && dsts && shard_bytes && nseg >= 1 && nseg <= MT_MAX_GATHER_SEGS, "%s: 1 to %d segments", name,
              MT_MAX_GATHER_SEGS);
-  MT_REQUIRE(ctas >= 1 && ctas <= 1024, "%s: CTA count %d out of range", name, ctas);
+  MT_REQUIRE(ctas >= 1 && ctas <= 4096, "%s: CTA count %d out of range", name, ctas);
   mt::GatherArgs a{};
   a.src = mt::make_table(shared, n);
   a.nseg = nseg; a.n = n; a.me = me;
@@ -271,7 +290,31 @@ int mt_peer_gather(const void* const* shared, int n, int me, const int64_t* src_
     a.seg[s].dst = static_cast<uint8_t*>(dsts[s]);
     a.seg[s].bytes = shard_bytes[s];
   }
-  mt::peer_gather_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  if (whole_sms) {
+    auto kern = mt::peer_gather_kernel<1024>;
+    static bool attr_set[mt::MT_MAX_DEVICES] = {};
+    const int slot = mt::current_device_slot();
+    if (!attr_set[slot]) {
+      MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mt::GATHER_EXCLUSIVE_SMEM));
+      attr_set[slot] = true;
+    }
+    // launched as clusters of two, which the hardware places on the two SMs of one TPC: the
+    // CTA pairs of the GEMM beside it need whole TPCs, so the copy should not break up more
+    // of them than it has to
+    MT_REQUIRE(ctas % 2 == 0, "%s: a whole-SM copy takes an even number of CTAs", name);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(1024);
+    cfg.dynamicSmemBytes = mt::GATHER_EXCLUSIVE_SMEM;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    MT_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+  } else {
+    mt::peer_gather_kernel<128><<<ctas, 128, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  }
   MT_CUDA(cudaGetLastError());
   return MT_OK;
 }

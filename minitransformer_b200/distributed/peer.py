@@ -44,7 +44,7 @@ class _Arena:
 
 class _EventHandle:
     """wait() makes the current stream wait for work recorded on another stream."""
-    needs_sm_margin = False     # the copy kernels use no shared memory: they share SMs with a running GEMM
+    needs_sm_margin = True      # the copy runs on SMs of its own, which the GEMM beside it must leave free
 
     def __init__(self, event, keep=()):
         self.event, self.keep = event, keep
@@ -144,13 +144,15 @@ class PeerGroup:
                   vals.data_ptr(), vals.numel(), self._stream())
         return vals
 
-    def gather(self, shared: SharedBuffer, segments, ctas: int = 48) -> None:
-        """segments: (byte offset inside every rank's shared range, destination tensor, shard bytes)."""
+    def gather(self, shared: SharedBuffer, segments, ctas: int = 296, whole_sms: bool = False) -> None:
+        """segments: (byte offset inside every rank's shared range, destination tensor, shard bytes).
+        whole_sms: `ctas` CTAs that each take one SM, for a copy that runs beside a GEMM which leaves
+        that many SMs free."""
         n = len(segments)
         offs = (ctypes.c_int64 * n)(*[s[0] for s in segments])
         dsts = (ctypes.c_void_p * n)(*[s[1].data_ptr() for s in segments])
         sizes = (ctypes.c_int64 * n)(*[s[2] for s in segments])
-        _lib.call("mt_peer_gather", shared.table, self.world, self.rank, offs, dsts, sizes, n, ctas, self._stream())
+        _lib.call("mt_peer_gather", shared.table, self.world, self.rank, offs, dsts, sizes, n, ctas, int(whole_sms), self._stream())
 
     def reduce_bf16(self, stage: SharedBuffer, rows: int, cols: int, amax_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         out = torch.empty((rows, cols), dtype=torch.bfloat16, device=self.device)

@@ -88,9 +88,9 @@ def _env_flag(name: str, default: bool) -> bool:
 
 
 def _margin_for(handles) -> int:
-    """SMs a GEMM leaves idle for the exchanges behind `handles`: NCCL kernels need shared memory
-    that a resident GEMM CTA leaves no room for, so they get SMs of their own; the peer copy
-    kernels of this library use none and run beside the GEMM's CTAs on the same SMs."""
+    """SMs a GEMM leaves idle for the exchanges behind `handles`: a resident GEMM CTA fills its
+    SM (shared memory and registers), so a collective or copy kernel that should run beside the
+    GEMM needs SMs of its own."""
     return _overlap_sm_margin() if any(getattr(h, "needs_sm_margin", True) for h in handles) else 0
 
 
@@ -442,7 +442,7 @@ class _QuantizedLinear(torch.autograd.Function):
             data_t = torch.empty((world, cols, sizes[2] // cols), dtype=u8, device=dev)
             scale_t = torch.empty(world * sizes[3], dtype=u8, device=dev)
             segs = [(offs[2], data_t, sizes[2]), (offs[3], scale_t, sizes[3])]
-            out._pending_handles_t = (pg.on_side_stream(lambda: pg.gather(shared, segs, ctas=32), keep=(data_t, scale_t)),)
+            out._pending_handles_t = (pg.on_side_stream(lambda: pg.gather(shared, segs, ctas=max(4, _overlap_sm_margin()) // 2 * 2, whole_sms=True), keep=(data_t, scale_t)),)
             if r.data_t.dtype != u8:
                 data_t = data_t.view(r.data_t.dtype)
             scale_t._mt_swz = scale_t
