@@ -171,7 +171,10 @@ def _workload_config(n):
                 "l2": "inputs (x 64 MiB, w 112 MiB, dy 224 MiB) exceed the 126 MB L2"}
     return {"workload": "tensor-parallel NVFP4 MLP fwd+bwd: column-parallel fc1 -> row-parallel fc2, "
                         "sequence parallel, quantized all-gather, bf16 reduce-scatter",
-            **C4, "parallelism": f"tp{n}", "l2": "per-rank operands exceed the 126 MB L2"}
+            **C4, "parallelism": f"tp{n}", "l2": "per-rank operands exceed the 126 MB L2",
+            "exchange": ("NVLink peer memory by this library's kernels (pull all-gather, GEMM epilogue that scatters rows + "
+                         "local reduce)" if os.environ.get("MT_BENCH_TP_EXCHANGE", "peer") != "nccl" else "NCCL collectives"),
+            "cuda_graph": os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"}
 
 
 class ClockSampler(threading.Thread):
@@ -601,15 +604,35 @@ def _llama_step_bench(torch, dims, tp_group, dev, steps=3, warmup=2, peer=True):
         # loss sum the ranks' gradients, so each rank back-propagates its 1/n share
         (loss / n).backward()
 
-    for _ in range(warmup):
-        step()
+    graphed = tp_group is not None and os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"
+    # warm-up on a side stream, as graph capture of a backward pass wants it (the gradient
+    # accumulation nodes remember the stream they first ran on)
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(max(warmup, 3 if graphed else 0)):
+            step()
+    torch.cuda.current_stream(dev).wait_stream(side)
     torch.cuda.synchronize()
     if tp_group is not None:
+        dist.barrier()
+    run = step
+    if graphed:
+        # the sharded step is a few hundred short kernels: replayed from a CUDA graph, like the MLP step
+        for p_ in model.parameters():
+            p_.grad = None
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            loss = model(ids, tgt)
+            (loss / n).backward()
+        run = graph.replay
+        run()
+        torch.cuda.synchronize()
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        step()
+        run()
     e1.record()
     torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
@@ -618,7 +641,7 @@ def _llama_step_bench(torch, dims, tp_group, dev, steps=3, warmup=2, peer=True):
     ms = float(ms.item())
     flops = llama_linear_flops(dims)
     return {"ms_per_step": ms, "linear_tflops_per_gpu": flops / n / (ms * 1e-3) / 1e12, "unit": UNIT,
-            "linear_flops_per_step": flops, "loss": float(loss.item()), "steps": steps, "tp": n,
+            "linear_flops_per_step": flops, "loss": float(loss.item()), "steps": steps, "tp": n, "cuda_graph": graphed,
             "workload": (f"{dims['layers']}-layer Llama-style decoder fwd+bwd, MXFP8 recipe on every Linear (LM head "
                          f"included), hidden {dims['hidden']}, {dims['heads']} heads / {dims['kv_heads']} KV heads, "
                          f"ffn {dims['ffn']}, vocab {dims['vocab']}, seq {dims['seq']} x micro-batch "
@@ -816,10 +839,38 @@ def run_gpu_arm(args):
             y.backward(dyd)
             return y
 
-        def step(record):
+        def eager_step(record):
             xd = x.detach().requires_grad_(True)
             y = mlp(xd, dy)
             return y, xd.grad
+
+        # The sharded step holds ~50 short kernels: at 8 ranks it would be bound by the host
+        # enqueueing them (about 1.6 ms of Python per step), so the whole forward + backward is
+        # captured once into a CUDA graph and replayed (MT_BENCH_CUDA_GRAPH=0 times the eager step).
+        use_graph = os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"
+        step = eager_step
+        if use_graph:
+            x_static = x.detach().clone().requires_grad_(True)
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(3):                      # warm-up: one-time setup, shared-buffer allocation
+                    x_static.grad = None
+                    mlp(x_static, dy)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            x_static.grad = None
+            before = kernels.LAUNCH_COUNT
+            with torch.cuda.graph(graph):
+                y_static = mlp(x_static, dy)
+            launches_per_replay = kernels.LAUNCH_COUNT - before
+
+            def step(record):
+                graph.replay()
+                kernels.LAUNCH_COUNT += launches_per_replay
+                return y_static, x_static.grad
 
         def e2e_step():
             xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
@@ -979,8 +1030,15 @@ def _profile_tp_step() -> None:
         step()
     e1.record()
     torch.cuda.synchronize()
+    # host time to enqueue one step (the GPU is kept busy by a long queue, so this is pure CPU time)
+    t0 = time.perf_counter()
+    for _ in range(10):
+        step()
+    host_ms = (time.perf_counter() - t0) / 10 * 1e3
+    torch.cuda.synchronize()
     if rank == 0:
-        print(f"tp{n} exchange={'peer' if peer else 'nccl'} ms/step {e0.elapsed_time(e1) / 5:.3f}")
+        print(f"tp{n} exchange={'peer' if peer else 'nccl'} ms/step {e0.elapsed_time(e1) / 5:.3f} "
+              f"host enqueue ms/step {host_ms:.3f}")
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
         for _ in range(3):
             step()

@@ -278,7 +278,8 @@ int mt_grouped_wgrad_mxfp8(const uint8_t* a_t, const uint8_t* sa_t_swz, const ui
  * Control block: MT_PEER_CTRL_BYTES bytes per rank, zeroed once before every rank's first call
  * (with a host-side barrier between the zeroing and the first use). `channel` (0..7) separates
  * call sequences that may overlap in time (different streams); on one channel every rank must
- * issue the same sequence of calls with the same, strictly increasing `epoch` (start at 1). */
+ * issue the same sequence of exchanges, one at a time. The exchanges number themselves with a
+ * counter in the control block, so a stream capture that contains them can be replayed. */
 #define MT_PEER_CTRL_BYTES 4096
 #define MT_MAX_GATHER_SEGS 8
 #define MT_IPC_HANDLE_BYTES 64
@@ -288,12 +289,12 @@ int mt_ipc_close(void* ptr, int64_t offset);
 
 /* All ranks' work enqueued before the barrier on `stream` (on each rank's own stream) is complete
  * and visible to every rank's work enqueued after it. One 32-thread kernel. */
-int mt_peer_barrier(const void* const* ctrl, int n, int me, int channel, uint32_t epoch, mt_stream_t stream);
+int mt_peer_barrier(const void* const* ctrl, int n, int me, int channel, mt_stream_t stream);
 
 /* vals[0..nvals) (device fp32, nvals <= 4, non-negative values) <- element-wise maximum over all
  * ranks; also a barrier. The per-tensor abs-max of a token-sharded activation before its shards
  * are quantized (the MAX all-reduce of miniTransformer/ops/quantization.py:100-119 `reduce_amax`). */
-int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, uint32_t epoch,
+int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel,
                           float* vals, int nvals, mt_stream_t stream);
 
 /* All-gather by pulling: for every segment s < nseg and every rank r < n, copies shard_bytes[s]

@@ -56,8 +56,8 @@ _SIGNATURES = {
     "mt_ipc_export": (_int, [_vp, _vp, _c.POINTER(_i64)]),
     "mt_ipc_import": (_int, [_vp, _i64, _c.POINTER(_vp)]),
     "mt_ipc_close": (_int, [_vp, _i64]),
-    "mt_peer_barrier": (_int, [_c.POINTER(_vp), _int, _int, _int, _c.c_uint32, _vp]),
-    "mt_peer_allreduce_max": (_int, [_c.POINTER(_vp), _int, _int, _int, _c.c_uint32, _vp, _int, _vp]),
+    "mt_peer_barrier": (_int, [_c.POINTER(_vp), _int, _int, _int, _vp]),
+    "mt_peer_allreduce_max": (_int, [_c.POINTER(_vp), _int, _int, _int, _vp, _int, _vp]),
     "mt_peer_gather": (_int, [_c.POINTER(_vp), _int, _int, _c.POINTER(_i64), _c.POINTER(_vp), _c.POINTER(_i64), _int, _int,
                               _int, _vp]),
     "mt_peer_reduce_bf16": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp]),

@@ -77,7 +77,6 @@ struct GemmArgs {
   float* d_amax;                 // optional: atomic max of |stored value| (pair kernel, no accumulation)
   int n_dest, my_rank;           // n_dest > 1 (pair kernel, dense, staged stores): output rows are scattered over
   int64_t dest_rows;             // the ranks' staging buffers, dest_rows rows each (PeerMaps), instead of d
-  int row_block_rotation;        // scattered output: the tile order starts this many 256-row blocks further down
 #ifdef MT_TIMING_KNOBS
   int knobs;                     // builds with -DMT_TIMING_KNOBS only (results are wrong when set): bit 0 the
                                  // epilogue drains tensor memory but writes nothing, bit 1 scale factors are
@@ -741,10 +740,15 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& a, int tile) {
   if (a.mode == MODE_DENSE) {
     int mb, nb;
     pair_tile_coord(a, tile, mb, nb);
-    // Scattered output: every rank starts with the row blocks of the rank after it and ends with
-    // its own, so that at any moment each destination receives from one sender only (all ranks
-    // walking the rows in the same order would have them all write to one rank at a time).
-    if (a.n_dest > 1) mb = (mb + a.row_block_rotation) % a.tiles_m;
+    // Scattered output: consecutive row blocks go to different destinations, starting with the
+    // rank after this one and ending with its own, so that a rank's stores are spread evenly over
+    // its links for the whole run of the kernel and no destination is written by every rank at
+    // once (all ranks walking the rows in the same order would do exactly that).
+    if (a.n_dest > 1) {
+      const int per_dest = a.tiles_m / a.n_dest;
+      const int dest = (a.my_rank + 1 + mb % a.n_dest) % a.n_dest;
+      mb = dest * per_dest + mb / a.n_dest;
+    }
     t.a_row0 = (int64_t)mb * 256;
     t.b_row0 = (int64_t)nb * BN;
     t.d_row_lo = 0;
@@ -1239,7 +1243,6 @@ static int gemm_common(int format, const uint8_t* a, const uint8_t* sa, const fl
   args.d_amax = d_amax;
   if (n_dest > 1) {
     args.n_dest = n_dest; args.my_rank = opts->my_rank; args.dest_rows = opts->dest_rows;
-    args.row_block_rotation = (int)(((opts->my_rank + 1) % n_dest) * (opts->dest_rows / 256));
   }
   args.k_elems_per_byte_x2 = format == FMT_NVFP4 ? 4 : 2;
   // K == 0 never reaches this point; tensor maps below need K_bytes >= 16

@@ -22,10 +22,14 @@
 namespace mt {
 
 constexpr int PEER_CHANNELS = 8;
-// Control block layout (bytes): flags[channel][src] u32, then values[channel][parity][src][4] f32.
+// Control block layout (bytes): flags[channel][src] u32, values[channel][parity][src][4] f32, then
+// epoch[channel] u32: the number of exchanges this rank has done on the channel. The epoch lives
+// on the device (each exchange kernel increments it), so that a captured sequence of exchanges
+// can be replayed: every replay signals and waits for fresh values.
 constexpr int CTRL_FLAGS_BYTES = PEER_CHANNELS * MT_MAX_PEERS * 4;
 constexpr int CTRL_VALUES_BYTES = PEER_CHANNELS * 2 * MT_MAX_PEERS * 4 * 4;
-static_assert(CTRL_FLAGS_BYTES + CTRL_VALUES_BYTES <= MT_PEER_CTRL_BYTES, "control block too small");
+constexpr int CTRL_EPOCH_OFFSET = CTRL_FLAGS_BYTES + CTRL_VALUES_BYTES;
+static_assert(CTRL_EPOCH_OFFSET + PEER_CHANNELS * 4 <= MT_PEER_CTRL_BYTES, "control block too small");
 
 struct PeerTable {
   void* p[MT_MAX_PEERS];
@@ -57,9 +61,18 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
 // One warp: lane t signals peer t and waits for peer t's signal. With nvals > 0 the lane first
 // writes this rank's values into the peer's control block and afterwards reads the peer's values
 // from its own block; vals[] is replaced by the maximum over all ranks.
-__global__ void __launch_bounds__(32) peer_exchange_kernel(PeerTable ctrl, int me, int n, int channel, uint32_t epoch,
-                                                           float* vals, int nvals, int* status, uint64_t timeout_ns) {
+__global__ void __launch_bounds__(32) peer_exchange_kernel(PeerTable ctrl, int me, int n, int channel, float* vals,
+                                                           int nvals, int* status, uint64_t timeout_ns) {
   const int t = threadIdx.x;
+  // this exchange's number: one more than the last one on this channel (only this kernel, one
+  // launch at a time per channel, touches the counter)
+  uint32_t* counter = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctrl.p[me]) + CTRL_EPOCH_OFFSET) + channel;
+  uint32_t epoch = 0;
+  if (t == 0) {
+    epoch = *counter + 1;
+    *counter = epoch;
+  }
+  epoch = __shfl_sync(0xffffffffu, epoch, 0);
   const int parity = epoch & 1;
   float mine[4] = {0.f, 0.f, 0.f, 0.f}, got[4] = {0.f, 0.f, 0.f, 0.f};
   for (int i = 0; i < nvals; ++i) mine[i] = vals[i];
@@ -246,19 +259,19 @@ int mt_ipc_close(void* ptr, int64_t offset) {
   return MT_OK;
 }
 
-int mt_peer_barrier(const void* const* ctrl, int n, int me, int channel, uint32_t epoch, mt_stream_t stream) {
+int mt_peer_barrier(const void* const* ctrl, int n, int me, int channel, mt_stream_t stream) {
   int rc = mt::check_peers("mt_peer_barrier", ctrl, n, me);
   if (rc != MT_OK) return rc;
   MT_REQUIRE(channel >= 0 && channel < mt::PEER_CHANNELS, "mt_peer_barrier: channel %d out of range", channel);
   int* status = mt::device_status_ptr();
   if (!status) return mt::fail(MT_ERR_CUDA, "device status word not reachable");
-  mt::peer_exchange_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mt::make_table(ctrl, n), me, n, channel, epoch,
+  mt::peer_exchange_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mt::make_table(ctrl, n), me, n, channel,
                                                                             nullptr, 0, status, 2000000000ull);
   MT_CUDA(cudaGetLastError());
   return MT_OK;
 }
 
-int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, uint32_t epoch, float* vals, int nvals,
+int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, float* vals, int nvals,
                           mt_stream_t stream) {
   int rc = mt::check_peers("mt_peer_allreduce_max", ctrl, n, me);
   if (rc != MT_OK) return rc;
@@ -266,7 +279,7 @@ int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, u
   MT_REQUIRE(vals != nullptr && nvals >= 1 && nvals <= 4, "mt_peer_allreduce_max: 1 to 4 values");
   int* status = mt::device_status_ptr();
   if (!status) return mt::fail(MT_ERR_CUDA, "device status word not reachable");
-  mt::peer_exchange_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mt::make_table(ctrl, n), me, n, channel, epoch,
+  mt::peer_exchange_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mt::make_table(ctrl, n), me, n, channel,
                                                                             vals, nvals, status, 2000000000ull);
   MT_CUDA(cudaGetLastError());
   return MT_OK;

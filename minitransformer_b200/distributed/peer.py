@@ -17,7 +17,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from .. import _lib
+from .. import _lib, kernels
 
 _ARENA_MIN_BYTES = 64 << 20     # large enough to be an allocation of its own in torch's caching allocator
 _ALIGN = 4096
@@ -63,7 +63,6 @@ class PeerGroup:
         self.device = torch.device(device)
         self._arenas: List[_Arena] = []
         self._named: Dict[str, SharedBuffer] = {}
-        self._epochs = [0] * 8
         self._parity: Dict[str, int] = {}
         self._imported: Dict[bytes, int] = {}
         self.side_stream = torch.cuda.Stream(device=self.device)
@@ -120,28 +119,31 @@ class PeerGroup:
 
     def alternating(self, name: str, nbytes: int) -> SharedBuffer:
         """Two ranges used in turn: a range is rewritten only after a later exchange on the same
-        name has passed its barrier, by which time every rank has finished reading it."""
+        name has passed its barrier, by which time every rank has finished reading it. Under
+        stream capture the turn cannot advance from replay to replay: the first range is used
+        and a barrier is issued first, which shows that every rank is done with its last use."""
+        if torch.cuda.is_current_stream_capturing():
+            self.barrier()
+            return self.buffer(f"{name}#0", nbytes)
         p = self._parity.get(name, 0)
         self._parity[name] = p ^ 1
         return self.buffer(f"{name}#{p}", nbytes)
 
     # ---- exchanges (all stream-ordered on the current stream) ----
-    def _next_epoch(self, channel: int) -> int:
-        self._epochs[channel] = (self._epochs[channel] + 1) & 0xFFFFFFFF
-        return self._epochs[channel]
-
     @staticmethod
     def _stream():
         return torch.cuda.current_stream().cuda_stream
 
     def barrier(self, channel: int = 0) -> None:
-        _lib.call("mt_peer_barrier", self.ctrl.table, self.world, self.rank, channel, self._next_epoch(channel), self._stream())
+        _lib.call("mt_peer_barrier", self.ctrl.table, self.world, self.rank, channel, self._stream())
+        kernels._count(1)
 
     def allreduce_max_(self, vals: torch.Tensor, channel: int = 0) -> torch.Tensor:
         """In-place MAX over the ranks of up to 4 non-negative fp32 device values; also a barrier."""
         assert vals.dtype == torch.float32 and vals.is_cuda and vals.is_contiguous() and 1 <= vals.numel() <= 4
-        _lib.call("mt_peer_allreduce_max", self.ctrl.table, self.world, self.rank, channel, self._next_epoch(channel),
-                  vals.data_ptr(), vals.numel(), self._stream())
+        _lib.call("mt_peer_allreduce_max", self.ctrl.table, self.world, self.rank, channel, vals.data_ptr(), vals.numel(),
+                  self._stream())
+        kernels._count(1)
         return vals
 
     def gather(self, shared: SharedBuffer, segments, ctas: int = 296, whole_sms: bool = False) -> None:
@@ -153,11 +155,13 @@ class PeerGroup:
         dsts = (ctypes.c_void_p * n)(*[s[1].data_ptr() for s in segments])
         sizes = (ctypes.c_int64 * n)(*[s[2] for s in segments])
         _lib.call("mt_peer_gather", shared.table, self.world, self.rank, offs, dsts, sizes, n, ctas, int(whole_sms), self._stream())
+        kernels._count(1)
 
     def reduce_bf16(self, stage: SharedBuffer, rows: int, cols: int, amax_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         out = torch.empty((rows, cols), dtype=torch.bfloat16, device=self.device)
         _lib.call("mt_peer_reduce_bf16", stage.tensor.data_ptr(), self.world, rows, cols, out.data_ptr(),
                   None if amax_out is None else amax_out.data_ptr(), self._stream())
+        kernels._count(1)
         return out
 
     def on_side_stream(self, fn, keep=()) -> _EventHandle:
