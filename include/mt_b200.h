@@ -80,6 +80,18 @@ int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags,
                       uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
                       mt_stream_t stream);
 
+/* The same cast with stochastic rounding of the codes: every element becomes one of its two
+ * neighbouring E2M1 values, the nearer one more often, so that the expectation of the dequantized
+ * value equals the input (for gradients; scales and abs-max handling are unchanged, 1x16 blocks
+ * only). `seed` makes a launch reproducible; use a fresh one per call. The reference carries this
+ * path compiled out (miniTransformer/csrc/util/ptx.cuh:222-260, 319-352;
+ * csrc/ops/fp4/quantization/quantize_transpose_nvfp4.cu:1145 use_stochastic_rounding = false). */
+int mt_quantize_nvfp4_sr(const void* x, int64_t rows, int64_t cols, int flags,
+                         const float* amax_row, const float* amax_col,
+                         uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                         uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz,
+                         uint64_t seed, mt_stream_t stream);
+
 /* MXFP8 cast (+ transpose): E4M3 elements, one E8M0 scale byte (exponent + 127) per 1x32
  * block. Scale rule: 2^ceil(log2(amax/448)) clamped to 2^+-127 (cast_to_e8,
  * miniTransformer/ops/nvfp4_quantize_op_ref.py:12-21).

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "mt_swizzled_scale_bytes": (_i64, [_i64, _i64]),
     "mt_amax_bf16": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "mt_quantize_nvfp4": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "mt_quantize_nvfp4_sr": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _c.c_uint64,
+                                    _vp]),
     "mt_quantize_mxfp8": (_int, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
     "mt_swizzle_scales": (_int, [_vp, _i64, _i64, _i64, _vp, _vp]),
     "mt_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _int, _opts, _vp]),

@@ -223,6 +223,46 @@ __device__ __forceinline__ void e2m1x8_two_columns(const uint32_t* w, f32x2_t en
       : "f"(hi[0]), "f"(hi[1]), "f"(hi[2]), "f"(hi[3]), "f"(hi[4]), "f"(hi[5]), "f"(hi[6]), "f"(hi[7]));
 }
 
+// ---- stochastic rounding (gradient codes) ----
+// 32 random bits for one group of four elements: a counter-based hash of (seed, group index), so
+// that a launch is reproducible from its seed and independent of the grid.
+__device__ __forceinline__ uint32_t sr_bits(uint64_t seed, uint64_t group) {
+  uint64_t z = (group + seed) * 0x9E3779B97F4A7C15ull;
+  z ^= z >> 32;
+  uint32_t x = static_cast<uint32_t>(z) ^ static_cast<uint32_t>(seed >> 32);
+  x ^= x >> 16; x *= 0x85EBCA6Bu; x ^= x >> 13; x *= 0xC2B2AE35u; x ^= x >> 16;
+  return x;
+}
+// Four scaled fp32 values -> four E2M1 nibbles (x0 in the lowest), each rounded to one of its
+// two neighbouring codes with probability proportional to its distance from the other
+// (cvt.rs: stochastic rounding with the given random bits).
+__device__ __forceinline__ uint32_t e2m1x4_sr(float x0, float x1, float x2, float x3, uint32_t rbits) {
+  uint16_t out;
+  asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;" : "=h"(out) : "f"(x3), "f"(x2), "f"(x1), "f"(x0), "r"(rbits));
+  return out;
+}
+// Stochastic-rounding forms of e2m1x8_from_words / e2m1x8_two_columns.
+__device__ __forceinline__ uint32_t e2m1x8_from_words_sr(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, float enc,
+                                                         bool fused, uint32_t rb0, uint32_t rb1) {
+  const f32x2_t e2 = pack2(enc, enc);
+  float a0, a1, b0, b1, c0, c1, d0, d1;
+  unpack2(scale2(bf16x2_to_f32x2(w0), e2, fused), a0, a1);
+  unpack2(scale2(bf16x2_to_f32x2(w1), e2, fused), b0, b1);
+  unpack2(scale2(bf16x2_to_f32x2(w2), e2, fused), c0, c1);
+  unpack2(scale2(bf16x2_to_f32x2(w3), e2, fused), d0, d1);
+  return e2m1x4_sr(a0, a1, b0, b1, rb0) | (e2m1x4_sr(c0, c1, d0, d1, rb1) << 16);
+}
+__device__ __forceinline__ void e2m1x8_two_columns_sr(const uint32_t* w, f32x2_t enc2, bool fused, uint32_t& codes_lo,
+                                                      uint32_t& codes_hi, uint32_t rb0, uint32_t rb1) {
+  float lo[8], hi[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) unpack2(scale2(bf16x2_to_f32x2(w[j]), enc2, fused), lo[j], hi[j]);
+  codes_lo = e2m1x4_sr(lo[0], lo[1], lo[2], lo[3], rb0) | (e2m1x4_sr(lo[4], lo[5], lo[6], lo[7], rb1) << 16);
+  // the neighbouring column gets its own bits (a rotation keeps them decorrelated enough for rounding)
+  const uint32_t r2 = __funnelshift_l(rb0, rb1, 13), r3 = __funnelshift_l(rb1, rb0, 7);
+  codes_hi = e2m1x4_sr(hi[0], hi[1], hi[2], hi[3], r2) | (e2m1x4_sr(hi[4], hi[5], hi[6], hi[7], r3) << 16);
+}
+
 // ---- MXFP8 scale arithmetic ----
 // ceil(log2(amax/448)) clamped to [-127, 127], from the bits of the fp32 quotient.
 __device__ __forceinline__ int e8m0_exponent(float amax) {

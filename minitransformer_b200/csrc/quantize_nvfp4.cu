@@ -106,9 +106,11 @@ struct Nvfp4Args {
   const float* amax_col;
   uint8_t *q, *s, *s_swz, *q_t, *s_t, *s_t_swz;
   int* status;
+  uint64_t seed;        // stochastic rounding only
 };
 
-template <bool kTranspose, bool k2D, bool kRHT>
+// kSR: codes are rounded stochastically (cvt.rs) instead of to nearest-even; scales are unchanged.
+template <bool kTranspose, bool k2D, bool kRHT, bool kSR = false>
 __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_constant__ CUtensorMap in_map,
                                                                    const Nvfp4Args a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -177,9 +179,15 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
     float enc;
     nvfp4_block_scale_lut(vmax, g_row.ges, sm.lut_row, sbyte, enc);
     uint2 codes;
-    codes.x = e2m1x8_from_words(w0.x, w0.y, w0.z, w0.w, enc, fuse_row);
-    codes.y = e2m1x8_from_words(w1.x, w1.y, w1.z, w1.w, enc, fuse_row);
     const int64_t gr = m0 + r, gc = k0 + b * 16;
+    if (kSR) {
+      const uint64_t grp = (uint64_t)(gr * a.cols + gc) >> 2;     // groups of four consecutive elements
+      codes.x = e2m1x8_from_words_sr(w0.x, w0.y, w0.z, w0.w, enc, fuse_row, sr_bits(a.seed, grp), sr_bits(a.seed, grp + 1));
+      codes.y = e2m1x8_from_words_sr(w1.x, w1.y, w1.z, w1.w, enc, fuse_row, sr_bits(a.seed, grp + 2), sr_bits(a.seed, grp + 3));
+    } else {
+      codes.x = e2m1x8_from_words(w0.x, w0.y, w0.z, w0.w, enc, fuse_row);
+      codes.y = e2m1x8_from_words(w1.x, w1.y, w1.z, w1.w, enc, fuse_row);
+    }
     if (gr < a.rows && gc < a.cols)
       *reinterpret_cast<uint2*>(a.q + gr * (a.cols >> 1) + (gc >> 1)) = codes;
     sm.s_lin[r][b] = static_cast<uint8_t>(sbyte);
@@ -215,9 +223,16 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
       nvfp4_block_scale_lut(vmax_hi, g_col.ges, sm.lut_col, sb_hi, enc_hi);
       const f32x2_t enc2 = pack2(enc_lo, enc_hi);
       uint2 c_lo, c_hi;
-      e2m1x8_two_columns(&wp[p][0], enc2, fuse_col, c_lo.x, c_hi.x);
-      e2m1x8_two_columns(&wp[p][8], enc2, fuse_col, c_lo.y, c_hi.y);
       const int col = lane * 4 + 2 * p;
+      if (kSR) {
+        // the transposed copy draws from its own part of the counter space
+        const uint64_t grp = (((uint64_t)(k0 + col) * (uint64_t)a.rows + (uint64_t)(m0 + warp * 16)) >> 2) + (1ull << 40);
+        e2m1x8_two_columns_sr(&wp[p][0], enc2, fuse_col, c_lo.x, c_hi.x, sr_bits(a.seed, grp), sr_bits(a.seed, grp + 1));
+        e2m1x8_two_columns_sr(&wp[p][8], enc2, fuse_col, c_lo.y, c_hi.y, sr_bits(a.seed, grp + 2), sr_bits(a.seed, grp + 3));
+      } else {
+        e2m1x8_two_columns(&wp[p][0], enc2, fuse_col, c_lo.x, c_hi.x);
+        e2m1x8_two_columns(&wp[p][8], enc2, fuse_col, c_lo.y, c_hi.y);
+      }
       const int slot = warp ^ (lane & 7);
       *reinterpret_cast<uint2*>(&sm.out_t[col][slot * 8]) = c_lo;
       *reinterpret_cast<uint2*>(&sm.out_t[col + 1][slot * 8]) = c_hi;
@@ -336,11 +351,11 @@ __global__ void swizzle_scales_kernel(const uint8_t* __restrict__ s, int64_t row
 
 static int64_t padded_chunks(int64_t k_blocks) { return ((k_blocks + 3) / 4 + 3) / 4 * 4; }
 
-template <bool T, bool D2, bool R>
+template <bool T, bool D2, bool R, bool SR = false>
 static int launch_nvfp4(const CUtensorMap& map, const Nvfp4Args& args, dim3 grid, cudaStream_t st) {
   static bool attr_set[MT_MAX_DEVICES] = {};
   const int slot = current_device_slot();
-  auto kern = quantize_nvfp4_kernel<T, D2, R>;
+  auto kern = quantize_nvfp4_kernel<T, D2, R, SR>;
   const int smem = (int)sizeof(Nvfp4Smem) + 128;
   if (!attr_set[slot]) {
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -385,9 +400,12 @@ int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* am
   return MT_OK;
 }
 
-int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
-                      const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz, uint8_t* q_t,
-                      uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, mt_stream_t stream) {
+}  // extern "C"
+
+static int quantize_nvfp4_impl(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
+                               const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
+                               uint8_t* q_t, uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, bool sr, uint64_t seed,
+                               mt_stream_t stream) {
   using namespace mt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MT_REQUIRE(rows >= 0 && cols >= 0, "mt_quantize_nvfp4: negative shape");
@@ -401,6 +419,7 @@ int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, cons
   MT_REQUIRE(!transpose || (s_t && amax_col), "mt_quantize_nvfp4: q_t given without s_t / amax_col");
   MT_REQUIRE(!transpose || rows % 2 == 0, "mt_quantize_nvfp4: the transposed copy needs an even row count (rows=%lld)", (long long)rows);
   MT_REQUIRE(!(d2 && rht), "mt_quantize_nvfp4: 2-D scaling together with the Hadamard transform is not supported");
+  MT_REQUIRE(!(sr && d2), "mt_quantize_nvfp4_sr: stochastic rounding is offered for 1x16 blocks only");
   MT_REQUIRE(!rht || rows % 16 == 0, "mt_quantize_nvfp4: the Hadamard transform needs rows %% 16 == 0");
   MT_REQUIRE(s_stride >= cols / 16 && (!transpose || s_t_stride >= (rows + 15) / 16), "mt_quantize_nvfp4: scale stride too small");
   MT_REQUIRE((!s_swz || aligned16(s_swz)) && (!s_t_swz || aligned16(s_t_swz)), "mt_quantize_nvfp4: swizzled scale buffers must be 16-byte aligned");
@@ -417,18 +436,40 @@ int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, cons
   args.q = q; args.s = s; args.s_swz = s_swz; args.q_t = q_t; args.s_t = s_t; args.s_t_swz = s_t_swz;
   args.status = device_status_ptr();
   if (!args.status) return fail(MT_ERR_CUDA, "device status word not reachable");
+  args.seed = seed;
 
   CUtensorMap map;
   int rc = make_tensor_map_2d(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, (uint64_t)cols, (uint64_t)rows,
                               (uint64_t)cols * 2, QT_COLS, QT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc != MT_OK) return rc;
   dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
+  if (sr) {
+    if (!transpose) return launch_nvfp4<false, false, false, true>(map, args, grid, st);
+    return rht ? launch_nvfp4<true, false, true, true>(map, args, grid, st)
+               : launch_nvfp4<true, false, false, true>(map, args, grid, st);
+  }
   if (!transpose) {
     return d2 ? launch_nvfp4<false, true, false>(map, args, grid, st) : launch_nvfp4<false, false, false>(map, args, grid, st);
   }
   if (d2) return launch_nvfp4<true, true, false>(map, args, grid, st);
   if (rht) return launch_nvfp4<true, false, true>(map, args, grid, st);
   return launch_nvfp4<true, false, false>(map, args, grid, st);
+}
+
+extern "C" {
+
+int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
+                      const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz, uint8_t* q_t,
+                      uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, mt_stream_t stream) {
+  return quantize_nvfp4_impl(x, rows, cols, flags, amax_row, amax_col, q, s, s_stride, s_swz, q_t, s_t, s_t_stride,
+                             s_t_swz, false, 0, stream);
+}
+
+int mt_quantize_nvfp4_sr(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
+                         const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz, uint8_t* q_t,
+                         uint8_t* s_t, int64_t s_t_stride, uint8_t* s_t_swz, uint64_t seed, mt_stream_t stream) {
+  return quantize_nvfp4_impl(x, rows, cols, flags, amax_row, amax_col, q, s, s_stride, s_swz, q_t, s_t, s_t_stride,
+                             s_t_swz, true, seed, stream);
 }
 
 int mt_swizzle_scales(const uint8_t* s, int64_t rows, int64_t k_blocks, int64_t s_stride, uint8_t* s_swz,

@@ -89,9 +89,9 @@ def quantized_shard_bytes(fmt: str, rows: int, cols: int):
 
 def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with_rht: bool = False,
                    return_transpose: bool = True, amax_row: Optional[torch.Tensor] = None,
-                   amax_col: Optional[torch.Tensor] = None, into=None) -> Quantized:
+                   amax_col: Optional[torch.Tensor] = None, into=None, sr_seed: Optional[int] = None) -> Quantized:
     """`into` (optional): dict of uint8 byte ranges for "q", "s_swz", "q_t", "s_t_swz" that the
-    kernel writes instead of fresh tensors."""
+    kernel writes instead of fresh tensors. sr_seed: round the codes stochastically with this seed."""
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     M, K = x.shape
@@ -114,9 +114,14 @@ def quantize_nvfp4(x: torch.Tensor, *, tile=(1, 16), with_2d: bool = False, with
         q_t = _out_bytes(into, "q_t", (K, M // 2), dev)
         s_t = torch.empty((cols_s, mb), dtype=u8, device=dev)
         s_t_swz = _out_bytes(into, "s_t_swz", (swizzled_scale_bytes(K, mb),), dev)
-    _lib.call("mt_quantize_nvfp4", x.data_ptr(), M, K, flags, amax_row.data_ptr(), _ptr(amax_col),
-              q.data_ptr(), s.data_ptr(), K // 16, s_swz.data_ptr(),
-              _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
+    if sr_seed is None:
+        _lib.call("mt_quantize_nvfp4", x.data_ptr(), M, K, flags, amax_row.data_ptr(), _ptr(amax_col),
+                  q.data_ptr(), s.data_ptr(), K // 16, s_swz.data_ptr(),
+                  _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), _stream())
+    else:
+        _lib.call("mt_quantize_nvfp4_sr", x.data_ptr(), M, K, flags, amax_row.data_ptr(), _ptr(amax_col),
+                  q.data_ptr(), s.data_ptr(), K // 16, s_swz.data_ptr(),
+                  _ptr(q_t), _ptr(s_t), mb, _ptr(s_t_swz), int(sr_seed) & 0xFFFFFFFFFFFFFFFF, _stream())
     _count(1 if x.numel() else 0)
     return Quantized(q, s, s_swz, q_t, s_t, s_t_swz, amax_row, amax_col if return_transpose else amax_row)
 

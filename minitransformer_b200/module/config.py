@@ -71,14 +71,16 @@ class QuantizeRecipe(enum.Enum):
     # additions of this implementation
     MXFP8_SUB_CHANNEL = "mxfp8_subchannel_scaling"
     FP4_SUB_CHANNEL_NO_RHT = "fp4_subchannel_scaling_no_rht"
+    FP4_SUB_CHANNEL_SR = "fp4_subchannel_scaling_sr"      # gradients rounded stochastically
 
 
-def _nvfp4_params(with_rht: bool, allgather_quantize: bool = True) -> QLinearParams:
+def _nvfp4_params(with_rht: bool, allgather_quantize: bool = True, grad_sr: bool = False) -> QLinearParams:
     act = QParams(output_dtype=torch.uint8, scaling_dtype=torch.float8_e4m3fn, quant_tile_shape=(1, 16),
                   with_2d_quantization=False, with_rht=with_rht)
+    grad = dataclasses.replace(act, stochastic_rounding=True) if grad_sr else act
     wgt = QParams(output_dtype=torch.uint8, scaling_dtype=torch.float8_e4m3fn, quant_tile_shape=(16, 16),
                   with_2d_quantization=False, with_rht=False)
-    return QLinearParams(quantize=True, quantize_type=QuantizeType.NVFP4, x_params=act, w_params=wgt, g_params=act,
+    return QLinearParams(quantize=True, quantize_type=QuantizeType.NVFP4, x_params=act, w_params=wgt, g_params=grad,
                          quantize_op=Nvfp4TiledQuantizeOp(), allgather_quantize=allgather_quantize)
 
 
@@ -99,6 +101,8 @@ def get_qlinear_params_from_predefined(recipe: QuantizeRecipe) -> QLinearParams:
         return _nvfp4_params(with_rht=True)
     if recipe == QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT:
         return _nvfp4_params(with_rht=False)
+    if recipe == QuantizeRecipe.FP4_SUB_CHANNEL_SR:
+        return _nvfp4_params(with_rht=True, grad_sr=True)
     if recipe == QuantizeRecipe.MXFP8_SUB_CHANNEL:
         return _mxfp8_params()
     raise ValueError(f"Unsupported quantize recipe: {recipe}")
@@ -107,12 +111,12 @@ def get_qlinear_params_from_predefined(recipe: QuantizeRecipe) -> QLinearParams:
 def get_qlinear_params_from_env_qat_params() -> QLinearParams:
     """QAT_PARAMS: 1 = bf16, 3 = NVFP4 (the reference's working indices,
     miniTransformer/module/config.py:181-201); 4 = MXFP8, 5 = NVFP4 without the Hadamard
-    transform (additions). Anything else is an error, as in the reference."""
+    transform, 6 = NVFP4 with stochastically rounded gradients (additions). Anything else is an error, as in the reference."""
     raw = os.environ.get("QAT_PARAMS")
     if not raw:
         raise ValueError("QAT_PARAMS is not set; use 1 (bf16), 3 (NVFP4), 4 (MXFP8) or 5 (NVFP4, no RHT)")
     table = {1: QuantizeRecipe.NON_QUANTIZE, 3: QuantizeRecipe.FP4_SUB_CHANNEL, 4: QuantizeRecipe.MXFP8_SUB_CHANNEL,
-             5: QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT}
+             5: QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT, 6: QuantizeRecipe.FP4_SUB_CHANNEL_SR}
     idx = int(raw)
     if idx not in table:
         raise ValueError(f"Unsupported QAT_PARAMS index: {idx}")

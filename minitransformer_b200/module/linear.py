@@ -87,6 +87,10 @@ def _env_flag(name: str, default: bool) -> bool:
     return default if v is None else v not in ("0", "")
 
 
+def _sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count if torch.device(device).type == "cuda" else 0
+
+
 def _margin_for(handles) -> int:
     """SMs a GEMM leaves idle for the exchanges behind `handles`: a resident GEMM CTA fills its
     SM (shared memory and registers), so a collective or copy kernel that should run beside the
@@ -127,6 +131,15 @@ def _scatter_possible(pg, M, N, out_dtype, bias, world) -> bool:
     256-row tiles, a tile-kernel shape, and no bias inside the GEMM."""
     return (pg is not None and out_dtype == torch.bfloat16 and bias is None and M % (256 * world) == 0
             and N % 8 == 0 and N > 128 and M > 128)
+
+
+def _scatter_is_link_bound(M, N, K, world) -> bool:
+    """Whether a scattering GEMM spends more time pushing its output over NVLink (bf16 rows of the
+    other ranks at about 600 GB/s) than computing (about 4.5 PFLOP/s): only then is there tensor
+    time to give to a second GEMM running beside it."""
+    link_s = M * N * 2.0 * (world - 1) / world / 600e9
+    gemm_s = 2.0 * M * N * K / 4.5e15
+    return link_s > 1.3 * gemm_s
 
 
 def _gemm_reduce_scatter(pg, gemm, M, N, site, out_meta=None, defer=False):
@@ -192,6 +205,12 @@ class _QuantizedLinear(torch.autograd.Function):
         # weights are re-quantized on the first microbatch (or when the caller gives no hint),
         # unless the layer keeps its quantized weights until told to refresh them
         keep = bool(getattr(weight_qresult_cache, "keep", False)) and weight_qresult_cache.data is not None
+        ready = getattr(weight_qresult_cache, "prefetched", None)
+        if ready is not None and weight_qresult_cache.data is not None:
+            # quantized ahead of this call on another stream (Linear.prefetch_quantized_weight)
+            weight_qresult_cache.prefetched = None
+            torch.cuda.current_stream().wait_event(ready)
+            keep = True
         if not keep and (is_first_microbatch or is_first_microbatch is None or weight_qresult_cache.data is None):
             qres_w = op.quantize(w, qlinear_params.w_params, return_transpose=True)
             weight_qresult_cache.store(qres_w)
@@ -292,48 +311,66 @@ class _QuantizedLinear(torch.autograd.Function):
                             accumulate=False, global_amax_qx=qres_dy.global_amax_row, global_amax_qw=amax_w_col,
                             qparams_x=p.g_params, qparams_w=p.w_params)
 
-        # a gather of dy^T or of x^T (memory-saving mode) may be in flight: leave it SMs
-        finish_dgrad = None
-        with _sm_margin(op, _overlap_sm_margin() if pending_x_t is not None else _margin_for(dy_t_handles)):
-            if scatter:
-                # the tiles travel to their owners while the GEMM runs; the barrier and the local
-                # sum wait until the wgrad GEMM has been enqueued behind it
-                finish_dgrad = _gemm_reduce_scatter(pg_rs, dgrad_gemm, M, N, f"{site}:dx", defer=True)
-                dgrad = None
-            else:
-                dgrad = dgrad_gemm()
-        for h in tuple(dy_t_handles) + tuple(getattr(ctx, "x_t_handles", ())):
-            h.wait()
-
-        if pending_x_t is not None:
-            qx_t, sx_t = _QuantizedLinear._finish_gather_transposed(pending_x_t, ctx.tp_group)
-
-        handle = None
-        if scatter:
-            pass
-        elif ctx.parallel_mode == "column" and ctx.sequence_parallel:
-            dgrad, handle = reduce_scatter_along_first_dim(dgrad, ctx.tp_group, True)
-        elif ctx.parallel_mode == "column" and ctx.tp_size > 1:
-            dgrad, handle = allreduce(dgrad, ctx.tp_group, True)
-
-        wgrad = None
-        if w.requires_grad:
+        def run_wgrad(margin):
             if ctx.is_first_microbatch is not None:
                 accumulate = ctx.fuse_wgrad_accumulation and not ctx.is_first_microbatch
             else:
                 accumulate = ctx.fuse_wgrad_accumulation
             main_grad = w.main_grad if ctx.fuse_wgrad_accumulation else None
-            # a reduce-scatter / all-reduce of dgrad is in flight: leave it SMs to run on
-            margin = _overlap_sm_margin() if handle is not None else 0
             with _sm_margin(op, margin):
-                wgrad = op.qgemm(qres_dy.data_t, qx_t, p.mm_wgrad,
-                                 # without main_grad: the parameter's type, what autograd would cast an
-                                 # fp32 gradient to (one rounding of the fp32 accumulator either way)
-                                 main_grad.dtype if main_grad is not None else (p.mm_wgrad.out_dtype or w.dtype),
-                                 qres_dy.scale_t, sx_t, None, out=main_grad, accumulate=accumulate,
-                                 global_amax_qx=qres_dy.global_amax_col, global_amax_qw=amax_x_col,
-                                 qparams_x=p.g_params, qparams_w=p.x_params)
-            wgrad = _QuantizedLinear.reset_wgrad_if_needed(ctx, w, wgrad)
+                return op.qgemm(qres_dy.data_t, qx_t_box[0], p.mm_wgrad,
+                                # without main_grad: the parameter's type, what autograd would cast an
+                                # fp32 gradient to (one rounding of the fp32 accumulator either way)
+                                main_grad.dtype if main_grad is not None else (p.mm_wgrad.out_dtype or w.dtype),
+                                qres_dy.scale_t, qx_t_box[1], None, out=main_grad, accumulate=accumulate,
+                                global_amax_qx=qres_dy.global_amax_col, global_amax_qw=amax_x_col,
+                                qparams_x=p.g_params, qparams_w=p.x_params)
+
+        qx_t_box = [qx_t, sx_t]
+        finish_dgrad, wgrad, handle = None, None, None
+        late_handles = tuple(dy_t_handles) + tuple(getattr(ctx, "x_t_handles", ()))
+        if (scatter and w.requires_grad and pending_x_t is None and _env_flag("MT_TP_CONCURRENT_WGRAD", True)
+                and _scatter_is_link_bound(M, N, qres_dy.data.shape[1] * (2 if qres_dy.data.dtype == torch.uint8 else 1),
+                                           get_distributed_world_size(ctx.tp_group))):
+            # The dgrad GEMM that scatters its rows over NVLink is bound by the links, not by the
+            # tensor cores: the wgrad GEMM runs beside it on a second stream, each on half of the
+            # SMs, instead of behind it.
+            for h in late_handles:
+                h.wait()
+            half = _sm_count(dy.device) // 2
+            box = []
+            joined = pg_rs.on_side_stream(lambda: box.append(run_wgrad(half)))
+            with _sm_margin(op, half):
+                finish_dgrad = _gemm_reduce_scatter(pg_rs, dgrad_gemm, M, N, f"{site}:dx", defer=True)
+            joined.wait()
+            wgrad = _QuantizedLinear.reset_wgrad_if_needed(ctx, w, box[0])
+        else:
+            # a gather of dy^T or of x^T (memory-saving mode) may be in flight: leave it SMs
+            with _sm_margin(op, _overlap_sm_margin() if pending_x_t is not None else _margin_for(dy_t_handles)):
+                if scatter:
+                    # the tiles travel to their owners while the GEMM runs; the barrier and the local
+                    # sum wait until the wgrad GEMM has been enqueued behind it
+                    finish_dgrad = _gemm_reduce_scatter(pg_rs, dgrad_gemm, M, N, f"{site}:dx", defer=True)
+                    dgrad = None
+                else:
+                    dgrad = dgrad_gemm()
+            for h in late_handles:
+                h.wait()
+
+            if pending_x_t is not None:
+                qx_t_box[0], qx_t_box[1] = _QuantizedLinear._finish_gather_transposed(pending_x_t, ctx.tp_group)
+
+            if scatter:
+                pass
+            elif ctx.parallel_mode == "column" and ctx.sequence_parallel:
+                dgrad, handle = reduce_scatter_along_first_dim(dgrad, ctx.tp_group, True)
+            elif ctx.parallel_mode == "column" and ctx.tp_size > 1:
+                dgrad, handle = allreduce(dgrad, ctx.tp_group, True)
+
+            if w.requires_grad:
+                # a reduce-scatter / all-reduce of dgrad is in flight: leave it SMs to run on
+                wgrad = run_wgrad(_overlap_sm_margin() if handle is not None else 0)
+                wgrad = _QuantizedLinear.reset_wgrad_if_needed(ctx, w, wgrad)
 
         if handle is not None:
             handle.wait()
@@ -666,6 +703,36 @@ class Linear(LayerLinearBaseModule):
         self.weight_qresult_cache = quantization.QuantizeResultCache()
         # a row-parallel bias can only be added after the collective
         self.gemm_bias_unfused_add = parallel_mode == "row" and self.apply_bias
+
+    _prefetch_streams: Dict[int, "torch.cuda.Stream"] = {}
+
+    def prefetch_quantized_weight(self) -> None:
+        """Quantizes the current weight now, on a side stream, for the next forward call, which
+        then uses these copies instead of quantizing on its own stream (whatever
+        is_first_microbatch says). A training loop calls it for the layers of a block once the
+        optimizer has updated them, e.g. at the start of the step: the quantize passes of all
+        weights then run beside the first layers' activation work instead of between their
+        GEMMs."""
+        if not self.qlinear_params.quantize:
+            return
+        weight = noop_cat([getattr(self, n) for n in self.weight_names]).detach()
+        dev = weight.device
+        side = Linear._prefetch_streams.get(dev.index)
+        if side is None:
+            side = Linear._prefetch_streams[dev.index] = torch.cuda.Stream(device=dev)
+        main = torch.cuda.current_stream(dev)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            q = self.qlinear_params.quantize_op.quantize(weight, self.qlinear_params.w_params, return_transpose=True)
+            ev = torch.cuda.Event()
+            ev.record(side)
+        if not torch.cuda.is_current_stream_capturing():
+            for t in (q.data, q.scale, q.data_t, q.scale_t, q.global_amax_row, q.global_amax_col, q.scale_swz,
+                      q.scale_t_swz):
+                if t is not None:
+                    t.record_stream(main)      # produced on the side stream, consumed on this one
+        self.weight_qresult_cache.store(q)
+        self.weight_qresult_cache.prefetched = ev
 
     def reset_parameters(self, defer_init=False):
         super().reset_parameters(defer_init=defer_init)

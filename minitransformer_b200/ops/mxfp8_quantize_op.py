@@ -10,7 +10,7 @@ import torch
 
 from .. import kernels
 from . import quantization as Q
-from .nvfp4_quantize_op import _as_2d_bf16, _swizzled
+from .nvfp4_quantize_op import _as_2d_bf16, _gemm_dtype, _swizzled
 
 mxfp8_output_t = torch.float8_e4m3fn
 mxfp8_scale_t = torch.uint8  # E8M0 byte = exponent + 127
@@ -48,9 +48,15 @@ class Mxfp8QuantizeOp(Q.QuantizeOpBase):
         if out is not None:
             assert out.dtype == out_dtype, "output dtype mismatch"
         M, N = qx.shape[-2], qw.shape[-2]   # a 3-D operand is [K slabs, rows, bytes per slab row]
-        return kernels.gemm_mxfp8(qx.view(torch.uint8), _swizzled(sx, M), qw.view(torch.uint8), _swizzled(sw, N),
-                                  out_dtype=out_dtype, out=out, accumulate=accumulate,
-                                  bias=bias if bias is not None and bias.numel() else None)
+        bias = bias if bias is not None and bias.numel() else None
+        kdt = _gemm_dtype(out_dtype)
+        if kdt != out_dtype:
+            assert out is None, "in-place output needs a bf16 or fp32 tensor"
+        if bias is not None and bias.dtype not in (torch.bfloat16, torch.float32):
+            bias = bias.float()
+        y = kernels.gemm_mxfp8(qx.view(torch.uint8), _swizzled(sx, M), qw.view(torch.uint8), _swizzled(sw, N),
+                               out_dtype=kdt, out=out, accumulate=accumulate, bias=bias)
+        return y if kdt == out_dtype or not isinstance(y, torch.Tensor) else y.to(out_dtype)
 
     # ---- grouped (per-expert) operations used by GroupedLinear ----
     def grouped_quantize(self, w: torch.Tensor, qparams, return_transpose: bool = False) -> Q.QuantizeResult:

@@ -19,12 +19,22 @@ nvfp4_scale_t = torch.float8_e4m3fn
 
 
 def _as_2d_bf16(x: torch.Tensor) -> torch.Tensor:
+    """The kernels read bf16. fp32 / fp16 tensors (the reference module accepts them,
+    miniTransformer/module/linear.py:864-870) are rounded to bf16 first, one extra pass; the
+    bit-exact contract with the reference emulation holds for bf16 inputs only."""
     if x.dim() > 2:
         x = x.reshape(-1, x.shape[-1])
-    if x.dtype != torch.bfloat16:
-        raise kernels._lib.MtError(
-            f"the sm_100a quantize kernels take bf16 inputs, got {x.dtype}; cast explicitly if that is intended")
+    if x.dtype in (torch.float32, torch.float16):
+        x = x.to(torch.bfloat16)
+    elif x.dtype != torch.bfloat16:
+        raise kernels._lib.MtError(f"the sm_100a quantize kernels take bf16 / fp16 / fp32 inputs, got {x.dtype}")
     return x.contiguous()
+
+
+def _gemm_dtype(out_dtype: torch.dtype) -> torch.dtype:
+    """Type the GEMM kernel writes for a requested output type: bf16 and fp32 natively, anything
+    else (fp16) through fp32 and a cast."""
+    return out_dtype if out_dtype in (torch.bfloat16, torch.float32) else torch.float32
 
 
 def _swizzled(scale: torch.Tensor, rows: int) -> torch.Tensor:
@@ -38,6 +48,13 @@ def _swizzled(scale: torch.Tensor, rows: int) -> torch.Tensor:
 
 class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
     format_name = "nvfp4"
+    _sr_calls = 0
+
+    def _next_sr_seed(self) -> int:
+        """A fresh seed per stochastic-rounding call, derived from torch's seed so that a run is
+        reproducible (a captured graph replays the seed it was captured with)."""
+        Nvfp4TiledQuantizeOp._sr_calls += 1
+        return (torch.initial_seed() * 0x9E3779B97F4A7C15 + Nvfp4TiledQuantizeOp._sr_calls * 0xD1B54A32D192ED03) & (2 ** 64 - 1)
 
     @property
     def supports_allgather(self) -> bool:
@@ -70,7 +87,8 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
                 allreduce_max_(both, tp_group)
         r = kernels.quantize_nvfp4(x, tile=qparams.quant_tile_shape, with_2d=qparams.with_2d_quantization,
                                    with_rht=rht, return_transpose=return_transpose,
-                                   amax_row=amax_row, amax_col=amax_col, into=getattr(input_meta, "into", None))
+                                   amax_row=amax_row, amax_col=amax_col, into=getattr(input_meta, "into", None),
+                                   sr_seed=self._next_sr_seed() if getattr(qparams, "stochastic_rounding", False) else None)
         scale = r.scale.view(nvfp4_scale_t)
         scale._mt_swz = r.scale_swz
         scale_t = None
@@ -94,6 +112,12 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
         if out is not None:
             assert out.dtype == out_dtype, "output dtype mismatch"
         M, N = qx.shape[-2], qw.shape[-2]   # a 3-D operand is [K slabs, rows, bytes per slab row]
-        return kernels.gemm_nvfp4(qx, _swizzled(sx, M), global_amax_qx, qw, _swizzled(sw, N), global_amax_qw,
-                                  out_dtype=out_dtype, out=out, accumulate=accumulate,
-                                  bias=bias if bias is not None and bias.numel() else None)
+        bias = bias if bias is not None and bias.numel() else None
+        kdt = _gemm_dtype(out_dtype)
+        if kdt != out_dtype:
+            assert out is None, "in-place output needs a bf16 or fp32 tensor"
+        if bias is not None and bias.dtype not in (torch.bfloat16, torch.float32):
+            bias = bias.float()
+        y = kernels.gemm_nvfp4(qx, _swizzled(sx, M), global_amax_qx, qw, _swizzled(sw, N), global_amax_qw,
+                               out_dtype=kdt, out=out, accumulate=accumulate, bias=bias)
+        return y if kdt == out_dtype or not isinstance(y, torch.Tensor) else y.to(out_dtype)

@@ -22,6 +22,9 @@ class QParams:
         on amax. pow_2_scales: block scales are powers of two (MXFP8). quant_tile_shape:
         (rows, cols) of one scale block. with_2d_quantization: one scale per 16x16 block.
         with_rht: 16-point randomized Hadamard transform on the transposed copy.
+        stochastic_rounding (an addition; the reference carries the device code compiled out,
+        miniTransformer/csrc/util/ptx.cuh:222-260): E2M1 codes are rounded stochastically, for
+        gradients.
     """
     scaling_dtype: Optional[torch.dtype] = None
     output_dtype: Optional[torch.dtype] = None
@@ -30,6 +33,7 @@ class QParams:
     quant_tile_shape: Optional[Tuple[int, int]] = None
     with_2d_quantization: bool = False
     with_rht: bool = False
+    stochastic_rounding: bool = False
 
 
 @dataclasses.dataclass(frozen=True)

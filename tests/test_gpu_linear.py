@@ -339,3 +339,56 @@ def test_kept_quantized_weights_and_their_checkpoint(recipe):
     lin.refresh_quantized_weights()
     assert torch.equal(lin(x).detach(), 2 * y0)  # now the doubled weight: same codes, doubled scale
     assert K.read_device_status() == 0
+
+
+def test_prefetched_weight_quantization_gives_the_same_step():
+    """prefetch_quantized_weight() moves the weight's quantize pass to a side stream ahead of the
+    forward call; outputs and gradients are those of the ordinary call."""
+    M, Kd, N = 512, 1024, 768
+    tx, _ = seeded_bf16((M, Kd), 91)
+    tw, _ = seeded_bf16((N, Kd), 92, 0.02)
+    tdy, _ = seeded_bf16((M, N), 93, 1e-3)
+    outs = []
+    for prefetch in (False, True):
+        lin = _make_linear(Kd, N, config.QuantizeRecipe.FP4_SUB_CHANNEL, tw.cuda())
+        x = tx.cuda().requires_grad_(True)
+        if prefetch:
+            lin.prefetch_quantized_weight()
+        y = lin(x, is_first_microbatch=True)
+        y.backward(tdy.cuda())
+        outs.append((y.detach(), x.grad, lin.weight.grad))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert K.read_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_linear_accepts_fp32_and_fp16_activations(dtype):
+    """The reference module takes fp32 / fp16 / bf16 activations with parameters of the same type
+    (its own module grid runs fp32 as well). Here such inputs are rounded to bf16 before the
+    quantize kernels, so the result equals the bf16 layer on the rounded tensors, returned in the
+    caller's type."""
+    M, Kd, N = 256, 512, 384
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, Kd, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, Kd, generator=g) * 0.02).to(dtype).cuda()
+    dy = (torch.randn(M, N, generator=g) * 1e-3).to(dtype).cuda()
+    params = config.get_qlinear_params_from_predefined(config.QuantizeRecipe.FP4_SUB_CHANNEL)
+    lin = Linear(Kd, N, bias=True, params_dtype=dtype, device="cuda", qlinear_params=params)
+    with torch.no_grad():
+        lin.weight.copy_(w)
+        lin.bias.fill_(0.25)
+    xd = x.clone().requires_grad_(True)
+    y = lin(xd)
+    y.backward(dy)
+    assert y.dtype == dtype and xd.grad.dtype == dtype and lin.weight.grad.dtype == dtype
+    ref = _make_linear(Kd, N, config.QuantizeRecipe.FP4_SUB_CHANNEL, w.to(torch.bfloat16))
+    xr = x.to(torch.bfloat16).requires_grad_(True)
+    yr = ref(xr)
+    yr.backward(dy.to(torch.bfloat16))
+    tol = 1e-2 if dtype == torch.float16 else 5e-3     # the bf16 layer rounds its outputs to bf16
+    assert _relf(y - 0.25, yr.float().cpu().numpy()) <= tol
+    assert _relf(xd.grad, xr.grad.float().cpu().numpy()) <= tol
+    assert _relf(lin.weight.grad, ref.weight.grad.float().cpu().numpy()) <= tol
+    assert torch.allclose(lin.bias.grad.float(), dy.float().sum(0), rtol=1e-2, atol=1e-4)
+    assert K.read_device_status() == 0

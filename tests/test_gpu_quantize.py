@@ -170,3 +170,49 @@ def test_empty_input_is_a_no_op():
     assert r.data.shape == (0, 32) and float(r.amax_row.cpu()) == 0.0
     r = K.quantize_mxfp8(x)
     assert r.data.shape == (0, 64)
+
+
+def test_nvfp4_stochastic_rounding_is_unbiased_and_brackets_the_exact_value():
+    """mt_quantize_nvfp4_sr (parity unpinned: the reference ships this path compiled out): scale
+    bytes are those of the nearest-even cast; every code is one of the two E2M1 neighbours of the
+    scaled element; averaged over seeds the dequantized value converges to the input (the
+    nearest-even cast keeps a bias the average of stochastic casts must not have); one seed gives
+    one result."""
+    from oracle import formats as F
+    M, Kd = 128, 256
+    t, x = seeded_bf16((M, Kd), 77, 1e-3)
+    xt = t.cuda()
+    base = K.quantize_nvfp4(xt, with_rht=False)
+    grid = np.sort(np.unique(np.abs(F.E2M1_VALUES)))                    # 0, 0.5, 1, 1.5, 2, 3, 4, 6
+    sc = F.e4m3_decode(np_u8(base.scale)[:M])
+    amax = float(base.amax_row.cpu())
+    ges = np.float32(448.0 * 6.0) / np.float32(amax)
+    scale_el = np.repeat(sc, 16, axis=1) / ges                          # decode factor of every element
+    scaled = x / scale_el                                               # what the codes approximate, in E2M1 units
+    acc = np.zeros_like(x, dtype=np.float64)
+    acc_t = np.zeros((Kd, M), dtype=np.float64)
+    n_seeds = 48
+    clipped = np.minimum(np.abs(scaled), 6.0)
+    lo = grid[np.searchsorted(grid, clipped, side="right") - 1]
+    hi = grid[np.searchsorted(grid, clipped, side="left")]
+    for seed in range(n_seeds):
+        r = K.quantize_nvfp4(xt, with_rht=False, amax_row=base.amax_row, amax_col=base.amax_col, sr_seed=1000 + seed)
+        assert torch.equal(r.scale, base.scale) and torch.equal(r.scale_t, base.scale_t)
+        vals = F.unpack_e2m1(np_u8(r.data))
+        mag = np.abs(vals)
+        assert np.all((mag == lo) | (mag == hi)), "a code is not a neighbour of the exact value"
+        assert np.all((np.sign(vals) == np.sign(scaled)) | (vals == 0))
+        acc += vals * scale_el
+        acc_t += F.unpack_e2m1(np_u8(r.data_t)).astype(np.float64)
+    mean = acc / n_seeds
+    rn = F.unpack_e2m1(np_u8(base.data)) * scale_el
+    err_sr = np.abs(mean - x).mean()
+    err_rn = np.abs(rn - x).mean()
+    assert err_sr < 0.45 * err_rn, (err_sr, err_rn)                     # ~1/sqrt(48) of one rounding step
+    assert np.abs(acc_t).sum() > 0                                      # the transposed copy is rounded too
+    a = K.quantize_nvfp4(xt, with_rht=True, sr_seed=5)
+    b = K.quantize_nvfp4(xt, with_rht=True, sr_seed=5)
+    c = K.quantize_nvfp4(xt, with_rht=True, sr_seed=6)
+    assert torch.equal(a.data, b.data) and torch.equal(a.data_t, b.data_t)
+    assert not torch.equal(a.data, c.data) and not torch.equal(a.data_t, c.data_t)
+    assert K.read_device_status() == 0
