@@ -387,7 +387,7 @@ def test_linear_accepts_fp32_and_fp16_activations(dtype):
     yr = ref(xr)
     yr.backward(dy.to(torch.bfloat16))
     tol = 1e-2 if dtype == torch.float16 else 5e-3     # the bf16 layer rounds its outputs to bf16
-    assert _relf(y - 0.25, yr.float().cpu().numpy()) <= tol
+    assert _relf(y - 0.25, yr.detach().float().cpu().numpy()) <= tol
     assert _relf(xd.grad, xr.grad.float().cpu().numpy()) <= tol
     assert _relf(lin.weight.grad, ref.weight.grad.float().cpu().numpy()) <= tol
     assert torch.allclose(lin.bias.grad.float(), dy.float().sum(0), rtol=1e-2, atol=1e-4)
