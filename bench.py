@@ -177,7 +177,7 @@ def _workload_config(n):
             **C4, "parallelism": f"tp{n}", "l2": "per-rank operands exceed the 126 MB L2",
             "exchange": ("NVLink peer memory by this library's kernels (pull all-gather, GEMM epilogue that scatters rows + "
                          "local reduce)" if os.environ.get("MT_BENCH_TP_EXCHANGE", "peer") != "nccl" else "NCCL collectives"),
-            "cuda_graph": os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"}
+            "cuda_graph": os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"}   # intent; see line["cuda_graph"]
 
 
 class ClockSampler(threading.Thread):
@@ -880,14 +880,23 @@ def run_gpu_arm(args):
             graph = torch.cuda.CUDAGraph()
             x_static.grad = None
             before = kernels.LAUNCH_COUNT
-            with torch.cuda.graph(graph):
-                y_static = mlp(x_static, dy)
+            try:
+                with torch.cuda.graph(graph):
+                    y_static = mlp(x_static, dy)
+            except RuntimeError as e:       # the same on every rank: time the eager step instead
+                use_graph = False
+                if rank == 0:
+                    print(f"[bench] graph capture failed ({str(e)[:200]}); timing the eager step", file=sys.stderr)
+                torch.cuda.synchronize()
             launches_per_replay = kernels.LAUNCH_COUNT - before
 
-            def step(record):
+            def graph_step(record):
                 graph.replay()
                 kernels.LAUNCH_COUNT += launches_per_replay
                 return y_static, x_static.grad
+
+            if use_graph:
+                step = graph_step
 
         def e2e_step():
             xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
@@ -957,6 +966,8 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
         }
+        if n > 1:
+            line["cuda_graph"] = bool(use_graph)
         if n > 1 and not quick:
             line["parity"] = parity
             line["scaling_base_ms"] = base["ms_per_step"]

@@ -59,6 +59,13 @@ int64_t mt_swizzled_scale_bytes(int64_t rows, int64_t k_blocks);
 int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags,
                  float* amax_row, float* amax_col, mt_stream_t stream);
 
+/* mt_amax_bf16 that also returns the column sums of x in col_sum[cols] (fp32, overwritten;
+ * rows % 16 == 0): the bias gradient b_grad = sum over tokens of dy, taken from the pass over dy
+ * that its quantization needs anyway instead of a pass of its own
+ * (miniTransformer/module/linear.py:352). Summation order varies with scheduling (fp32 atomics). */
+int mt_amax_colsum_bf16(const void* x, int64_t rows, int64_t cols, int flags,
+                        float* amax_row, float* amax_col, float* col_sum, mt_stream_t stream);
+
 /* NVFP4 cast (+ transpose): E2M1 codes packed two per byte (even column in the low
  * nibble), one E4M3 scale per 1x16 block (or per 16x16 block with MT_Q_2D), using the
  * per-tensor abs-max values already on the device (mt_amax_bf16, optionally max-reduced

@@ -32,6 +32,7 @@ _SIGNATURES = {
     "mt_last_error_string": (_c.c_char_p, []),
     "mt_swizzled_scale_bytes": (_i64, [_i64, _i64]),
     "mt_amax_bf16": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "mt_amax_colsum_bf16": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp]),
     "mt_quantize_nvfp4": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp]),
     "mt_quantize_nvfp4_sr": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _c.c_uint64,
                                     _vp]),

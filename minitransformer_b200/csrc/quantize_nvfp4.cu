@@ -50,12 +50,17 @@ __global__ void __launch_bounds__(256) amax_plain_kernel(const uint4* __restrict
 
 // Row abs-max and abs-max of the Hadamard-transformed transpose in one read of x.
 // Lane <-> 4 adjacent columns, warp <-> 16 consecutive rows, CTA <-> 128x128 tile.
-__global__ void __launch_bounds__(256) amax_rht_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
-                                                       float* __restrict__ amax_row, float* __restrict__ amax_col) {
+// kColSum: the same read also accumulates the column sums of x (fp32 atomics into col_sum[cols]):
+// the bias gradient of a linear layer, taken from the pass over dy that its quantization needs anyway.
+template <bool kRHT, bool kColSum>
+__global__ void __launch_bounds__(256) amax_tiled_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
+                                                         float* __restrict__ amax_row, float* __restrict__ amax_col,
+                                                         float* __restrict__ col_sum) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t c0 = (int64_t)blockIdx.x * QT_COLS + lane * 4;
   const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS + warp * 16;
   float frow = 0.f, fcol = 0.f;
+  float cs[4] = {0.f, 0.f, 0.f, 0.f};
   if (c0 < cols && r0 < rows) {  // rows % 16 == 0, cols % 4 == 0: the strip is all-in or all-out
     uint32_t wa[16], wb[16];   // columns (c0, c0+1) and (c0+2, c0+3), one packed word per row
 #pragma unroll
@@ -68,25 +73,45 @@ __global__ void __launch_bounds__(256) amax_rht_kernel(const uint16_t* __restric
 #pragma unroll
     for (int j = 0; j < 16; ++j) m = absmax2(absmax2(m, wa[j]), wb[j]);
     frow = absmax2_to_float(m);
-    rht16_x2(wa);
-    rht16_x2(wb);
-    m = 0;
+    if (kColSum) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) m = absmax2(absmax2(m, wa[j]), wb[j]);
-    fcol = absmax2_to_float(m);
+      for (int j = 0; j < 16; ++j) {
+        cs[0] += bf16_lo(wa[j]); cs[1] += bf16_hi(wa[j]);
+        cs[2] += bf16_lo(wb[j]); cs[3] += bf16_hi(wb[j]);
+      }
+    }
+    if (kRHT) {
+      rht16_x2(wa);
+      rht16_x2(wb);
+      m = 0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) m = absmax2(absmax2(m, wa[j]), wb[j]);
+      fcol = absmax2_to_float(m);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     frow = fmaxf(frow, __shfl_xor_sync(0xffffffffu, frow, o));
-    fcol = fmaxf(fcol, __shfl_xor_sync(0xffffffffu, fcol, o));
+    if (kRHT) fcol = fmaxf(fcol, __shfl_xor_sync(0xffffffffu, fcol, o));
   }
   __shared__ float red[2][8];
+  __shared__ float csum[8][QT_COLS];
   if (lane == 0) { red[0][warp] = frow; red[1][warp] = fcol; }
+  if (kColSum) *reinterpret_cast<float4*>(&csum[warp][lane * 4]) = make_float4(cs[0], cs[1], cs[2], cs[3]);
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int i = 1; i < 8; ++i) { frow = fmaxf(frow, red[0][i]); fcol = fmaxf(fcol, red[1][i]); }
     atomicMax(reinterpret_cast<unsigned int*>(amax_row), __float_as_uint(frow));
-    atomicMax(reinterpret_cast<unsigned int*>(amax_col), __float_as_uint(fcol));
+    if (amax_col != nullptr) atomicMax(reinterpret_cast<unsigned int*>(amax_col), __float_as_uint(kRHT ? fcol : frow));
+  }
+  if (kColSum && threadIdx.x < QT_COLS) {
+    const int64_t c = (int64_t)blockIdx.x * QT_COLS + threadIdx.x;
+    if (c < cols) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += csum[w][threadIdx.x];
+      atomicAdd(col_sum + c, t);
+    }
   }
 }
 
@@ -368,10 +393,8 @@ static int launch_nvfp4(const CUtensorMap& map, const Nvfp4Args& args, dim3 grid
 
 }  // namespace mt
 
-extern "C" {
-
-int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* amax_row, float* amax_col,
-                 mt_stream_t stream) {
+static int amax_impl(const void* x, int64_t rows, int64_t cols, int flags, float* amax_row, float* amax_col,
+                     float* col_sum, mt_stream_t stream) {
   using namespace mt;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MT_REQUIRE(amax_row != nullptr, "mt_amax_bf16: null amax_row");
@@ -379,17 +402,24 @@ int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* am
   if (rows == 0 || cols == 0) {  // an empty tensor has abs-max 0 and may come with a null pointer
     MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
     if (amax_col) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+    if (col_sum && cols > 0) MT_CUDA(cudaMemsetAsync(col_sum, 0, sizeof(float) * cols, st));
     return MT_OK;
   }
   MT_REQUIRE(x != nullptr, "mt_amax_bf16: null x");
+  MT_REQUIRE(col_sum == nullptr || rows % 16 == 0, "mt_amax_colsum_bf16: column sums need rows %% 16 == 0 (rows=%lld)",
+             (long long)rows);
   MT_REQUIRE(aligned16(x), "mt_amax_bf16: x must be 16-byte aligned");
   const bool rht = (flags & MT_Q_RHT) && amax_col != nullptr;
   MT_REQUIRE(!rht || rows % 16 == 0, "mt_amax_bf16: the Hadamard transform needs rows %% 16 == 0 (rows=%lld)", (long long)rows);
   MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
-  if (rht) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
-  if (rht) {
+  if (rht || (col_sum && amax_col)) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+  if (col_sum) MT_CUDA(cudaMemsetAsync(col_sum, 0, sizeof(float) * cols, st));
+  if (rht || col_sum) {
     dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
-    amax_rht_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x), rows, cols, amax_row, amax_col);
+    const uint16_t* xp = static_cast<const uint16_t*>(x);
+    if (rht && col_sum) amax_tiled_kernel<true, true><<<grid, 256, 0, st>>>(xp, rows, cols, amax_row, amax_col, col_sum);
+    else if (rht) amax_tiled_kernel<true, false><<<grid, 256, 0, st>>>(xp, rows, cols, amax_row, amax_col, nullptr);
+    else amax_tiled_kernel<false, true><<<grid, 256, 0, st>>>(xp, rows, cols, amax_row, amax_col, col_sum);
   } else {
     const int64_t n_vec = rows * cols / 8;
     int blocks = (int)std::min<int64_t>((n_vec + 255) / 256, 148 * 8);
@@ -399,8 +429,6 @@ int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* am
   MT_CUDA(cudaGetLastError());
   return MT_OK;
 }
-
-}  // extern "C"
 
 static int quantize_nvfp4_impl(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
                                const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz,
@@ -457,6 +485,17 @@ static int quantize_nvfp4_impl(const void* x, int64_t rows, int64_t cols, int fl
 }
 
 extern "C" {
+
+int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* amax_row, float* amax_col,
+                 mt_stream_t stream) {
+  return amax_impl(x, rows, cols, flags, amax_row, amax_col, nullptr, stream);
+}
+
+int mt_amax_colsum_bf16(const void* x, int64_t rows, int64_t cols, int flags, float* amax_row, float* amax_col,
+                        float* col_sum, mt_stream_t stream) {
+  MT_REQUIRE(col_sum != nullptr, "mt_amax_colsum_bf16: null col_sum");
+  return amax_impl(x, rows, cols, flags, amax_row, amax_col, col_sum, stream);
+}
 
 int mt_quantize_nvfp4(const void* x, int64_t rows, int64_t cols, int flags, const float* amax_row,
                       const float* amax_col, uint8_t* q, uint8_t* s, int64_t s_stride, uint8_t* s_swz, uint8_t* q_t,

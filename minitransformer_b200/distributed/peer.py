@@ -194,6 +194,11 @@ def get_peer_group(group, device) -> Optional[PeerGroup]:
         if ok:
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
             if int(flag.item()) == 1:
-                pg = PeerGroup(group, device)
+                try:
+                    pg = PeerGroup(group, device)
+                except _lib.MtError as e:       # raised on every rank together (see _new_arena)
+                    import warnings
+                    warnings.warn(f"peer-memory exchange unavailable, keeping to the process group: {e}")
+                    pg = None
         _GROUPS[key] = pg
     return _GROUPS[key]

@@ -52,16 +52,24 @@ class Quantized:
     amax_col: Optional[torch.Tensor] = None
 
 
-def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True):
-    """Per-tensor abs-max (and abs-max of the Hadamard-transformed transpose) as device scalars."""
+def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True, col_sum: Optional[torch.Tensor] = None):
+    """Per-tensor abs-max (and abs-max of the Hadamard-transformed transpose) as device scalars.
+    col_sum (optional fp32 [cols], rows % 16 == 0): also receives the column sums of x from the
+    same read."""
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     amax = torch.empty(2, dtype=torch.float32, device=x.device)
     flags = MT_Q_RHT if with_rht else 0
-    _lib.call("mt_amax_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
-              amax[1:2].data_ptr() if need_col else None, _stream())
-    if x.numel():
-        _count(1 if with_rht else (2 if need_col else 1))
+    if col_sum is not None:
+        assert col_sum.dtype == torch.float32 and col_sum.numel() == x.shape[1] and col_sum.is_contiguous()
+        _lib.call("mt_amax_colsum_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
+                  amax[1:2].data_ptr() if need_col else None, col_sum.data_ptr(), _stream())
+        _count(1 if x.numel() else 0)
+    else:
+        _lib.call("mt_amax_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
+                  amax[1:2].data_ptr() if need_col else None, _stream())
+        if x.numel():
+            _count(1 if with_rht else (2 if need_col else 1))
     return amax[0:1], (amax[1:2] if need_col else amax[0:1])
 
 

@@ -284,14 +284,21 @@ class _QuantizedLinear(torch.autograd.Function):
             sw_t._mt_swz = ctx.sw_t_swz
         out_dtype_dgrad = p.mm_dgrad.out_dtype or dy.dtype
         dy = dy.contiguous().view(-1, dy.shape[-1])
-        b_grad = dy.sum(dim=0) if ctx.use_bias else None
+        # the bias gradient (column sums of dy) comes out of the abs-max pass that quantizing dy
+        # needs anyway, where the backend has such a pass; otherwise from a reduction of its own
+        dy_meta = None
+        if ctx.use_bias and dy.is_cuda and dy.dtype == torch.bfloat16:
+            dy_meta = quantization.QuantizeInputMeta(col_sum=torch.empty(dy.shape[1], dtype=torch.float32, device=dy.device))
 
         gather_required = ctx.parallel_mode == "row" and ctx.sequence_parallel
         pg_ag, pg_rs, site, _ = _peer_groups(ctx.ub, ctx.tp_group, dy.device)
         qres_dy = _QuantizedLinear.quantize_optionally_allgather(
             op, dy, p.g_params, transpose_required=True, allgather_required=gather_required,
             allgather_quantize=p.allgather_quantize, tp_group=ctx.tp_group, weight_shape=tuple(w.shape),
-            async_gather=True, peer_group=pg_ag, site=f"{site}:dy")
+            async_gather=True, input_meta=dy_meta, peer_group=pg_ag, site=f"{site}:dy")
+        b_grad = None
+        if ctx.use_bias:
+            b_grad = dy_meta.col_sum.to(dy.dtype) if (dy_meta is not None and dy_meta.col_sum_done) else dy.sum(dim=0)
         for h in getattr(qres_dy, "_pending_handles", ()):
             h.wait()
         dy_t_handles = getattr(qres_dy, "_pending_handles_t", ())
@@ -458,9 +465,11 @@ class _QuantizedLinear(torch.autograd.Function):
         into = {k: shared.tensor[o:o + n] for k, o, n in zip(keys, offs, sizes) if transpose_required or k in keys[:2]}
         meta = quantization.QuantizeInputMeta(
             amax=getattr(input_meta, "amax", None), amax_col=getattr(input_meta, "amax_col", None), into=into,
-            amax_reduce=pg.allreduce_max_)
+            amax_reduce=pg.allreduce_max_, col_sum=getattr(input_meta, "col_sum", None))
         r = op.quantize(x, qparams, return_transpose=transpose_required, reduce_amax=True, tp_group=tp_group,
                         input_meta=meta)
+        if meta.col_sum_done:
+            input_meta.col_sum_done = True
         pg.barrier()
         dev, u8 = x.device, torch.uint8
         data = torch.empty((world * rows, sizes[0] // rows), dtype=u8, device=dev)

@@ -76,7 +76,12 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
             both = torch.cat([known.reshape(1), (known_col if rht else known).reshape(1)])
             amax_row, amax_col = both[0:1], both[1:2]
         else:
-            amax_row, amax_col = kernels.amax_bf16(x, with_rht=rht, need_col=return_transpose)
+            col_sum = getattr(input_meta, "col_sum", None)
+            if col_sum is not None and x.shape[0] % 16 == 0 and x.shape[0] > 0:
+                input_meta.col_sum_done = True
+            else:
+                col_sum = None
+            amax_row, amax_col = kernels.amax_bf16(x, with_rht=rht, need_col=return_transpose, col_sum=col_sum)
         if reduce_amax:
             # both scalars live in one 2-element buffer: one tiny exchange
             both = amax_row._base if amax_row._base is not None else amax_row

@@ -119,10 +119,15 @@ class QuantizeInputMeta(QuantizeInputMetaBase):
     into: byte ranges ("q", "s_swz", "q_t", "s_t_swz") the outputs are written into instead of
         fresh tensors (a rank's slot of a peer all-gather buffer).
     amax_reduce: callable that MAX-reduces the 2-element abs-max buffer across the ranks in
-        place, used instead of the process-group all-reduce when reduce_amax is set."""
+        place, used instead of the process-group all-reduce when reduce_amax is set.
+    col_sum: fp32 [features] tensor that receives the column sums of the input from the
+        quantizer's abs-max pass (the bias gradient, when the input is dy); the quantizer sets
+        col_sum_done when it has filled it (formats without an abs-max pass leave it alone)."""
     amax_col: Optional[torch.Tensor] = None
     into: Optional[dict] = None
     amax_reduce: Optional[object] = None
+    col_sum: Optional[torch.Tensor] = None
+    col_sum_done: bool = False
 
 
 class QuantizeOpBase:

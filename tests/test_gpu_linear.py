@@ -392,3 +392,24 @@ def test_linear_accepts_fp32_and_fp16_activations(dtype):
     assert _relf(lin.weight.grad, ref.weight.grad.float().cpu().numpy()) <= tol
     assert torch.allclose(lin.bias.grad.float(), dy.float().sum(0), rtol=1e-2, atol=1e-4)
     assert K.read_device_status() == 0
+
+
+@pytest.mark.parametrize("recipe", [config.QuantizeRecipe.FP4_SUB_CHANNEL, config.QuantizeRecipe.FP4_SUB_CHANNEL_NO_RHT,
+                                    config.QuantizeRecipe.MXFP8_SUB_CHANNEL])
+def test_bias_gradient_from_the_quantize_pass(recipe):
+    """b_grad = sum over tokens of dy (miniTransformer/module/linear.py:352): with the NVFP4 recipes
+    it is taken from the abs-max pass of the dy quantization, with MXFP8 (no such pass) from a
+    reduction of its own; both must equal the fp64 column sums to bf16 rounding."""
+    M, Kd, N = 512, 256, 384
+    tx, _ = seeded_bf16((M, Kd), 101)
+    tw, _ = seeded_bf16((N, Kd), 102, 0.02)
+    tdy, dy = seeded_bf16((M, N), 103, 1e-3)
+    params = config.get_qlinear_params_from_predefined(recipe)
+    lin = Linear(Kd, N, bias=True, params_dtype=torch.bfloat16, device="cuda", qlinear_params=params)
+    with torch.no_grad():
+        lin.weight.copy_(tw)
+    lin(tx.cuda().requires_grad_(True)).backward(tdy.cuda())
+    want = dy.astype(np.float64).sum(0)
+    got = lin.bias.grad.float().cpu().numpy().astype(np.float64)
+    assert np.abs(got - want).max() <= 2 ** -8 * np.abs(want).max() + 1e-9
+    assert K.read_device_status() == 0

@@ -216,3 +216,21 @@ def test_nvfp4_stochastic_rounding_is_unbiased_and_brackets_the_exact_value():
     assert torch.equal(a.data, b.data) and torch.equal(a.data_t, b.data_t)
     assert not torch.equal(a.data, c.data) and not torch.equal(a.data_t, c.data_t)
     assert K.read_device_status() == 0
+
+
+@pytest.mark.parametrize("rht", [True, False])
+@pytest.mark.parametrize("shape", [(256, 384), (48, 72 * 8), (1024, 4096)])
+def test_amax_pass_also_returns_column_sums(shape, rht):
+    """mt_amax_colsum_bf16: the abs-max values are bit-identical to mt_amax_bf16 and the column sums
+    equal the fp64 sums to fp32 accumulation accuracy (the bias gradient taken from the pass over dy)."""
+    M, Kd = shape
+    t, x = seeded_bf16((M, Kd), 7, 1e-3)
+    xt = t.cuda()
+    a0, c0 = K.amax_bf16(xt, with_rht=rht)
+    col = torch.full((Kd,), 7.0, dtype=torch.float32, device="cuda")      # stale contents must be overwritten
+    a1, c1 = K.amax_bf16(xt, with_rht=rht, col_sum=col)
+    assert float(a0) == float(a1) and float(c0) == float(c1)
+    want = x.astype(np.float64).sum(0)
+    got = col.cpu().numpy().astype(np.float64)
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(x).sum(0).max() + 1e-12
+    assert K.read_device_status() == 0
