@@ -33,9 +33,9 @@ UNIT = "TFLOP/s"
 C2 = dict(tokens=8192, in_features=4096, out_features=14336)
 # DRAM bytes (read + write) per GEMM launch of this workload, average of fprop / dgrad / wgrad,
 # from a one-pass ncu capture of this script (dram__bytes_read.sum + dram__bytes_write.sum:
-# 270.4, 155.5 and 279.0 MB). Slightly below the algorithmic bytes because part of each output
+# 281.5, 167.3 and 281.4 MB). Slightly below the algorithmic bytes because part of each output
 # is still in L2 when the kernel ends.
-GEMM_DRAM_BYTES_PER_LAUNCH = 235.0e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 243.0e6
 # sm__pipe_tensor_cycles_active of the NVFP4 pair kernel under ncu (4096 x 9472 x 4096 case,
 # profiles/gemm_nvfp4_pair_4096x9472x4096.md)
 GEMM_TENSOR_PIPE_ACTIVE_PCT = 52.3
@@ -1006,7 +1006,7 @@ def run_gpu_arm(args):
             q_bytes = elts * 3.125          # the input once, every output once; the abs-max pre-pass is overhead
             q_gbs = q_bytes / (q_avg * 1e-3) / 1e9
             line["roofline_quantize"] = {
-                "bound": "hbm", "kernel": "amax_rht_kernel + quantize_nvfp4_kernel on dy (row + transposed, RHT)",
+                "bound": "hbm", "kernel": "amax_tiled_kernel<RHT> + quantize_nvfp4_kernel on dy (row + transposed, RHT)",
                 "achieved": q_gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": q_gbs / peaks["hbm"],
                 "algorithmic_bytes": q_bytes, "avg_sequence_ms": q_avg,
                 "achieved_counting_both_reads": elts * 5.125 / (q_avg * 1e-3) / 1e9,
