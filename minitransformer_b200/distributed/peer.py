@@ -46,11 +46,13 @@ class _EventHandle:
     """wait() makes the current stream wait for work recorded on another stream."""
     needs_sm_margin = True      # the copy runs on SMs of its own, which the GEMM beside it must leave free
 
-    def __init__(self, event, keep=()):
-        self.event, self.keep = event, keep
+    def __init__(self, event, keep=(), captured=False):
+        self.event, self.keep, self.captured, self.done = event, keep, captured, False
 
     def wait(self):
         torch.cuda.current_stream().wait_event(self.event)
+        self.done = True
+        self.keep = ()
 
 
 class PeerGroup:
@@ -65,6 +67,7 @@ class PeerGroup:
         self._named: Dict[str, SharedBuffer] = {}
         self._parity: Dict[str, int] = {}
         self._imported: Dict[bytes, int] = {}
+        self._side_handles: List[_EventHandle] = []
         self.side_stream = torch.cuda.Stream(device=self.device)
         self.ctrl = self.buffer("__ctrl__", _lib.MT_PEER_CTRL_BYTES)
         self.ctrl.tensor.zero_()
@@ -123,6 +126,12 @@ class PeerGroup:
         stream capture the turn cannot advance from replay to replay: the first range is used
         and a barrier is issued first, which shows that every rank is done with its last use."""
         if torch.cuda.is_current_stream_capturing():
+            # this rank's own pulls on the side stream count as "done" only once they have joined:
+            # the barrier tells the peers that their slots may be rewritten
+            for h in self._side_handles:
+                if h.captured and not h.done:
+                    h.wait()
+            self._side_handles = [h for h in self._side_handles if not h.done]
             self.barrier()
             return self.buffer(f"{name}#0", nbytes)
         p = self._parity.get(name, 0)
@@ -168,12 +177,16 @@ class PeerGroup:
         """Runs fn() on the side stream, ordered after the work already enqueued on the current
         stream; the returned handle's wait() orders later work of the current stream after it."""
         main = torch.cuda.current_stream()
+        capturing = torch.cuda.is_current_stream_capturing()
         self.side_stream.wait_stream(main)
         with torch.cuda.stream(self.side_stream):
             fn()
             ev = torch.cuda.Event()
             ev.record(self.side_stream)
-        return _EventHandle(ev, keep)
+        h = _EventHandle(ev, keep, captured=capturing)
+        if capturing:
+            self._side_handles.append(h)
+        return h
 
 
 _GROUPS: Dict[int, Optional[PeerGroup]] = {}
