@@ -353,38 +353,70 @@ __device__ __forceinline__ void store_block_staged(const GemmArgs& a, const CUte
   }
 }
 
-// The same for a scattered (peer) output, bf16 only: 32 rows x 128 bytes per store (64 columns,
-// 128-byte swizzle, the warp's whole 4 KiB buffer), because stores that cross NVLink are far
-// more efficient in 128-byte than in 64-byte segments. The buffer is refilled once the previous
-// store has read it.
+// The same with 128-byte rows: 32 rows x 128 bytes per store (64 bf16 or 32 fp32 columns, 128-byte
+// swizzle, the warp's whole 4 KiB buffer). Whole 128-byte lines per row measured 2 - 3 % faster
+// than the 64-byte halves for local outputs and are what stores across NVLink need; the buffer is
+// refilled once the previous store has read it. Used for every staged output (local or a peer's
+// staging buffer); fp32 accumulation goes through the TMA add-reduction.
 __device__ __forceinline__ void store_block_staged_wide(const GemmArgs& a, const CUtensorMap* map_d,
                                                         const uint32_t (&acc)[4][32], int ncols, uint8_t* stage,
                                                         int lane, int64_t row0, int64_t map_rows, int64_t colw,
-                                                        float alpha, bool has_k) {
+                                                        float alpha, bool has_k, AmaxAcc& am) {
   const uint32_t swz = lane & 7;
+  const bool f32 = a.d_dtype == MT_F32;
+  const bool track = a.d_amax != nullptr;
+  const int cols_per = f32 ? 32 : 64;
+  const int nchunks = ncols / cols_per;
 #pragma unroll
-  for (int ch = 0; ch < 2; ++ch) {
-    if (ch * 64 >= ncols) break;
+  for (int ch = 0; ch < 4; ++ch) {
+    if (ch >= nchunks) break;
     if (lane == 0) bulk_wait_read_all();
     __syncwarp();
+    if (!f32) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {                 // 16-byte piece j = columns 8j .. 8j+7 of the chunk
-      uint32_t w[4];
+      for (int j = 0; j < 8; ++j) {               // 16-byte piece j = columns 8j .. 8j+7 of the chunk
+        uint32_t w[4];
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int col = ch * 64 + j * 8 + t * 2;
-        const float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
-        const float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
-        __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-        w[t] = *reinterpret_cast<uint32_t*>(&h);
+        for (int t = 0; t < 4; ++t) {
+          const int col = (ch & 1) * 64 + j * 8 + t * 2;
+          float v0 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
+          float v1 = has_k ? __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])) : 0.0f;
+          if (a.bias != nullptr) {
+            const int64_t gc = colw + col;
+            if (gc < a.N) v0 += bias_at(a, gc);
+            if (gc + 1 < a.N) v1 += bias_at(a, gc + 1);
+          }
+          __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+          w[t] = *reinterpret_cast<uint32_t*>(&h);
+          if (track) amax_bf16x2(am, w[t]);
+        }
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {               // 16-byte piece j = columns 4j .. 4j+3 of the chunk
+        float v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int col = ch * 32 + j * 4 + t;
+          v[t] = has_k ? __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])) : 0.0f;
+          if (a.bias != nullptr) {
+            const int64_t gc = colw + col;
+            if (gc < a.N) v[t] += bias_at(a, gc);
+          }
+          if (track) am.f = fmaxf(am.f, fabsf(v[t]));
+        }
+        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+      }
     }
     fence_proxy_async_smem();
     __syncwarp();
-    const int64_t c0 = colw + (int64_t)ch * 64;
+    const int64_t c0 = colw + (int64_t)ch * cols_per;
     if (lane == 0) {
-      if (row0 < map_rows && c0 < a.N) tma_store_2d(map_d, stage, (int32_t)c0, (int32_t)row0);
+      if (row0 < map_rows && c0 < a.N && !MT_KNOB(a, 8)) {
+        if (f32 && a.accumulate) tma_reduce_add_2d(map_d, stage, (int32_t)c0, (int32_t)row0);
+        else tma_store_2d(map_d, stage, (int32_t)c0, (int32_t)row0);
+      }
       bulk_commit_group();
     }
   }
@@ -973,7 +1005,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
       // so a block that straddles a group boundary takes the direct, row-masked path (as do
       // unaligned outputs and bf16 accumulation).
-      const bool staged = a.tma_store == 1 && row0 >= t.d_row_lo && (row0 + 32 <= t.d_row_hi || t.hi_is_end);
+      const bool staged = a.tma_store >= 1 && row0 >= t.d_row_lo && (row0 + 32 <= t.d_row_hi || t.hi_is_end);
       if (!staged) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -989,11 +1021,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         const int dest = (int)(row0 / a.dest_rows);
         const int64_t srow = (int64_t)a.my_rank * a.dest_rows + (row0 - (int64_t)dest * a.dest_rows);
         store_block_staged_wide(a, &maps_peer.m[dest], acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, srow, a.map_rows,
-                                colw, alpha, num_k > 0);
+                                colw, alpha, num_k > 0, am);
         continue;
       }
-      store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
-                         t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
+#ifdef MT_TIMING_KNOBS
+      if (a.tma_store == 2) {   // the 64-byte-wide variant, kept for comparison
+        store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
+                           t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
+        continue;
+      }
+#endif
+      store_block_staged_wide(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
+                              t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
     }
     if (a.d_amax != nullptr) amax_publish(a.d_amax, am, lane);
   }
@@ -1145,11 +1184,20 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   args.tma_store = (allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16)) ? allow_tma_store : 0;
   args.map_rows = d_rows;
   if (args.n_dest > 1 && args.tma_store != 1) return fail(MT_ERR_INVALID_ARG, "scattered output needs the staged store path");
+  static int narrow_store = -1;   // timing-knob builds only: MT_GEMM_NARROW_STORE=1 selects the 64-byte-wide variant
+  if (narrow_store < 0) narrow_store = env_knob("MT_GEMM_NARROW_STORE", 0);
   if (args.tma_store) {
     const CUtensorMapDataType dt = d_dtype == MT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    // box: 32 rows x 64 bytes (half of a warp's staging buffer), 64-byte swizzle
-    rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)d_cols, (uint64_t)d_rows, (uint64_t)ldd * es,
-                            d_dtype == MT_F32 ? 16 : 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (narrow_store && args.n_dest <= 1) {
+      // box: 32 rows x 64 bytes (half of a warp's staging buffer), 64-byte swizzle
+      rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)d_cols, (uint64_t)d_rows, (uint64_t)ldd * es,
+                              d_dtype == MT_F32 ? 16 : 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+      args.tma_store = 2;
+    } else {
+      // box: 32 rows x 128 bytes (a warp's whole staging buffer), 128-byte swizzle
+      rc = make_tensor_map_2d(&md, dt, (int)es, d, (uint64_t)d_cols, (uint64_t)d_rows, (uint64_t)ldd * es,
+                              d_dtype == MT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
     if (rc != MT_OK) return rc;
   }
   static PeerMaps no_peers{};
