@@ -679,10 +679,9 @@ struct PairCfg {
   static constexpr int OFF_B = STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
-  // one 4 KiB output staging buffer per epilogue warp, used as two alternating 2 KiB halves (a
-  // second 4 KiB buffer per warp would cost a pipeline stage, which measured slower);
-  // 1024-byte aligned so the swizzle pattern of the TMA store lines up with the row index
-  // used when filling it
+  // one 4 KiB output staging buffer per epilogue warp: 32 rows x 128 bytes (a second buffer per
+  // warp would cost a pipeline stage, which measured slower); 1024-byte aligned so the swizzle
+  // pattern of the TMA store lines up with the row index used when filling it
   static constexpr int OFF_EPI = (OFF_SFB + STAGES * SFB_BYTES + 1023) / 1024 * 1024;
   static constexpr int EPI_BYTES = P_EPI_WARPS * 4096;
   static constexpr int OFF_BAR = OFF_EPI + EPI_BYTES;

@@ -344,10 +344,14 @@ class _QuantizedLinear(torch.autograd.Function):
             # SMs, instead of behind it.
             for h in late_handles:
                 h.wait()
-            half = _sm_count(dy.device) // 2
+            sms = _sm_count(dy.device)
+            try:        # SMs of the scattering GEMM (MT_TP_SCATTER_SMS, default half); the wgrad GEMM takes the rest
+                mine = min(sms - 8, max(8, int(os.environ.get("MT_TP_SCATTER_SMS", sms // 2)))) // 2 * 2
+            except ValueError:
+                mine = sms // 2
             box = []
-            joined = pg_rs.on_side_stream(lambda: box.append(run_wgrad(half)))
-            with _sm_margin(op, half):
+            joined = pg_rs.on_side_stream(lambda: box.append(run_wgrad(mine)))
+            with _sm_margin(op, sms - mine):
                 finish_dgrad = _gemm_reduce_scatter(pg_rs, dgrad_gemm, M, N, f"{site}:dx", defer=True)
             joined.wait()
             wgrad = _QuantizedLinear.reset_wgrad_if_needed(ctx, w, box[0])
