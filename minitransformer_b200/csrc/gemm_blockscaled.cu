@@ -73,6 +73,7 @@ struct GemmArgs {
   int64_t d_group_stride;        // MODE_GROUPED_K: elements between consecutive group outputs
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
+  int direct_bf16;               // pair kernel: plain bf16 rows go from registers to global memory in 32-byte pieces
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
   float* d_amax;                 // optional: atomic max of |stored value| (pair kernel, no accumulation)
   int n_dest, my_rank;           // n_dest > 1 (pair kernel, dense, staged stores): output rows are scattered over
@@ -98,9 +99,18 @@ struct GemmArgs {
 // Timing experiments exist only in builds with -DMT_TIMING_KNOBS (a separate library used for
 // A/B measurements); the shipped library reads no tuning variable from the environment.
 #ifdef MT_TIMING_KNOBS
+// Phase timestamps of one epilogue warp (CTA 0, first epilogue warp), summed over its tiles:
+// [0] tiles, [1] wait for the accumulator, [2] tensor-memory loads, [3] staging + stores, [4] whole tile.
+__device__ unsigned long long g_epi_prof[8];
+#define MT_PROF_T(var) const uint64_t var = global_timer_ns()
+#define MT_PROF_C(var) const long long var = clock64()
+#define MT_PROF_ADD(i, v) do { if (blockIdx.x == 0 && (threadIdx.x >> 5) == 2 && lane == 0) atomicAdd(&g_epi_prof[i], (unsigned long long)(v)); } while (0)
 #define MT_KNOB(args, bit) (((args).knobs & (bit)) != 0)
 static int env_knob(const char* name, int dflt) { const char* e = getenv(name); return e ? atoi(e) : dflt; }
 #else
+#define MT_PROF_T(var)
+#define MT_PROF_C(var)
+#define MT_PROF_ADD(i, v)
 #define MT_KNOB(args, bit) false
 static int env_knob(const char*, int dflt) { return dflt; }
 #endif
@@ -365,14 +375,43 @@ __device__ __forceinline__ void store_block_staged_wide(const GemmArgs& a, const
   const uint32_t swz = lane & 7;
   const bool f32 = a.d_dtype == MT_F32;
   const bool track = a.d_amax != nullptr;
+  const bool plain = has_k && a.bias == nullptr && !track;
   const int cols_per = f32 ? 32 : 64;
   const int nchunks = ncols / cols_per;
 #pragma unroll
   for (int ch = 0; ch < 4; ++ch) {
     if (ch >= nchunks) break;
+    MT_PROF_C(pc0);
     if (lane == 0) bulk_wait_read_all();
     __syncwarp();
-    if (!f32) {
+    MT_PROF_C(pc1);
+    if (plain && !f32) {
+      // the common case (no bias, no abs-max, K > 0) free of per-element branches: two multiplies
+      // and one packing conversion per pair of columns
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int col = (ch & 1) * 64 + j * 8 + t * 2;
+          const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])),
+                                                         __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])));
+          w[t] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else if (plain) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int col = ch * 32 + j * 4 + t;
+          v[t] = __fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31]));
+        }
+        *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    } else if (!f32) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {               // 16-byte piece j = columns 8j .. 8j+7 of the chunk
         uint32_t w[4];
@@ -409,8 +448,9 @@ __device__ __forceinline__ void store_block_staged_wide(const GemmArgs& a, const
         *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ swz) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
       }
     }
-    fence_proxy_async_smem();
-    __syncwarp();
+    MT_PROF_C(pc2);
+    if (!MT_KNOB(a, 16)) fence_proxy_async_smem();   // bit 4 (knob builds): no proxy fence
+    if (!MT_KNOB(a, 32)) __syncwarp();                // bit 5 (knob builds): no warp barrier before the store
     const int64_t c0 = colw + (int64_t)ch * cols_per;
     if (lane == 0) {
       if (row0 < map_rows && c0 < a.N && !MT_KNOB(a, 8)) {
@@ -419,6 +459,8 @@ __device__ __forceinline__ void store_block_staged_wide(const GemmArgs& a, const
       }
       bulk_commit_group();
     }
+    MT_PROF_C(pc3);
+    MT_PROF_ADD(5, pc1 - pc0); MT_PROF_ADD(6, pc2 - pc1); MT_PROF_ADD(7, pc3 - pc2);
   }
 }
 
@@ -882,10 +924,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   if (warp == 0) {
     // ================= TMA producer (one per CTA) =================
     if (elect_one()) {
-      uint32_t it = 0;
+      uint32_t it = 0, ph = 0;
+      int s = 0;
       bool alive = true;
       for (int tile = pair; tile < num_tiles && alive; tile += num_pairs) {
-        const PairTile t = pair_tile<kFormat, BN>(a, tile);
+        // bit 7 (knob builds): every tile loads the first tile's operands (no per-tile index arithmetic)
+        const PairTile t = pair_tile<kFormat, BN>(a, MT_KNOB(a, 128) ? pair : tile);
         const int32_t a_row = (int32_t)t.a_row0 + (int)rank * 128;
         const int32_t b_row = (int32_t)t.b_row0 + (int)rank * (BN / 2);
         const int32_t sfa_chunk0 = (int32_t)((t.sfa_rb + (int)rank) * a.kc_a + t.sfa_kc0);
@@ -893,16 +937,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         const int32_t sfb_kc0 = (int32_t)t.sfb_kc0;
         const int32_t a_kx0 = (int32_t)t.a_k_byte0, b_kx0 = (int32_t)t.b_k_byte0;
         const int num_k = t.num_k;
+        // slab of each operand the K step falls in and the step inside the slab, kept as counters
+        // (this single thread issues every load of the CTA: no divisions in its loop)
+        int sl_a = 0, ka = 0, sl_b = 0, kb = 0;
         for (int k = 0; k < num_k; ++k, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, a.status, DS_EMPTY_WAIT)) { alive = false; break; }
           const bool skip_b = MT_KNOB(a, 4);
           if (leader) mbar_expect_tx(&full_bar[s], 2 * (Cfg::STAGE_BYTES - (skip_b ? Cfg::B_BYTES : 0)));
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
-          // slab of each operand this K step falls in, and the step inside the slab
-          const int sl_a = k / a.a_slab_steps, ka = k - sl_a * a.a_slab_steps;
-          const int sl_b = k / a.b_slab_steps, kb = k - sl_b * a.b_slab_steps;
           tma_load_2d_pair(smem + Cfg::OFF_A + s * Cfg::A_BYTES, &map_a, bar, a_kx0 + ka * G_BLOCK_KB,
                            a_row + (int32_t)(sl_a * a.a_slab_rows));
           if (!skip_b)
@@ -914,6 +956,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
           for (int h = 0; h < NSB; ++h)
             tma_load_2d_pair(smem + Cfg::OFF_SFB + s * Cfg::SFB_BYTES + h * CH * 512, &map_sfb, bar, 0,
                              (int32_t)((sfb_rb0 + h) * a.kc_b + sl_b * a.b_slab_chunks) + sfb_kc0 + kb * CH);
+          if (++ka == a.a_slab_steps) { ka = 0; ++sl_a; }
+          if (++kb == a.b_slab_steps) { kb = 0; ++sl_b; }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -921,22 +966,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   } else if (warp == 1) {
     // ================= MMA issuer (leader CTA only) =================
     if (leader && elect_one()) {
-      uint32_t it = 0, tile_it = 0;
+      uint32_t it = 0, tile_it = 0, ph = 0;
+      int s = 0;
       bool alive = true;
+      const int dense_num_k = (int)((a.K_bytes + G_BLOCK_KB - 1) / G_BLOCK_KB);
       const uint32_t a_base = smem_u32(smem + Cfg::OFF_A), b_base = smem_u32(smem + Cfg::OFF_B);
       const uint32_t sfa_base = smem_u32(smem + Cfg::OFF_SFA), sfb_base = smem_u32(smem + Cfg::OFF_SFB);
       for (int tile = pair; tile < num_tiles && alive; tile += num_pairs, ++tile_it) {
-        const PairTile t = pair_tile<kFormat, BN>(a, tile);
-        const int num_k = t.num_k;
+        // The issuing thread needs the tile's K steps and where the tile starts inside its first
+        // 128-row chunk of B scales (in columns); with 256-wide tiles the latter is always 0 (the
+        // per-group row offset of B is a multiple of 128) and only grouped-K tiles differ in K, so
+        // the index arithmetic and table reads of the full tile description stay off this thread.
+        int num_k = dense_num_k;
+        uint32_t sfb_col_off = 0;
+        if (BN != 256 || (a.mode != MODE_DENSE && a.mode != MODE_GROUPED_ROWS)) {
+          const PairTile t = pair_tile<kFormat, BN>(a, tile);
+          num_k = t.num_k;
+          sfb_col_off = ((uint32_t)t.b_row0 & 127u) >> 5;
+        }
         const int as = tile_it % ACC;
         const uint32_t aph = (tile_it / ACC) & 1;
+        // bit 8 (knob builds, with bit 6): no wait for the epilogue, one accumulator for every tile
+        if (!MT_KNOB(a, 256))
         if (!mbar_wait_bounded(&acc_empty[as], aph ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + as * BN;
-        const uint32_t sfb_col_off = ((uint32_t)t.b_row0 & 127u) >> 5;   // tile start inside its first scale chunk, in columns
+        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + (MT_KNOB(a, 256) ? 0 : as * BN);
         for (int k = 0; k < num_k; ++k, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
           tc_fence_after();
           if (!MT_KNOB(a, 2) || k == 0) {
@@ -960,6 +1015,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
             issue_mma_pair<kFormat>(tmem_d, adesc + 2 * j, bdesc + 2 * j, idesc, sfa_t, sfb_t, (k > 0 || j > 0) ? 1u : 0u);
           }
           tc_commit_pair(&empty_bar[s], 3);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (alive) tc_commit_pair(&acc_full[as], 3);
       }
@@ -983,8 +1039,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       const int as = tile_it % ACC;
       const uint32_t aph = (tile_it / ACC) & 1;
       const uint32_t acc_empty_leader = map_to_cta(smem_u32(&acc_empty[as]), 0);
+      MT_PROF_T(pt0);
       if (!mbar_wait_bounded(&acc_full[as], aph, abort_flag, a.status, DS_ACC_FULL_WAIT)) { alive = false; break; }
       tc_fence_after();
+      MT_PROF_T(pt1);
       const int64_t row0 = t.d_row0 + rank * 128 + q * 32;   // first of this warp's 32 rows
       const int64_t row = row0 + lane;
       const bool row_ok = row >= t.d_row_lo && row < t.d_row_hi;
@@ -993,6 +1051,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       // Pull this warp's accumulator block into registers and hand tensor memory back to the
       // MMA issuer at once; conversion and stores overlap the MMAs that follow.
       uint32_t acc[4][32];
+#ifdef MT_TIMING_KNOBS
+      if (MT_KNOB(a, 64)) {   // bit 6: the accumulator is handed back unread
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        continue;
+      }
+#endif
 #pragma unroll
       for (int c = 0; c < 4; ++c)
         if (BN == 256 || c < 2 || half == 0) tc_ld_32x32(tmem_w + c * 32, acc[c]);
@@ -1000,7 +1066,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      MT_PROF_T(pt2);
+      MT_PROF_ADD(0, 1); MT_PROF_ADD(1, pt1 - pt0); MT_PROF_ADD(2, pt2 - pt1);
       if (MT_KNOB(a, 1)) continue;
+      if (a.direct_bf16 && num_k > 0) {
+        // Plain bf16 output (no bias, abs-max, accumulation or peer destination; 32-byte aligned
+        // rows): each lane converts its row and writes it as whole 32-byte sectors, masked by
+        // row, so blocks that straddle a group boundary need no special case. No shared-memory
+        // traffic, which the main loop saturates; measured 2 - 4 % faster than the staged stores
+        // at K >= 4096 and equal at short K.
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + t.d_base + row * a.ldd + colw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int col = 16 * i + 2 * j;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])),
+                                                           __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])));
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          if (16 * i < ncols && row_ok && colw + 16 * i + 16 <= a.N) st_global_v8(dst + 16 * i, w);
+        }
+        MT_PROF_T(pt3d);
+        MT_PROF_ADD(3, pt3d - pt2); MT_PROF_ADD(4, pt3d - pt0);
+        continue;
+      }
       // The staged path stores whole 32-row blocks; the tensor map clips at its own last row only,
       // so a block that straddles a group boundary takes the direct, row-masked path (as do
       // unaligned outputs and bf16 accumulation).
@@ -1014,24 +1105,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         }
         continue;
       }
+      const CUtensorMap* out_map = &map_d;
+      int64_t out_row = t.d_map_row0 + rank * 128 + q * 32;
       if (a.n_dest > 1) {
         // this warp's 32 rows belong to one destination rank (dest_rows is a multiple of 256):
         // they go to that rank's staging buffer, into the slice reserved for this rank
         const int dest = (int)(row0 / a.dest_rows);
-        const int64_t srow = (int64_t)a.my_rank * a.dest_rows + (row0 - (int64_t)dest * a.dest_rows);
-        store_block_staged_wide(a, &maps_peer.m[dest], acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, srow, a.map_rows,
-                                colw, alpha, num_k > 0, am);
-        continue;
+        out_map = &maps_peer.m[dest];
+        out_row = (int64_t)a.my_rank * a.dest_rows + (row0 - (int64_t)dest * a.dest_rows);
       }
 #ifdef MT_TIMING_KNOBS
-      if (a.tma_store == 2) {   // the 64-byte-wide variant, kept for comparison
+      if (a.tma_store == 2 && a.n_dest <= 1) {   // the 64-byte-wide variant, kept for comparison
         store_block_staged(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
-                           t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
+                           out_row, a.map_rows, colw, alpha, num_k > 0, am);
         continue;
       }
 #endif
-      store_block_staged_wide(a, &map_d, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane,
-                              t.d_map_row0 + rank * 128 + q * 32, a.map_rows, colw, alpha, num_k > 0, am);
+      store_block_staged_wide(a, out_map, acc, ncols, smem + Cfg::OFF_EPI + e * 4096, lane, out_row, a.map_rows,
+                              colw, alpha, num_k > 0, am);
+      MT_PROF_T(pt3);
+      MT_PROF_ADD(3, pt3 - pt2); MT_PROF_ADD(4, pt3 - pt0);
     }
     if (a.d_amax != nullptr) amax_publish(a.d_amax, am, lane);
   }
@@ -1182,6 +1275,11 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   }
   args.tma_store = (allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16)) ? allow_tma_store : 0;
   args.map_rows = d_rows;
+  static int allow_direct = -1;     // timing-knob builds only: MT_GEMM_DIRECT=0 keeps plain bf16 outputs on the staged path
+  if (allow_direct < 0) allow_direct = env_knob("MT_GEMM_DIRECT", 1);
+  args.direct_bf16 = allow_direct && d_dtype == MT_BF16 && !accumulate && args.bias == nullptr && args.d_amax == nullptr &&
+                     args.n_dest <= 1 && (args.mode == MODE_DENSE || args.mode == MODE_GROUPED_ROWS) &&
+                     (reinterpret_cast<uintptr_t>(d) & 31) == 0 && ldd % 16 == 0 && d_cols % 16 == 0;
   if (args.n_dest > 1 && args.tma_store != 1) return fail(MT_ERR_INVALID_ARG, "scattered output needs the staged store path");
   static int narrow_store = -1;   // timing-knob builds only: MT_GEMM_NARROW_STORE=1 selects the 64-byte-wide variant
   if (narrow_store < 0) narrow_store = env_knob("MT_GEMM_NARROW_STORE", 0);
@@ -1339,6 +1437,8 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
   MT_REQUIRE(N_out > 0 && N_out % 128 == 0, "%s: N (%lld) must be a positive multiple of 128", name, (long long)N_out);
   MT_REQUIRE(Kc > 0 && Kc % 128 == 0, "%s: K (%lld) must be a positive multiple of 128", name, (long long)Kc);
   MT_REQUIRE(ldd >= N_out, "%s: ldd smaller than N", name);
+  MT_REQUIRE(b_group_rows >= 0 && b_group_rows % 128 == 0, "%s: rows of B per group (%lld) must be a multiple of 128", name,
+             (long long)b_group_rows);
   if (R == 0) return MT_OK;
   MT_REQUIRE(a && sa && b && sb && d && plan, "%s: null pointer", name);
   MT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sa) && aligned16(sb) && aligned16(plan),
@@ -1392,6 +1492,17 @@ static int grouped_rows_gemm(const char* name, const uint8_t* a, const uint8_t* 
 }  // namespace mt
 
 extern "C" {
+
+#ifdef MT_TIMING_KNOBS
+// knob builds only: reads and clears the epilogue phase sums
+int mt_debug_epilogue_profile(unsigned long long* out8) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out8, mt::g_epi_prof, 64);
+  unsigned long long z[8] = {};
+  cudaMemcpyToSymbol(mt::g_epi_prof, z, 64);
+  return 0;
+}
+#endif
 
 int mt_grouped_gemm_mxfp8(const uint8_t* a, const uint8_t* sa_swz, const uint8_t* b, const uint8_t* sb_swz,
                           int64_t b_rows, int64_t ldb, const void* plan, int64_t G, int64_t rows, int64_t N, int64_t K,
