@@ -13,7 +13,8 @@ row-parallel fc2, sequence parallel, quantized all-gather) strong-scaled over N 
 
 `value` = GEMM flops of the step (2*M*N*K per GEMM, all ranks) / device time of the step
 with inputs resident in HBM. `e2e` = the same metric through the public `Linear` module with
-pinned host inputs copied to the device and a checksum read back inside every timed step.
+pinned host inputs copied to the device and a checksum read back inside every timed step (the
+copies of step i + 1 are issued on a copy stream while step i computes).
 `--impl reference` times the CPU restatement of the reference's PyTorch emulation on a
 bounded sample of the same workload on the host cores.
 """
@@ -267,6 +268,40 @@ def _tp_workload_single_gpu(torch, Linear, params, dev, kernels, steps=5, warmup
     flops = 6 * 2.0 * T * H * Fd
     return {"value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms, "steps": steps,
             "workload": f"NVFP4 MLP fc1+fc2 fwd+bwd, tokens={T}, hidden={H}, ffn={Fd}, no sharding"}
+
+
+class _HostInputPipeline:
+    """Pinned host inputs of the end-to-end step, double-buffered on the device: `take()` hands out
+    the buffers of the current step (waiting on the copy stream's event for them) and starts the
+    copies of the next step's inputs into the other pair, so that they cross PCIe under the
+    current step's kernels. Every step's inputs are still copied once per step inside the timed
+    region; the pair that a step reads was last read two steps earlier, whose result the host has
+    already read back."""
+
+    def __init__(self, torch, dev, host_tensors):
+        self.torch, self.host = torch, host_tensors
+        self.stream = torch.cuda.Stream(device=dev)
+        self.slots = [[torch.empty(t.shape, dtype=t.dtype, device=dev) for t in host_tensors] for _ in range(2)]
+        self.ready = [[torch.cuda.Event() for _ in host_tensors] for _ in range(2)]
+        self.step = 0
+        self._issue(0)
+
+    def _issue(self, slot):
+        with self.torch.cuda.stream(self.stream):
+            for dst, src, ev in zip(self.slots[slot], self.host, self.ready[slot]):
+                dst.copy_(src, non_blocking=True)
+                ev.record(self.stream)
+
+    def take(self):
+        """-> list of (device tensor, event to wait for before reading it)."""
+        slot = self.step & 1
+        self.step += 1
+        self._issue(slot ^ 1)
+        return list(zip(self.slots[slot], self.ready[slot]))
+
+    @property
+    def bytes_per_step(self):
+        return sum(t.numel() * t.element_size() for t in self.host)
 
 
 def _timed_loop(torch, fn, steps, warmup):
@@ -801,29 +836,27 @@ def run_gpu_arm(args):
             lin.weight.copy_(w)
         lin.weight.main_grad = torch.zeros((N_out, K_in), dtype=torch.float32, device=dev)
 
-        copy_stream = torch.cuda.Stream(device=dev)
-
         def module_step():
             """The same step through the public Linear module with inputs resident in HBM: autograd,
             the weight cache protocol and main_grad fusion inside the timed region."""
             xd = x.detach().requires_grad_(True)
             lin(xd, is_first_microbatch=True).backward(dy)
 
+        inputs = _HostInputPipeline(torch, dev, [x_h, dy_h])
+
         def e2e_step():
-            # the gradient's host->device copy runs on its own stream under the forward pass
+            # this step's x and dy were sent while the previous step ran; the next step's start now
             main = torch.cuda.current_stream(dev)
-            copy_stream.wait_stream(main)
-            with torch.cuda.stream(copy_stream):
-                dyd = dy_h.to(dev, non_blocking=True)
-            xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+            (xb, x_ready), (dyb, dy_ready) = inputs.take()
+            main.wait_event(x_ready)
+            xd = xb.detach().requires_grad_(True)
             y = lin(xd, is_first_microbatch=True)
-            main.wait_stream(copy_stream)
-            dyd.record_stream(main)
-            y.backward(dyd)
+            main.wait_event(dy_ready)
+            y.backward(dyb)
             chk = torch.stack([y.sum(dtype=torch.float32), xd.grad.sum(dtype=torch.float32), lin.weight.main_grad.sum()])
             return chk.cpu()
 
-        h2d = x_h.numel() * 2 + dy_h.numel() * 2
+        h2d = inputs.bytes_per_step
         d2h = 12
         launches_per_step = None
     else:
@@ -898,14 +931,27 @@ def run_gpu_arm(args):
             if use_graph:
                 step = graph_step
 
+        inputs = _HostInputPipeline(torch, dev, [x_h, dy_h])
+
         def e2e_step():
-            xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
-            dyd = dy_h.to(dev, non_blocking=True)
-            y = mlp(xd, dyd)
-            chk = torch.stack([y.sum(dtype=torch.float32), xd.grad.sum(dtype=torch.float32)])
+            main = torch.cuda.current_stream(dev)
+            (xb, x_ready), (dyb, dy_ready) = inputs.take()
+            main.wait_event(x_ready)
+            main.wait_event(dy_ready)
+            if use_graph:
+                # the captured step reads fixed buffers: refill them (device-to-device) and replay
+                with torch.no_grad():
+                    x_static.copy_(xb)
+                    dy.copy_(dyb)
+                y, xgrad = graph_step(True)
+            else:
+                xd = xb.detach().requires_grad_(True)
+                y = mlp(xd, dyb)
+                xgrad = xd.grad
+            chk = torch.stack([y.sum(dtype=torch.float32), xgrad.sum(dtype=torch.float32)])
             return chk.cpu()
 
-        h2d = x_h.numel() * 2 + dy_h.numel() * 2
+        h2d = inputs.bytes_per_step
         d2h = 8
 
     def barrier():
