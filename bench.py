@@ -233,7 +233,7 @@ def _physical_gpu_index(local_rank):
     return local_rank
 
 
-def _tp_workload_single_gpu(torch, Linear, params, dev, kernels, steps=5, warmup=3):
+def _tp_workload_single_gpu(torch, Linear, params, dev, kernels, steps=10, warmup=5):
     """The workload the N > 1 runs shard (tensor-parallel MLP, fc1 then fc2, fwd+bwd), unsharded on
     one GPU: the base of the strong-scaling series, reported beside the N = 1 headline."""
     T, H, Fd = C4["tokens"], C4["hidden"], C4["ffn"]
