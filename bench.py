@@ -34,12 +34,12 @@ UNIT = "TFLOP/s"
 C2 = dict(tokens=8192, in_features=4096, out_features=14336)
 # DRAM bytes (read + write) per GEMM launch of this workload, average of fprop / dgrad / wgrad,
 # from a one-pass ncu capture of this script (dram__bytes_read.sum + dram__bytes_write.sum:
-# 281.5, 167.3 and 281.4 MB). Slightly below the algorithmic bytes because part of each output
+# 275.3, 165.9 and 279.0 MB). Slightly below the algorithmic bytes because part of each output
 # is still in L2 when the kernel ends.
-GEMM_DRAM_BYTES_PER_LAUNCH = 243.0e6
+GEMM_DRAM_BYTES_PER_LAUNCH = 240.0e6
 # sm__pipe_tensor_cycles_active of the NVFP4 pair kernel under ncu (4096 x 9472 x 4096 case,
 # profiles/gemm_nvfp4_pair_4096x9472x4096.md)
-GEMM_TENSOR_PIPE_ACTIVE_PCT = 52.3
+GEMM_TENSOR_PIPE_ACTIVE_PCT = 59.7
 C3 = dict(experts=128, rows=131072, hidden=2048, ffn=768)
 C4 = dict(tokens=8192, hidden=8192, ffn=28672)
 CPU_SAMPLE = dict(tokens=512, in_features=4096, out_features=3584)
