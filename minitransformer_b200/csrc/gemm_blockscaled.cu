@@ -73,7 +73,7 @@ struct GemmArgs {
   int64_t d_group_stride;        // MODE_GROUPED_K: elements between consecutive group outputs
   int k_elems_per_byte_x2;       // 4 for FP4 (2 elements per byte), 2 for FP8
   int tma_store;                 // pair kernel: output goes through shared memory and TMA stores
-  int direct_bf16;               // pair kernel: plain bf16 rows go from registers to global memory in 32-byte pieces
+  int direct_store;              // pair kernel: plain output rows go from registers to global memory in 32-byte pieces
   int64_t map_rows;              // rows of the output tensor map (all groups' matrices when stacked)
   float* d_amax;                 // optional: atomic max of |stored value| (pair kernel, no accumulation)
   int n_dest, my_rank;           // n_dest > 1 (pair kernel, dense, staged stores): output rows are scattered over
@@ -896,8 +896,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_tiles = a.entries_dev ? min(a.num_tiles, *a.entries_dev * a.tiles_n) : a.num_tiles;
 
+  // Everything up to pdl_wait() touches shared memory, tensor memory and kernel parameters only:
+  // it may run while the kernel before this one in the stream is finishing.
+  pdl_trigger();
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
@@ -920,6 +922,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
   cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+  const int num_tiles = a.entries_dev ? min(a.num_tiles, *a.entries_dev * a.tiles_n) : a.num_tiles;
 
   if (warp == 0) {
     // ================= TMA producer (one per CTA) =================
@@ -1069,24 +1073,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       MT_PROF_T(pt2);
       MT_PROF_ADD(0, 1); MT_PROF_ADD(1, pt1 - pt0); MT_PROF_ADD(2, pt2 - pt1);
       if (MT_KNOB(a, 1)) continue;
-      if (a.direct_bf16 && num_k > 0) {
-        // Plain bf16 output (no bias, abs-max, accumulation or peer destination; 32-byte aligned
-        // rows): each lane converts its row and writes it as whole 32-byte sectors, masked by
-        // row, so blocks that straddle a group boundary need no special case. No shared-memory
-        // traffic, which the main loop saturates; measured 2 - 4 % faster than the staged stores
-        // at K >= 4096 and equal at short K.
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + t.d_base + row * a.ldd + colw;
+      if (a.direct_store && num_k > 0) {
+        // Plain output (no bias, abs-max, accumulation or peer destination; 32-byte aligned rows):
+        // each lane converts its row and writes it as whole 32-byte sectors, masked by row, so
+        // blocks that straddle a group boundary need no special case. No shared-memory traffic,
+        // which the main loop saturates; measured 2 - 4 % faster than the staged stores at
+        // K >= 4096 (bf16 and fp32) and equal at short K.
+        if (a.d_dtype == MT_BF16) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.d) + t.d_base + row * a.ldd + colw;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          uint32_t w[8];
+          for (int i = 0; i < 8; ++i) {
+            uint32_t w[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int col = 16 * i + 2 * j;
-            const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])),
-                                                           __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])));
-            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            for (int j = 0; j < 8; ++j) {
+              const int col = 16 * i + 2 * j;
+              const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])),
+                                                             __fmul_rn(alpha, __uint_as_float(acc[(col + 1) >> 5][(col + 1) & 31])));
+              w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            if (16 * i < ncols && row_ok && colw + 16 * i + 16 <= a.N) st_global_v8(dst + 16 * i, w);
           }
-          if (16 * i < ncols && row_ok && colw + 16 * i + 16 <= a.N) st_global_v8(dst + 16 * i, w);
+        } else {
+          float* dst = static_cast<float*>(a.d) + t.d_base + row * a.ldd + colw;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int col = 8 * i + j;
+              w[j] = __float_as_uint(__fmul_rn(alpha, __uint_as_float(acc[col >> 5][col & 31])));
+            }
+            if (8 * i < ncols && row_ok && colw + 8 * i + 8 <= a.N) st_global_v8(dst + 8 * i, w);
+          }
         }
         MT_PROF_T(pt3d);
         MT_PROF_ADD(3, pt3d - pt2); MT_PROF_ADD(4, pt3d - pt0);
@@ -1198,8 +1216,7 @@ static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, const 
     max_pairs = n;
   }
   const int pairs = std::min(args.num_tiles, std::max(1, max_pairs - (args.sm_margin + 1) / 2));
-  kern<<<2 * pairs, P_THREADS, Cfg::SMEM_ALLOC, st>>>(ma, mb, msa, msb, md, mp, args);
-  MT_CUDA(cudaGetLastError());
+  MT_CUDA(launch_pdl(kern, dim3(2 * pairs), dim3(P_THREADS), (size_t)Cfg::SMEM_ALLOC, st, ma, mb, msa, msb, md, mp, args));
   return MT_OK;
 }
 
@@ -1275,11 +1292,12 @@ static int launch_pair_any(int format, int pbn, const uint8_t* a, int64_t a_rows
   }
   args.tma_store = (allow_tma_store && aligned16(d) && ((size_t)ldd * es) % 16 == 0 && !(accumulate && d_dtype == MT_BF16)) ? allow_tma_store : 0;
   args.map_rows = d_rows;
-  static int allow_direct = -1;     // timing-knob builds only: MT_GEMM_DIRECT=0 keeps plain bf16 outputs on the staged path
+  static int allow_direct = -1;     // timing-knob builds only: MT_GEMM_DIRECT=0 keeps plain outputs on the staged path
   if (allow_direct < 0) allow_direct = env_knob("MT_GEMM_DIRECT", 1);
-  args.direct_bf16 = allow_direct && d_dtype == MT_BF16 && !accumulate && args.bias == nullptr && args.d_amax == nullptr &&
-                     args.n_dest <= 1 && (args.mode == MODE_DENSE || args.mode == MODE_GROUPED_ROWS) &&
-                     (reinterpret_cast<uintptr_t>(d) & 31) == 0 && ldd % 16 == 0 && d_cols % 16 == 0;
+  const int per_sector = d_dtype == MT_F32 ? 8 : 16;   // elements per 32-byte sector
+  args.direct_store = allow_direct && !accumulate && args.bias == nullptr && args.d_amax == nullptr && args.n_dest <= 1 &&
+                      (args.mode == MODE_DENSE || args.mode == MODE_GROUPED_ROWS) &&
+                      (reinterpret_cast<uintptr_t>(d) & 31) == 0 && ldd % per_sector == 0 && d_cols % per_sector == 0;
   if (args.n_dest > 1 && args.tma_store != 1) return fail(MT_ERR_INVALID_ARG, "scattered output needs the staged store path");
   static int narrow_store = -1;   // timing-knob builds only: MT_GEMM_NARROW_STORE=1 selects the 64-byte-wide variant
   if (narrow_store < 0) narrow_store = env_knob("MT_GEMM_NARROW_STORE", 0);

@@ -4,6 +4,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <cstdlib>
 #include "mt_common.cuh"
 #include "../../include/mt_b200_test.h"
 
@@ -28,6 +29,16 @@ int fail(int code, const char* fmt, ...) {
 
 // One status word per device that loads the library.
 __device__ int g_device_status = 0;
+
+bool pdl_enabled() {
+#ifdef MT_TIMING_KNOBS
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("MT_PDL"); on = e ? atoi(e) : 1; }
+  return on != 0;
+#else
+  return true;
+#endif
+}
 
 int* device_status_ptr() {
   static thread_local int cached_dev = -1;

@@ -35,6 +35,31 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 // it when a bounded wait expires. Returns its device address for the current device.
 int* device_status_ptr();
 
+// Programmatic dependent launch. A kernel started through launch_pdl() may become resident
+// while its predecessor in the stream is still draining its last blocks: its launch latency and
+// whatever it does before pdl_wait() (barrier set-up, tensor-memory allocation) then overlap the
+// predecessor's tail. pdl_wait() returns once the predecessor has completed and its writes are
+// visible; every thread of such a kernel calls it before touching global memory, so data
+// dependencies and the order of completion along the stream stay what they were.
+// pdl_trigger() lets this kernel's own successor do the same. Timing-knob builds read MT_PDL=0
+// to launch everything the ordinary way.
+bool pdl_enabled();
+
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 enum DeviceStatusBits : int {
   DS_TMA_WAIT = 1,       // consumer waited too long for a TMA/bulk copy
   DS_EMPTY_WAIT = 2,     // producer waited too long for a free smem stage
@@ -59,6 +84,9 @@ int make_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_byt
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;

@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_mxfp8_kernel(const __grid_
   const int64_t k0 = (int64_t)blockIdx.x * QT_COLS;
   int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
   int4 gt = make_int4(0, QT_ROWS, 0, 0);
+  pdl_trigger();
+  pdl_wait();   // before the plan, the tensor or anything else in global memory is read
   if (kGrouped) {
     if ((int)blockIdx.y >= *a.num_tiles_dev) return;   // uniform for the CTA: the plan holds fewer tiles
     gt = a.tiles[blockIdx.y];
@@ -264,8 +266,7 @@ static int launch_mxfp8(const CUtensorMap& map, const Mxfp8Args& args, dim3 grid
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[slot] = true;
   }
-  kern<<<grid, Q_THREADS, smem, st>>>(map, args);
-  MT_CUDA(cudaGetLastError());
+  MT_CUDA(launch_pdl(kern, grid, dim3(Q_THREADS), (size_t)smem, st, map, args));
   return MT_OK;
 }
 

@@ -115,7 +115,11 @@ __global__ void __launch_bounds__(256) amax_tiled_kernel(const uint16_t* __restr
   }
 }
 
-__global__ void copy_scalar_kernel(const float* src, float* dst) { *dst = *src; }
+__global__ void copy_scalar_kernel(const float* src, float* dst) {
+  pdl_trigger();
+  pdl_wait();
+  *dst = *src;
+}
 
 // ------------------------------------------------------------------------------------------
 // cast + transpose
@@ -145,11 +149,13 @@ __global__ void __launch_bounds__(Q_THREADS) quantize_nvfp4_kernel(const __grid_
   const int64_t k0 = (int64_t)blockIdx.x * QT_COLS;
   const int64_t m0 = (int64_t)blockIdx.y * QT_ROWS;
 
+  pdl_trigger();
   if (tid == 0) {
     sm.abort_flag = 0;
     mbar_init(&sm.bar, 1);
     mbar_fence_init();
   }
+  pdl_wait();   // the tensor and its abs-max come from the kernels before this one
   __syncthreads();
   if (tid == 0) {
     mbar_expect_tx(&sm.bar, QT_ROWS * QT_COLS * 2);
@@ -386,8 +392,7 @@ static int launch_nvfp4(const CUtensorMap& map, const Nvfp4Args& args, dim3 grid
     MT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set[slot] = true;
   }
-  kern<<<grid, Q_THREADS, smem, st>>>(map, args);
-  MT_CUDA(cudaGetLastError());
+  MT_CUDA(launch_pdl(kern, grid, dim3(Q_THREADS), (size_t)smem, st, map, args));
   return MT_OK;
 }
 
@@ -424,7 +429,7 @@ static int amax_impl(const void* x, int64_t rows, int64_t cols, int flags, float
     const int64_t n_vec = rows * cols / 8;
     int blocks = (int)std::min<int64_t>((n_vec + 255) / 256, 148 * 8);
     amax_plain_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), n_vec, amax_row);
-    if (amax_col) copy_scalar_kernel<<<1, 1, 0, st>>>(amax_row, amax_col);
+    if (amax_col) MT_CUDA(launch_pdl(copy_scalar_kernel, dim3(1), dim3(1), 0, st, (const float*)amax_row, amax_col));
   }
   MT_CUDA(cudaGetLastError());
   return MT_OK;
