@@ -731,10 +731,16 @@ def run_gpu_arm(args):
             dist.barrier()
             dist.destroy_process_group()
             raise SystemExit(3)
-        # base of the strong-scaling series: the same MLP unsharded, timed on rank 0 alone
+        # base of the strong-scaling series: the same MLP unsharded, timed on rank 0 alone. The
+        # other ranks block on the rendezvous store meanwhile (a socket wait): waiting in an NCCL
+        # barrier would spin one host thread per rank beside rank 0's enqueue loop.
+        store = dist.distributed_c10d._get_default_store()
         if rank == 0:
             base = _tp_workload_single_gpu(torch, Linear, params, dev, kernels)
             torch.cuda.empty_cache()
+            store.set("mt_bench_base_done", "1")
+        else:
+            store.wait(["mt_bench_base_done"])
         dist.barrier()
 
     if n == 1:

@@ -64,6 +64,8 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
 __global__ void __launch_bounds__(32) peer_exchange_kernel(PeerTable ctrl, int me, int n, int channel, float* vals,
                                                            int nvals, int* status, uint64_t timeout_ns) {
   const int t = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();   // what this rank announces to its peers is the work of the kernels before this one
   // this exchange's number: one more than the last one on this channel (only this kernel, one
   // launch at a time per channel, touches the counter)
   uint32_t* counter = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctrl.p[me]) + CTRL_EPOCH_OFFSET) + channel;
@@ -132,6 +134,8 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS) peer_gather_kernel(const GatherArgs a) {
   constexpr int UNIT = THREADS * 16 * 8;   // 8 loads of 16 bytes in flight per thread
+  pdl_trigger();
+  pdl_wait();
   int64_t first = 0;   // first unit of the current segment
   int64_t u = blockIdx.x;
   for (int s = 0; s < a.nseg; ++s) {
@@ -169,6 +173,8 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ out, float* amax_out) {
   const int64_t vecs = elems >> 3;   // 8 bf16 per 16 bytes
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  pdl_trigger();
+  pdl_wait();
   const uint4* src = reinterpret_cast<const uint4*>(stage);
   uint4* dst = reinterpret_cast<uint4*>(out);
   uint32_t am = 0;
@@ -265,9 +271,8 @@ int mt_peer_barrier(const void* const* ctrl, int n, int me, int channel, mt_stre
   MT_REQUIRE(channel >= 0 && channel < mt::PEER_CHANNELS, "mt_peer_barrier: channel %d out of range", channel);
   int* status = mt::device_status_ptr();
   if (!status) return mt::fail(MT_ERR_CUDA, "device status word not reachable");
-  mt::peer_exchange_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mt::make_table(ctrl, n), me, n, channel,
-                                                                            nullptr, 0, status, 2000000000ull);
-  MT_CUDA(cudaGetLastError());
+  MT_CUDA(mt::launch_pdl(mt::peer_exchange_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream),
+                         mt::make_table(ctrl, n), me, n, channel, (float*)nullptr, 0, status, (uint64_t)2000000000ull));
   return MT_OK;
 }
 
@@ -279,9 +284,8 @@ int mt_peer_allreduce_max(const void* const* ctrl, int n, int me, int channel, f
   MT_REQUIRE(vals != nullptr && nvals >= 1 && nvals <= 4, "mt_peer_allreduce_max: 1 to 4 values");
   int* status = mt::device_status_ptr();
   if (!status) return mt::fail(MT_ERR_CUDA, "device status word not reachable");
-  mt::peer_exchange_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(mt::make_table(ctrl, n), me, n, channel,
-                                                                            vals, nvals, status, 2000000000ull);
-  MT_CUDA(cudaGetLastError());
+  MT_CUDA(mt::launch_pdl(mt::peer_exchange_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream),
+                         mt::make_table(ctrl, n), me, n, channel, vals, nvals, status, (uint64_t)2000000000ull));
   return MT_OK;
 }
 
@@ -326,7 +330,7 @@ int mt_peer_gather(const void* const* shared, int n, int me, const int64_t* src_
     cfg.attrs = &attr; cfg.numAttrs = 1;
     MT_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   } else {
-    mt::peer_gather_kernel<128><<<ctas, 128, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    MT_CUDA(mt::launch_pdl(mt::peer_gather_kernel<128>, dim3((unsigned)ctas), dim3(128), 0, static_cast<cudaStream_t>(stream), a));
   }
   MT_CUDA(cudaGetLastError());
   return MT_OK;
@@ -341,9 +345,8 @@ int mt_peer_reduce_bf16(const void* stage, int n, int64_t rows, int64_t cols, vo
   if (rows * cols == 0) return MT_OK;
   const int64_t vecs = rows * cols / 8;
   const int blocks = (int)std::min<int64_t>((vecs + 255) / 256, 148 * 8);
-  mt::peer_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(stage), n, rows * cols, static_cast<__nv_bfloat16*>(out), amax_out);
-  MT_CUDA(cudaGetLastError());
+  MT_CUDA(mt::launch_pdl(mt::peer_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                         static_cast<const __nv_bfloat16*>(stage), n, rows * cols, static_cast<__nv_bfloat16*>(out), amax_out));
   return MT_OK;
 }
 

@@ -416,8 +416,14 @@ static int amax_impl(const void* x, int64_t rows, int64_t cols, int flags, float
   MT_REQUIRE(aligned16(x), "mt_amax_bf16: x must be 16-byte aligned");
   const bool rht = (flags & MT_Q_RHT) && amax_col != nullptr;
   MT_REQUIRE(!rht || rows % 16 == 0, "mt_amax_bf16: the Hadamard transform needs rows %% 16 == 0 (rows=%lld)", (long long)rows);
-  MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
-  if (rht || (col_sum && amax_col)) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+  // one memset node when the two scalars are neighbours in one buffer (how the Python front end allocates them)
+  const bool zero_col = rht || (col_sum && amax_col);
+  if (zero_col && amax_col == amax_row + 1) {
+    MT_CUDA(cudaMemsetAsync(amax_row, 0, 2 * sizeof(float), st));
+  } else {
+    MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));
+    if (zero_col) MT_CUDA(cudaMemsetAsync(amax_col, 0, sizeof(float), st));
+  }
   if (col_sum) MT_CUDA(cudaMemsetAsync(col_sum, 0, sizeof(float) * cols, st));
   if (rht || col_sum) {
     dim3 grid((unsigned)((cols + QT_COLS - 1) / QT_COLS), (unsigned)((rows + QT_ROWS - 1) / QT_ROWS));
