@@ -30,7 +30,10 @@ def _operands_mxfp8(M, N, Kd, seed=1):
 
 
 SHAPES = [(128, 128, 256), (128, 256, 256), (128, 128, 32), (256, 512, 1024), (100, 72, 96), (384, 640, 2048),
-          (1, 8, 64), (129, 257, 288), (512, 128, 4096)]
+          (1, 8, 64), (129, 257, 288), (512, 128, 4096),
+          # register-store epilogue of the pair kernel: a row mask inside a 32-row block, a last
+          # column tile of 16 (bf16) / 8 (fp32) columns
+          (300, 272, 512), (520, 264, 256)]
 
 
 @pytest.mark.parametrize("shape", SHAPES)
