@@ -31,6 +31,8 @@ struct __align__(128) Nvfp4Smem {
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) amax_plain_kernel(const uint4* __restrict__ x, int64_t n_vec,
                                                          float* __restrict__ amax_row) {
+  pdl_trigger();   // the kernel that reads the result may take its place on the SMs this one leaves
+  pdl_wait();
   uint32_t m = 0;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
     uint4 v = __ldg(x + i);
@@ -60,6 +62,8 @@ __global__ void __launch_bounds__(256) amax_tiled_kernel(const uint16_t* __restr
   const int64_t c0 = (int64_t)blockIdx.x * QT_COLS + lane * 4;
   const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS + warp * 16;
   float frow = 0.f, fcol = 0.f;
+  pdl_trigger();
+  pdl_wait();
   float cs[4] = {0.f, 0.f, 0.f, 0.f};
   if (c0 < cols && r0 < rows) {  // rows % 16 == 0, cols % 4 == 0: the strip is all-in or all-out
     uint32_t wa[16], wb[16];   // columns (c0, c0+1) and (c0+2, c0+3), one packed word per row
