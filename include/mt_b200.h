@@ -41,6 +41,16 @@ enum mt_quantize_flags {
 int mt_version(void);
 const char* mt_last_error_string(void);
 
+/* Launch overlap (process-wide switch, on by default). When on, the quantize, pair-GEMM and peer
+ * exchange / gather / reduce kernels are launched programmatically dependent on the kernel
+ * before them in the stream: they may become resident on the SMs which that kernel's last
+ * blocks leave, wait there for it to complete, and start without a launch gap; results and the
+ * order of completion along a stream are the same either way. A caller that runs other kernels
+ * on side streams beside these and has sized their grids to share the SMs should switch it off:
+ * blocks that are resident early hold SM resources which the side stream's kernels then find
+ * taken. Returns the previous setting. */
+int mt_set_launch_overlap(int enabled);
+
 /* Number of bytes of the GEMM-ready ("swizzled") scale-factor tensor for an operand with
  * `rows` rows and `k_blocks` scale factors per row: ceil(rows/128) x ceil(k_blocks/4)
  * chunks of 512 bytes, chunk (rb, kc) holding rows rb*128.. and blocks kc*4.., byte

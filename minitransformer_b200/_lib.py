@@ -29,6 +29,7 @@ _opts = _c.POINTER(GemmOpts)
 
 _SIGNATURES = {
     "mt_version": (_int, []),
+    "mt_set_launch_overlap": (_int, [_int]),
     "mt_last_error_string": (_c.c_char_p, []),
     "mt_swizzled_scale_bytes": (_i64, [_i64, _i64]),
     "mt_amax_bf16": (_int, [_vp, _i64, _i64, _int, _vp, _vp, _vp]),

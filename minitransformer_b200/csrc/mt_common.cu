@@ -30,14 +30,21 @@ int fail(int code, const char* fmt, ...) {
 // One status word per device that loads the library.
 __device__ int g_device_status = 0;
 
+static int g_launch_overlap = 1;
+
 bool pdl_enabled() {
 #ifdef MT_TIMING_KNOBS
   static int on = -1;
   if (on < 0) { const char* e = getenv("MT_PDL"); on = e ? atoi(e) : 1; }
-  return on != 0;
-#else
-  return true;
+  if (!on) return false;
 #endif
+  return g_launch_overlap != 0;
+}
+
+int set_launch_overlap(int enabled) {
+  const int before = g_launch_overlap;
+  g_launch_overlap = enabled ? 1 : 0;
+  return before;
 }
 
 int* device_status_ptr() {
@@ -118,6 +125,8 @@ int mt_test_bounded_wait(int64_t timeout_ns, mt_stream_t stream) {
 }
 
 int mt_version(void) { return 200; }
+
+int mt_set_launch_overlap(int enabled) { return mt::set_launch_overlap(enabled); }
 
 const char* mt_last_error_string(void) { return mt::g_error; }
 

@@ -41,9 +41,10 @@ int* device_status_ptr();
 // predecessor's tail. pdl_wait() returns once the predecessor has completed and its writes are
 // visible; every thread of such a kernel calls it before touching global memory, so data
 // dependencies and the order of completion along the stream stay what they were.
-// pdl_trigger() lets this kernel's own successor do the same. Timing-knob builds read MT_PDL=0
-// to launch everything the ordinary way.
+// pdl_trigger() lets this kernel's own successor do the same. mt_set_launch_overlap(0) launches
+// everything the ordinary way (timing-knob builds also read MT_PDL=0).
 bool pdl_enabled();
+int set_launch_overlap(int enabled);
 
 template <typename... P, typename... A>
 inline cudaError_t launch_pdl(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {

@@ -472,6 +472,12 @@ def grouped_wgrad_mxfp8(qa_t, sa_t_swz, qb_t, sb_t_swz, m_splits, *, out_dtype=t
     return out
 
 
+def set_launch_overlap(enabled: bool) -> bool:
+    """Process-wide switch of the programmatically dependent kernel launches (on by default, see
+    mt_set_launch_overlap in include/mt_b200.h); returns the previous setting."""
+    return bool(_lib.load().mt_set_launch_overlap(1 if enabled else 0))
+
+
 def read_device_status() -> int:
     """Status word raised by bounded device-side waits (0 = clean); clears it."""
     import ctypes

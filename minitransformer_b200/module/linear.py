@@ -664,6 +664,13 @@ class Linear(LayerLinearBaseModule):
             assert parameters_split is None, "Cannot split module parameters on 'meta' device."
         assert parallel_mode in ("row", "column", None), f"parallel_mode {parallel_mode} not supported"
         self.parallel_mode = parallel_mode
+        if self.tp_size > 1 and torch.cuda.is_available():
+            # The tensor-parallel paths run gathers, weight quantization and wgrad GEMMs on side
+            # streams with grids sized to share the SMs with the main stream's kernels; kernels
+            # that become resident ahead of their turn would take those SMs (the 8-rank MLP step
+            # measured slower with early launches than in the runs before they existed).
+            from .. import kernels
+            kernels.set_launch_overlap(False)
         if parallel_mode == "column":
             self.out_features = divide(out_features, self.tp_size)
         elif parallel_mode == "row":
