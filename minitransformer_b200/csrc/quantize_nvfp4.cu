@@ -439,7 +439,9 @@ static int amax_impl(const void* x, int64_t rows, int64_t cols, int flags, float
     const int64_t n_vec = rows * cols / 8;
     int blocks = (int)std::min<int64_t>((n_vec + 255) / 256, 148 * 8);
     amax_plain_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint4*>(x), n_vec, amax_row);
-    if (amax_col) MT_CUDA(launch_pdl(copy_scalar_kernel, dim3(1), dim3(1), 0, st, (const float*)amax_row, amax_col));
+    // without the transform both copies share one abs-max: a caller that passes the same scalar twice needs no copy
+    if (amax_col && amax_col != amax_row)
+      MT_CUDA(launch_pdl(copy_scalar_kernel, dim3(1), dim3(1), 0, st, (const float*)amax_row, amax_col));
   }
   MT_CUDA(cudaGetLastError());
   return MT_OK;

@@ -58,7 +58,8 @@ def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True, co
     same read."""
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
-    amax = torch.empty(2, dtype=torch.float32, device=x.device)
+    two = col_sum is not None or (need_col and with_rht)
+    amax = torch.empty(2 if two else 1, dtype=torch.float32, device=x.device)
     flags = MT_Q_RHT if with_rht else 0
     if col_sum is not None:
         assert col_sum.dtype == torch.float32 and col_sum.numel() == x.shape[1] and col_sum.is_contiguous()
@@ -66,10 +67,13 @@ def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True, co
                   amax[1:2].data_ptr() if need_col else None, col_sum.data_ptr(), _stream())
         _count(1 if x.numel() else 0)
     else:
+        # without the transform the transposed copy has the same abs-max: one scalar serves both
+        col = amax[1:2] if (need_col and with_rht) else amax[0:1]
         _lib.call("mt_amax_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
-                  amax[1:2].data_ptr() if need_col else None, _stream())
+                  col.data_ptr() if need_col else None, _stream())
         if x.numel():
-            _count(1 if with_rht else (2 if need_col else 1))
+            _count(1)
+        return amax[0:1], col
     return amax[0:1], (amax[1:2] if need_col else amax[0:1])
 
 
