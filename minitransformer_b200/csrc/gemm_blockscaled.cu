@@ -82,7 +82,8 @@ struct GemmArgs {
   int knobs;                     // builds with -DMT_TIMING_KNOBS only (results are wrong when set): bit 0 the
                                  // epilogue drains tensor memory but writes nothing, bit 1 scale factors are
                                  // copied for the first K step only, bit 2 B tiles are not loaded, bit 3 the
-                                 // epilogue stages the output in shared memory but issues no TMA store
+                                 // epilogue stages the output in shared memory but issues no TMA store,
+                                 // bit 6 the accumulator is handed back unread
 #endif
   int sm_margin;                 // host only: SMs the persistent grid leaves idle (room for a collective's
                                  // kernel that should run beside the GEMM instead of behind it)
@@ -449,8 +450,8 @@ __device__ __forceinline__ void store_block_staged_wide(const GemmArgs& a, const
       }
     }
     MT_PROF_C(pc2);
-    if (!MT_KNOB(a, 16)) fence_proxy_async_smem();   // bit 4 (knob builds): no proxy fence
-    if (!MT_KNOB(a, 32)) __syncwarp();                // bit 5 (knob builds): no warp barrier before the store
+    fence_proxy_async_smem();
+    __syncwarp();
     const int64_t c0 = colw + (int64_t)ch * cols_per;
     if (lane == 0) {
       if (row0 < map_rows && c0 < a.N && !MT_KNOB(a, 8)) {
@@ -932,8 +933,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
       int s = 0;
       bool alive = true;
       for (int tile = pair; tile < num_tiles && alive; tile += num_pairs) {
-        // bit 7 (knob builds): every tile loads the first tile's operands (no per-tile index arithmetic)
-        const PairTile t = pair_tile<kFormat, BN>(a, MT_KNOB(a, 128) ? pair : tile);
+        const PairTile t = pair_tile<kFormat, BN>(a, tile);
         const int32_t a_row = (int32_t)t.a_row0 + (int)rank * 128;
         const int32_t b_row = (int32_t)t.b_row0 + (int)rank * (BN / 2);
         const int32_t sfa_chunk0 = (int32_t)((t.sfa_rb + (int)rank) * a.kc_a + t.sfa_kc0);
@@ -990,11 +990,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
         }
         const int as = tile_it % ACC;
         const uint32_t aph = (tile_it / ACC) & 1;
-        // bit 8 (knob builds, with bit 6): no wait for the epilogue, one accumulator for every tile
-        if (!MT_KNOB(a, 256))
         if (!mbar_wait_bounded(&acc_empty[as], aph ^ 1, abort_flag, a.status, DS_ACC_EMPTY_WAIT)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + (MT_KNOB(a, 256) ? 0 : as * BN);
+        const uint32_t tmem_d = tmem_base + Cfg::TMEM_ACC + as * BN;
         for (int k = 0; k < num_k; ++k, ++it) {
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, a.status, DS_TMA_WAIT)) { alive = false; break; }
           tc_fence_after();

@@ -204,3 +204,30 @@ def test_bounded_wait_gives_up_and_reports():
     assert K.read_device_status() == 0      # cleared by the read
     x = torch.ones(8, device="cuda")
     assert float(x.sum()) == 8.0
+
+
+def test_launch_overlap_switch_changes_no_result():
+    """quantize -> GEMM -> quantize -> GEMM with the programmatically dependent launches on and
+    off: bit-identical outputs, clean status word, and the switch reports its previous setting."""
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn(1024, 512, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(768, 512, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+
+    def chain():
+        qx, qw = K.quantize_nvfp4(x, with_rht=True), K.quantize_nvfp4(w)
+        y = K.gemm_nvfp4(qx.data, qx.scale_swz, qx.amax_row, qw.data, qw.scale_swz, qw.amax_row)
+        qy = K.quantize_mxfp8(y, return_transpose=False)
+        qw8 = K.quantize_mxfp8(w.t().contiguous()[:, :768].contiguous(), return_transpose=False)
+        z = K.gemm_mxfp8(qy.data, qy.scale_swz, qw8.data, qw8.scale_swz, out_dtype=torch.float32)
+        return y, z
+
+    before = K.set_launch_overlap(False)
+    try:
+        y0, z0 = chain()
+        assert K.set_launch_overlap(True) is False
+        y1, z1 = chain()
+        assert K.set_launch_overlap(True) is True
+    finally:
+        K.set_launch_overlap(before)
+    assert torch.equal(y0, y1) and torch.equal(z0, z1)
+    assert K.read_device_status() == 0
