@@ -12,7 +12,8 @@ tensor-parallel MLP (tokens 8192, hidden 8192, ffn 28672; column-parallel fc1 th
 row-parallel fc2, sequence parallel, quantized all-gather) strong-scaled over N ranks.
 
 `value` = GEMM flops of the step (2*M*N*K per GEMM, all ranks) / device time of the step
-with inputs resident in HBM. `e2e` = the same metric through the public `Linear` module with
+with inputs resident in HBM (the per-kernel events behind `roofline` are recorded on every
+fourth timed step). `e2e` = the same metric through the public `Linear` module with
 pinned host inputs copied to the device and a checksum read back inside every timed step (the
 copies of step i + 1 are issued on a copy stream while step i computes).
 `--impl reference` times the CPU restatement of the reference's PyTorch emulation on a
@@ -987,12 +988,22 @@ def run_gpu_arm(args):
     sampler = ClockSampler(_physical_gpu_index(local_rank)) if rank == 0 else None
     if sampler:
         sampler.start()
-    ms_step, launches = run_timed(lambda: step(True), args.steps, args.warmup)
+    # Per-kernel events (the roofline's launch durations) are recorded inside the timed region on
+    # every fourth step only, the first timed step included: an event between two kernels costs a
+    # few microseconds and keeps the second from being launched ahead of the first one's end.
+    calls = {"n": 0}
+
+    def timed_step():
+        i = calls["n"] - args.warmup      # index inside the timed region (warm-up steps come first)
+        calls["n"] += 1
+        return step(i >= 0 and i % 4 == 0)
+
+    ms_step, launches = run_timed(timed_step, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
-    # only the events recorded during the timed region count
+    # every recorded event pair lies in the timed region
     torch.cuda.synchronize()
-    g_ms = [a.elapsed_time(b) for a, b in gemm_ms[-3 * args.steps:]] if n == 1 else []
-    q_ms = [a.elapsed_time(b) for a, b in quant_ms[-args.steps:]] if n == 1 else []
+    g_ms = [a.elapsed_time(b) for a, b in gemm_ms] if n == 1 else []
+    q_ms = [a.elapsed_time(b) for a, b in quant_ms] if n == 1 else []
     e2e_ms = float("nan") if quick and n > 1 else run_timed(e2e_step, max(2, min(args.steps, 10)), 2)[0]
 
     c5 = None
