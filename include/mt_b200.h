@@ -35,7 +35,9 @@ enum mt_dtype { MT_BF16 = 0, MT_F32 = 1 };
 enum mt_quantize_flags {
   MT_Q_2D = 1,       /* one scale per 16x16 block, shared by both copies */
   MT_Q_RHT = 2,      /* 16-point randomized Hadamard transform on the transposed copy */
-  MT_Q_ROWPAD16 = 4  /* scale tensors have their row count padded to a multiple of 16 */
+  MT_Q_ROWPAD16 = 4, /* scale tensors have their row count padded to a multiple of 16 */
+  MT_Q_AMAX_ZEROED = 8 /* mt_amax_bf16: the caller has set amax_row / amax_col to 0 (ordered before this call on
+                        * the stream); no memset is issued, so the call is one kernel launch */
 };
 
 int mt_version(void);
@@ -63,7 +65,8 @@ int64_t mt_swizzled_scale_bytes(int64_t rows, int64_t k_blocks);
  * amax_row <- max|x|. If amax_col is non-null: with MT_Q_RHT it receives the abs-max of the
  * Hadamard-transformed transpose (groups of 16 consecutive rows of one column, fixed sign
  * vector, scale 1/4, rounded to bf16), otherwise a copy of amax_row. Both are device fp32
- * scalars and are overwritten. rows % 16 == 0 is required with MT_Q_RHT; cols % 8 == 0 always.
+ * scalars and are overwritten (with MT_Q_AMAX_ZEROED they must hold 0 on entry).
+ * rows % 16 == 0 is required with MT_Q_RHT; cols % 8 == 0 always.
  * Replaces the two torch.max(torch.abs(.)) reductions of
  * miniTransformer/ops/nvfp4_quantize_op_ref.py:357-369. */
 int mt_amax_bf16(const void* x, int64_t rows, int64_t cols, int flags,

@@ -12,7 +12,7 @@ INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 HEADER_PATHS = (os.path.join(INCLUDE_DIR, "mt_b200.h"), os.path.join(INCLUDE_DIR, "mt_b200_test.h"))
 
 MT_BF16, MT_F32 = 0, 1
-MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16 = 1, 2, 4
+MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16, MT_Q_AMAX_ZEROED = 1, 2, 4, 8
 MT_MAX_PEERS, MT_PEER_CTRL_BYTES, MT_IPC_HANDLE_BYTES = 8, 4096, 64
 
 _c = ctypes

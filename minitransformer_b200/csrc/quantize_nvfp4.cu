@@ -422,7 +422,9 @@ static int amax_impl(const void* x, int64_t rows, int64_t cols, int flags, float
   MT_REQUIRE(!rht || rows % 16 == 0, "mt_amax_bf16: the Hadamard transform needs rows %% 16 == 0 (rows=%lld)", (long long)rows);
   // one memset node when the two scalars are neighbours in one buffer (how the Python front end allocates them)
   const bool zero_col = rht || (col_sum && amax_col);
-  if (zero_col && amax_col == amax_row + 1) {
+  if (flags & MT_Q_AMAX_ZEROED) {
+    // the caller's scalars are zero already: nothing between the previous kernel and this one
+  } else if (zero_col && amax_col == amax_row + 1) {
     MT_CUDA(cudaMemsetAsync(amax_row, 0, 2 * sizeof(float), st));
   } else {
     MT_CUDA(cudaMemsetAsync(amax_row, 0, sizeof(float), st));

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import MT_BF16, MT_F32, MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16  # noqa: F401
+from ._lib import MT_BF16, MT_F32, MT_Q_2D, MT_Q_RHT, MT_Q_ROWPAD16, MT_Q_AMAX_ZEROED  # noqa: F401
 
 
 # Number of kernels of this library launched through this module since it was last reset
@@ -52,6 +52,27 @@ class Quantized:
     amax_col: Optional[torch.Tensor] = None
 
 
+# Zero-initialised fp32 scalars for abs-max results, handed out from one tensor per (device, stream)
+# that a single fill kernel zeroes for 256 calls: with them an abs-max is one kernel launch and no
+# memset sits between it and the kernel before it. A slot is never handed out twice; a tensor
+# stays alive as long as a result refers to it. Not used while the stream is being captured: a
+# replayed graph has to zero its own scalars.
+_ZEROED = {}
+
+
+def _zeroed_scalars(device, n: int):
+    if torch.cuda.is_current_stream_capturing():
+        return None
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    pool = _ZEROED.get(key)
+    if pool is None or pool[1] + n > pool[0].numel():
+        pool = [torch.zeros(512, dtype=torch.float32, device=device), 0]
+        _ZEROED[key] = pool
+    i = pool[1]
+    pool[1] = i + 2          # slots stay 8-byte aligned
+    return pool[0][i:i + n]
+
+
 def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True, col_sum: Optional[torch.Tensor] = None):
     """Per-tensor abs-max (and abs-max of the Hadamard-transformed transpose) as device scalars.
     col_sum (optional fp32 [cols], rows % 16 == 0): also receives the column sums of x from the
@@ -59,8 +80,12 @@ def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True, co
     _require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     two = col_sum is not None or (need_col and with_rht)
-    amax = torch.empty(2 if two else 1, dtype=torch.float32, device=x.device)
     flags = MT_Q_RHT if with_rht else 0
+    amax = _zeroed_scalars(x.device, 2 if two else 1) if col_sum is None else None
+    if amax is not None:
+        flags |= MT_Q_AMAX_ZEROED
+    else:
+        amax = torch.empty(2 if two else 1, dtype=torch.float32, device=x.device)
     if col_sum is not None:
         assert col_sum.dtype == torch.float32 and col_sum.numel() == x.shape[1] and col_sum.is_contiguous()
         _lib.call("mt_amax_colsum_bf16", x.data_ptr(), x.shape[0], x.shape[1], flags, amax[0:1].data_ptr(),
@@ -73,8 +98,12 @@ def amax_bf16(x: torch.Tensor, with_rht: bool = False, need_col: bool = True, co
                   col.data_ptr() if need_col else None, _stream())
         if x.numel():
             _count(1)
-        return amax[0:1], col
-    return amax[0:1], (amax[1:2] if need_col else amax[0:1])
+        row = amax[0:1]
+        row._mt_pair = amax      # both scalars as one tensor (what a tensor-parallel abs-max exchange reduces)
+        return row, col
+    row = amax[0:1]
+    row._mt_pair = amax
+    return row, (amax[1:2] if need_col else row)
 
 
 def _out_bytes(into, key: str, shape, device) -> torch.Tensor:

@@ -84,7 +84,9 @@ class Nvfp4TiledQuantizeOp(Q.QuantizeOpBase):
             amax_row, amax_col = kernels.amax_bf16(x, with_rht=rht, need_col=return_transpose, col_sum=col_sum)
         if reduce_amax:
             # both scalars live in one 2-element buffer: one tiny exchange
-            both = amax_row._base if amax_row._base is not None else amax_row
+            both = getattr(amax_row, "_mt_pair", None)
+            if both is None:
+                both = amax_row._base if amax_row._base is not None else amax_row
             reduce = getattr(input_meta, "amax_reduce", None)
             if reduce is not None:
                 reduce(both)
