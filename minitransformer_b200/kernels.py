@@ -58,18 +58,20 @@ class Quantized:
 # stays alive as long as a result refers to it. Not used while the stream is being captured: a
 # replayed graph has to zero its own scalars.
 _ZEROED = {}
+_ZEROED_LOCK = threading.Lock()      # forward and autograd threads may quantize at the same time
 
 
 def _zeroed_scalars(device, n: int):
     if torch.cuda.is_current_stream_capturing():
         return None
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
-    pool = _ZEROED.get(key)
-    if pool is None or pool[1] + n > pool[0].numel():
-        pool = [torch.zeros(512, dtype=torch.float32, device=device), 0]
-        _ZEROED[key] = pool
-    i = pool[1]
-    pool[1] = i + 2          # slots stay 8-byte aligned
+    with _ZEROED_LOCK:
+        pool = _ZEROED.get(key)
+        if pool is None or pool[1] + n > pool[0].numel():
+            pool = [torch.zeros(512, dtype=torch.float32, device=device), 0]
+            _ZEROED[key] = pool
+        i = pool[1]
+        pool[1] = i + 2          # slots stay 8-byte aligned
     return pool[0][i:i + n]
 
 
