@@ -645,7 +645,8 @@ def _llama_step_bench(torch, dims, tp_group, dev, steps=3, warmup=2, peer=True):
         # loss sum the ranks' gradients, so each rank back-propagates its 1/n share
         (loss / n).backward()
 
-    graphed = tp_group is not None and os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"
+    graph_env = os.environ.get("MT_BENCH_CUDA_GRAPH", "")
+    graphed = tp_group is not None and (graph_env == "1" or (graph_env != "0" and peer))   # as for the MLP step
     # warm-up on a side stream, as graph capture of a backward pass wants it (the gradient
     # accumulation nodes remember the stream they first ran on)
     side = torch.cuda.Stream(device=dev)
@@ -904,7 +905,14 @@ def run_gpu_arm(args):
         # The sharded step holds ~50 short kernels: at 8 ranks it would be bound by the host
         # enqueueing them (about 1.6 ms of Python per step), so the whole forward + backward is
         # captured once into a CUDA graph and replayed (MT_BENCH_CUDA_GRAPH=0 times the eager step).
-        use_graph = os.environ.get("MT_BENCH_CUDA_GRAPH", "1") != "0"
+        # Replay is for the peer-memory exchanges (this library's own kernels). With the process
+        # group's collectives (MT_BENCH_TP_EXCHANGE=nccl, or no peer access on this box) the step is
+        # timed eagerly unless MT_BENCH_CUDA_GRAPH=1 asks for capture: NCCL collectives and their
+        # side streams inside a capture are not something this benchmark should depend on.
+        from minitransformer_b200.distributed.peer import get_peer_group
+        peer_active = peer and get_peer_group(tp_group, dev) is not None
+        graph_env = os.environ.get("MT_BENCH_CUDA_GRAPH", "")
+        use_graph = graph_env == "1" or (graph_env != "0" and peer_active)
         step = eager_step
         if use_graph:
             x_static = x.detach().clone().requires_grad_(True)
@@ -1011,7 +1019,7 @@ def run_gpu_arm(args):
         # configuration 5 on the same ranks (every rank takes part; reported in the N > 1 line)
         del fc1, fc2
         torch.cuda.empty_cache()
-        c5 = _llama_step_bench(torch, C5, tp_group, dev, peer=peer)
+        c5 = _llama_step_bench(torch, C5, tp_group, dev, peer=peer_active)
 
     status = kernels.read_device_status()
     if status != 0:
