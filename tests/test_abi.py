@@ -99,3 +99,23 @@ def test_padded_offsets_of_a_split_list():
     from minitransformer_b200 import kernels
     assert kernels.grouped_padded_offsets([3, 0, 5]) == [0, 128, 128, 256]
     assert kernels.grouped_padded_offsets([128, 129]) == [0, 128, 384]
+
+
+def test_launch_overlap_switch_reports_the_previous_setting():
+    """Pure host state: on by default, the call returns what was set before."""
+    lib = _lib.load()
+    before = lib.mt_set_launch_overlap(0)
+    try:
+        assert before in (0, 1)
+        assert lib.mt_set_launch_overlap(1) == 0
+        assert lib.mt_set_launch_overlap(1) == 1
+    finally:
+        lib.mt_set_launch_overlap(before)
+
+
+def test_quantize_flag_values_match_the_header():
+    import re
+    text = open(_lib.HEADER_PATHS[0]).read()
+    for name in ("MT_Q_2D", "MT_Q_RHT", "MT_Q_ROWPAD16", "MT_Q_AMAX_ZEROED"):
+        m = re.search(name + r"\s*=\s*(\d+)", text)
+        assert m and int(m.group(1)) == getattr(_lib, name), name
